@@ -1,0 +1,430 @@
+/*
+ * rexsc_oracle.c -- CPU restatement of the REX-SC stochastic-computing arithmetic.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker for the CUDA library, never
+ * the thing shipped or measured: only tests/, __graft_entry__.smoke() and the
+ * cpu_baseline / reference legs of bench.py may build, load or call it.
+ *
+ * Parity status: PINNED for the integer paths.  The restatement is checked
+ * bit-for-bit against the reference's own CPU extensions compiled unchanged
+ * (oracle/build_ref.py) and against golden vectors produced by them
+ * (tests/golden/).  The reference CPU code implements the XOR-feedback LFSR only,
+ * so the XNOR generator (the GPU reference's production setting) is pinned through
+ * the shared code path (same seeds, same accumulation) plus the LFSR period /
+ * state-space properties tested in tests/test_oracle.py, not by an executed
+ * reference.  The floating-point point-wise functions are "parity unpinned": the
+ * reference holds no test vectors for them and its GPU kernels cannot run where
+ * the fixtures are made; they are checked against the closed-form formulas in
+ * double precision.
+ *
+ * Every function cites the reference file:line (paths inside nanocad-lab/rex-sc)
+ * whose behaviour it restates.  The algorithms are written differently on purpose
+ * (bit-sliced ripple counters over time-packed words instead of the reference's
+ * channel-packed AND/POPC GEMM), so that an agreement is evidence and not an echo.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define REXO_MAX_SLOTS 1024 /* bit_length * gen_config upper bound handled here */
+#define REXO_WORDS (REXO_MAX_SLOTS / 64)
+
+/* ------------------------------------------------------------------------------------------
+ * LFSR step.  torch_c/sc-extension/sc_device.cuh:108-248 (GPU), sc_cpu.hpp:49-137 (CPU):
+ * new = ((v << 1) & (2^l - 1)) | fb, fb = XOR of the tap bits, XNOR variant = 1 - fb.
+ * l = 1, 2 are the toggling / counting generators of sc_device.cuh:242-248.
+ * ---------------------------------------------------------------------------------------- */
+int rexo_lfsr_next(int v, int l, int xnor)
+{
+    int fb;
+    switch (l) {
+    case 1: return 1 - v;
+    case 2: return (v + 1) % 4;
+    case 3: fb = ((v >> 2) ^ (v >> 1)) & 1; break;
+    case 4: fb = ((v >> 3) ^ (v >> 2)) & 1; break;
+    case 5: fb = ((v >> 4) ^ (v >> 2)) & 1; break;
+    case 6: fb = ((v >> 5) ^ (v >> 4)) & 1; break;
+    case 7: fb = ((v >> 6) ^ (v >> 5)) & 1; break;
+    case 8: fb = ((v >> 7) ^ (v >> 5) ^ (v >> 4) ^ (v >> 3)) & 1; break;
+    default: return v;
+    }
+    if (xnor) fb = 1 - fb;
+    return ((v << 1) & ((1 << l) - 1)) | fb;
+}
+
+/* bit_length -> lfsr_length when the caller passes lfsr_length < 0.
+ * torch_c/sc-extension/sc_cuda_kernel.cu:594-619 (cases 2 and 4 fall through to 3). */
+int rexo_lfsr_length_for(int bit_length)
+{
+    switch (bit_length) {
+    case 2: case 4: case 8: return 3;
+    case 16: return 4;
+    case 32: return 5;
+    case 64: return 6;
+    case 128: return 7;
+    case 256: return 8;
+    default: return -1;
+    }
+}
+
+/* Quantisers.  torch_c/sc-extension/sc_cuda.cpp:88-94 (ceil) and fixed_cuda.cpp:25-30 (round,
+ * torch.round = round-half-to-even = rintf under the default rounding mode). */
+void rexo_quantize_act(const float *x, int64_t n, int scale, int32_t *q)
+{
+    for (int64_t i = 0; i < n; i++) {
+        float v = x[i] * (float)scale;
+        v = fminf(fmaxf(v, 0.f), (float)(scale - 1));
+        q[i] = (int32_t)ceilf(v);
+    }
+}
+void rexo_quantize_weight(const float *w, int64_t n, int scale, int32_t *wp, int32_t *wn)
+{
+    for (int64_t i = 0; i < n; i++) {
+        float v = w[i] * (float)scale;
+        float p = fminf(fmaxf(v, 0.f), (float)(scale - 1));
+        float m = -fminf(fmaxf(v, (float)(1 - scale)), 0.f);
+        wp[i] = (int32_t)ceilf(p);
+        wn[i] = (int32_t)ceilf(m);
+    }
+}
+void rexo_quantize_act_round(const float *x, int64_t n, int scale, int32_t *q)
+{
+    for (int64_t i = 0; i < n; i++) {
+        float v = x[i] * (float)scale;
+        v = fminf(fmaxf(v, 0.f), (float)(scale - 1));
+        q[i] = (int32_t)rintf(v);
+    }
+}
+void rexo_quantize_weight_round(const float *w, int64_t n, int scale, int32_t *wp, int32_t *wn)
+{
+    for (int64_t i = 0; i < n; i++) {
+        float v = w[i] * (float)scale;
+        float p = fminf(fmaxf(v, 0.f), (float)(scale - 1));
+        float m = -fminf(fmaxf(v, (float)(1 - scale)), 0.f);
+        wp[i] = (int32_t)rintf(p);
+        wn[i] = (int32_t)rintf(m);
+    }
+}
+
+/* One element's stream, time-packed: bit `slot` of words[] is the stream value in that slot.
+ * torch_c/sc-extension/sc_cuda_conv.cu:70-92 (weights) and :149-163 (activations):
+ *   - advance the LFSR, then compare (value_t > state_{t+1});
+ *   - progressive loading masks the low bits of the value: cur_width = min(total_width,
+ *     (t / load_wait + 1) * load_width - 1), value_t = (value >> (total_width - cur_width)) << same;
+ *   - state and value live in int8 storage on the GPU (:37-40,127-128), restated with int8_t casts;
+ *   - gen_config g > 1: weight bit t goes to slots t*g .. t*g+g-1, activation bit t to slots
+ *     (t/g)*g*g + j*g + t%g for j < g. */
+static void stream_words(int value, int seed, int l, int xnor, int bit_length, int gen_config,
+                         int total_width, int load_width, int load_wait, int is_weight,
+                         uint64_t *words, int nwords)
+{
+    memset(words, 0, sizeof(uint64_t) * nwords);
+    int8_t state = (int8_t)seed;
+    int8_t val8 = (int8_t)value;
+    for (int t = 0; t < bit_length; t++) {
+        int cur_width = (t / load_wait + 1) * load_width - 1;
+        if (cur_width > total_width) cur_width = total_width;
+        int sh = total_width - cur_width;
+        int actual = ((int)val8 >> sh) << sh;
+        int s = rexo_lfsr_next((int)state, l, xnor);
+        state = (int8_t)s;
+        if (actual > s) {
+            for (int j = 0; j < gen_config; j++) {
+                int slot = is_weight ? t * gen_config + j
+                                     : (t / gen_config) * gen_config * gen_config + j * gen_config + t % gen_config;
+                words[slot >> 6] |= (uint64_t)1 << (slot & 63);
+            }
+        }
+    }
+}
+
+/* Exposed for the tests: the stream of one element as 0/1 bytes per slot. */
+void rexo_stream_bits(int value, int seed, int l, int xnor, int bit_length, int gen_config,
+                      int total_width, int load_width, int load_wait, int is_weight, uint8_t *bits)
+{
+    uint64_t w[REXO_WORDS];
+    int slots = bit_length * gen_config;
+    stream_words(value, seed, l, xnor, bit_length, gen_config, total_width, load_width, load_wait,
+                 is_weight, w, REXO_WORDS);
+    for (int s = 0; s < slots; s++) bits[s] = (uint8_t)((w[s >> 6] >> (s & 63)) & 1);
+}
+
+/* ------------------------------------------------------------------------------------------
+ * SC conv2d / linear forward on already quantised, already padded integers.
+ *
+ * Seeds: torch_c/sc-extension/sc_cuda_conv.cu:45,55-56 (weights, offset 13 for both signs,
+ * sc_device.cuh:33-34) and :133,139 (activations, offset 0):
+ *   seed = (offset + c*H*W + h*W + w) % (2^l - 1) + 1 - xnor,
+ * with (H, W) the extent of the tensor the element belongs to (padded activation, or the filter).
+ * Linear (sc_cuda_matmul.cu:59-78,165-177) is the H = W = 1 case with xnor ignored.
+ *
+ * Accumulation: torch_c/sc-extension/sc_device.cu:127-151 + sc_device.cuh:338-340,380-384:
+ *   out = sum over slots of min(count_slot, bin_config + 1),
+ *   count_slot = sum over (ci, kh, kw) of a_bit & w_bit,
+ * separately for the positive and the negative weight stream; the int16 store wraps
+ * (sc_device.cu:352-385).
+ *
+ * act: int32 [N][C][H][W]; wpos/wneg: int32 [Co][C][KH][KW]; out_*: int16 [N][Co][OH][OW].
+ * Returns 0, or a negative code for arguments outside what the reference path defines.
+ * ---------------------------------------------------------------------------------------- */
+int rexo_sc_conv2d(const int32_t *act, const int32_t *wpos, const int32_t *wneg,
+                   int N, int C, int H, int W, int Co, int KH, int KW,
+                   int stride_h, int stride_w,
+                   int bit_length, int lfsr_length,
+                   int total_width, int load_width, int load_wait,
+                   int bin_config, int gen_config, int xnor,
+                   int16_t *out_pos, int16_t *out_neg)
+{
+    if (lfsr_length < 0) lfsr_length = rexo_lfsr_length_for(bit_length);
+    if (lfsr_length < 1 || lfsr_length > 8) return -1;
+    if (gen_config < 1 || load_wait < 1 || bin_config < 0) return -2;
+    int slots = bit_length * gen_config;
+    if (slots > REXO_MAX_SLOTS || slots < 1) return -3;
+    int nw = (slots + 63) / 64;
+    int period = (1 << lfsr_length) - 1;
+    int OH = (H - KH) / stride_h + 1, OW = (W - KW) / stride_w + 1;
+    int64_t K = (int64_t)C * KH * KW;
+    int n_or = bin_config + 1;
+
+    /* streams of every activation element and every weight element */
+    int64_t n_act = (int64_t)N * C * H * W, n_w = (int64_t)Co * K;
+    uint64_t *sa = (uint64_t *)malloc(sizeof(uint64_t) * nw * (size_t)n_act);
+    uint64_t *sp = (uint64_t *)malloc(sizeof(uint64_t) * nw * (size_t)n_w);
+    uint64_t *sn = (uint64_t *)malloc(sizeof(uint64_t) * nw * (size_t)n_w);
+    if (!sa || !sp || !sn) { free(sa); free(sp); free(sn); return -4; }
+
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n_act; i++) {
+        int64_t chw = i % ((int64_t)C * H * W);
+        int seed = (int)((0 + chw) % period) + 1 - (xnor ? 1 : 0);
+        uint64_t tmp[REXO_WORDS];
+        stream_words(act[i], seed, lfsr_length, xnor, bit_length, gen_config, total_width, load_width,
+                     load_wait, 0, tmp, nw);
+        memcpy(sa + i * nw, tmp, sizeof(uint64_t) * nw);
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n_w; i++) {
+        int64_t ckk = i % K;
+        int seed = (int)((13 + ckk) % period) + 1 - (xnor ? 1 : 0);
+        uint64_t tmp[REXO_WORDS];
+        stream_words(wpos[i], seed, lfsr_length, xnor, bit_length, gen_config, total_width, load_width,
+                     load_wait, 1, tmp, nw);
+        memcpy(sp + i * nw, tmp, sizeof(uint64_t) * nw);
+        stream_words(wneg[i], seed, lfsr_length, xnor, bit_length, gen_config, total_width, load_width,
+                     load_wait, 1, tmp, nw);
+        memcpy(sn + i * nw, tmp, sizeof(uint64_t) * nw);
+    }
+
+    int64_t n_out = (int64_t)N * Co * OH * OW;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t o = 0; o < n_out; o++) {
+        int ow = (int)(o % OW);
+        int oh = (int)((o / OW) % OH);
+        int co = (int)((o / ((int64_t)OW * OH)) % Co);
+        int n = (int)(o / ((int64_t)OW * OH * Co));
+        int32_t res[2] = {0, 0};
+        for (int sign = 0; sign < 2; sign++) {
+            const uint64_t *sw = sign ? sn : sp;
+            for (int wd = 0; wd < nw; wd++) {
+                /* bit-sliced per-slot counters: plane[j] holds bit j of 64 counts */
+                uint64_t plane[20];
+                memset(plane, 0, sizeof(plane));
+                for (int ci = 0; ci < C; ci++)
+                    for (int kh = 0; kh < KH; kh++)
+                        for (int kw = 0; kw < KW; kw++) {
+                            int64_t ai = (((int64_t)n * C + ci) * H + (oh * stride_h + kh)) * W + (ow * stride_w + kw);
+                            int64_t wi = (((int64_t)co * C + ci) * KH + kh) * KW + kw;
+                            uint64_t x = sa[ai * nw + wd] & sw[wi * nw + wd];
+                            for (int j = 0; x && j < 20; j++) {
+                                uint64_t carry = plane[j] & x;
+                                plane[j] ^= x;
+                                x = carry;
+                            }
+                        }
+                int lim = slots - wd * 64;
+                if (lim > 64) lim = 64;
+                for (int b = 0; b < lim; b++) {
+                    int cnt = 0;
+                    for (int j = 0; j < 20; j++) cnt |= (int)((plane[j] >> b) & 1) << j;
+                    res[sign] += cnt < n_or ? cnt : n_or;
+                }
+            }
+        }
+        out_pos[o] = (int16_t)res[0];
+        out_neg[o] = (int16_t)res[1];
+    }
+    free(sa); free(sp); free(sn);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * FXP saturating conv.  torch_c/sc-extension/fixed_cuda_kernel.cu:20-41 (adders), :103-120
+ * (max_value, precision_diff), :153-206 (product order ci,kh,kw, K padded to a multiple of 8
+ * with zero products on the GPU), :208-268 (add_config >= 2 pairs) and the CPU twin
+ * fixed.cpp:56-78,95-194 (no K padding).  pad8 = 1 restates the GPU kernel, 0 the CPU one;
+ * they only differ once an accumulator has saturated with precision_diff > 0.
+ * Integer products and the OR-adder cross term wrap in 32 bits as the device code does.
+ * act int32 [N][C][H][W], weights int32 [Co][C][KH][KW], out int32 [N][Co][OH][OW].
+ * ---------------------------------------------------------------------------------------- */
+static inline int32_t wrap_mul(int32_t a, int32_t b) { return (int32_t)((uint32_t)a * (uint32_t)b); }
+static inline int32_t wrap_add(int32_t a, int32_t b) { return (int32_t)((uint32_t)a + (uint32_t)b); }
+static inline int32_t wrap_sub(int32_t a, int32_t b) { return (int32_t)((uint32_t)a - (uint32_t)b); }
+
+static inline int32_t sat_shift(int32_t v, int32_t max_value, int d)
+{
+    int32_t s = v < max_value ? v : max_value;
+    int rb_shift = d - 1 > 0 ? d - 1 : 0;
+    int32_t round_bit = (s >> rb_shift) % 2;
+    return (int32_t)((uint32_t)((s >> d) + round_bit) << d);
+}
+
+typedef struct { int32_t v1, v2; } or2_t;
+
+static inline or2_t add_or2(or2_t a, or2_t b, int32_t max_value, int p, int d)
+{
+    int64_t a1 = a.v1, a2 = a.v2, b1 = b.v1, b2 = b.v2;
+    int32_t o1 = a.v1 + b.v1 - (int32_t)((a1 * a2 * b2) >> (p * 4)) - (int32_t)((a2 * b1 * b2) >> (p * 4)) +
+                 (int32_t)((a1 * a2 * b1 * b2) >> (p * 6));
+    int32_t o2 = a.v2 + b.v2 - (int32_t)((a1 * a2 * b1) >> (p * 4)) - (int32_t)((a1 * b1 * b2) >> (p * 4)) +
+                 (int32_t)((a1 * a2 * b1 * b2) >> (p * 6));
+    or2_t r = {sat_shift(o1, max_value, d), sat_shift(o2, max_value, d)};
+    return r;
+}
+
+int rexo_fxp_conv2d(const int32_t *act, const int32_t *wpos, const int32_t *wneg,
+                    int N, int C, int H, int W, int Co, int KH, int KW,
+                    int stride_h, int stride_w,
+                    int add_config, int precision_in, int precision_out, int pad8,
+                    int32_t *out)
+{
+    if (add_config < 0 || precision_in < 1 || precision_in > 15) return -1;
+    int OH = (H - KH) / stride_h + 1, OW = (W - KW) / stride_w + 1;
+    int64_t K = (int64_t)C * KH * KW;
+    int64_t Kp = pad8 ? (K + 7) / 8 * 8 : K;
+    int pm = precision_in * 2 > precision_out ? precision_in * 2 : precision_out;
+    if (pm > 31) pm = 31;
+    int d = precision_in * 2 - precision_out;
+    if (d < 0) d = 0;
+    int32_t max_value = (int32_t)(((uint32_t)1 << pm) - 1);
+    max_value = (max_value >> d) << d;
+    int p2 = precision_in * 2;
+
+    int64_t n_out = (int64_t)N * Co * OH * OW;
+#pragma omp parallel for schedule(dynamic, 64)
+    for (int64_t o = 0; o < n_out; o++) {
+        int ow = (int)(o % OW);
+        int oh = (int)((o / OW) % OH);
+        int co = (int)((o / ((int64_t)OW * OH)) % Co);
+        int n = (int)(o / ((int64_t)OW * OH * Co));
+        int32_t acc[2] = {0, 0};
+        or2_t acc2[2] = {{0, 0}, {0, 0}};
+        int32_t pend[2] = {0, 0};
+        for (int64_t k = 0; k < Kp; k++) {
+            int32_t a = 0, wp = 0, wn = 0;
+            if (k < K) {
+                int ci = (int)(k / (KH * KW)), kh = (int)((k / KW) % KH), kw = (int)(k % KW);
+                a = act[(((int64_t)n * C + ci) * H + (oh * stride_h + kh)) * W + (ow * stride_w + kw)];
+                wp = wpos[(int64_t)co * K + k];
+                wn = wneg[(int64_t)co * K + k];
+            }
+            int32_t prod[2] = {wrap_mul(a, wp), wrap_mul(a, wn)};
+            for (int s = 0; s < 2; s++) {
+                if (add_config == 0) {
+                    acc[s] = sat_shift(wrap_add(acc[s], prod[s]), max_value, d);
+                } else if (add_config == 1) {
+                    int32_t cross = wrap_mul(acc[s], prod[s]) >> p2;
+                    acc[s] = sat_shift(wrap_sub(wrap_add(acc[s], prod[s]), cross), max_value, d);
+                } else {
+                    if ((k & 1) == 0) {
+                        pend[s] = prod[s];
+                        if (k + 1 >= Kp) { /* lone last product pairs with 0 */
+                            or2_t b = {pend[s], 0};
+                            acc2[s] = add_or2(acc2[s], b, max_value, precision_in, d);
+                        }
+                    } else {
+                        or2_t b = {pend[s], prod[s]};
+                        acc2[s] = add_or2(acc2[s], b, max_value, precision_in, d);
+                    }
+                }
+            }
+        }
+        if (add_config < 2) out[o] = wrap_sub(acc[0], acc[1]);
+        else out[o] = acc2[0].v1 + acc2[0].v2 - acc2[1].v1 - acc2[1].v2;
+    }
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Point-wise functions in double precision (tolerance reference for the float kernels).
+ * torch_c/sc-extension/sc_device.cuh:393-430 (forward), :466-505 (derivative), :507-545
+ * (bias / std polynomials), TorchScript twins utils_functional.py:286-302,421-459.
+ *   f_n(s)  = n - exp(-s) * sum_{i<n} (n-i) s^i / i!
+ *   f_n'(s) = exp(-s) * sum_{i<n} s^i / i!
+ *   y = x + B(x) + S(x) * eps,  dy/dx = 1 + B'(x)   (noise held constant)
+ * ---------------------------------------------------------------------------------------- */
+double rexo_orn_fwd(double s, int n)
+{
+    double e = exp(-s), term = 1.0, acc = 0.0;
+    for (int i = 0; i < n; i++) {
+        acc += (double)(n - i) * term;
+        term *= s / (double)(i + 1);
+    }
+    return (double)n - e * acc;
+}
+double rexo_orn_bwd(double s, int n)
+{
+    double e = exp(-s), term = 1.0, acc = 0.0;
+    for (int i = 0; i < n; i++) {
+        acc += term;
+        term *= s / (double)(i + 1);
+    }
+    return e * acc;
+}
+static double poly5(const double *c, double x)
+{
+    return c[0] + x * (c[1] + x * (c[2] + x * (c[3] + x * (c[4] + x * c[5]))));
+}
+static double dpoly5(const double *c, double x)
+{
+    return c[1] + x * (2 * c[2] + x * (3 * c[3] + x * (4 * c[4] + x * 5 * c[5])));
+}
+void rexo_orn_fwd_array(const double *s, int64_t n_elem, int n, double *out)
+{
+    for (int64_t i = 0; i < n_elem; i++) out[i] = rexo_orn_fwd(s[i], n);
+}
+void rexo_orn_bwd_array(const double *grad, const double *s, int64_t n_elem, int n, double *out)
+{
+    for (int64_t i = 0; i < n_elem; i++) out[i] = grad[i] * rexo_orn_bwd(s[i], n);
+}
+/* mean and std of the injected output for one element: y = x + B(x) + S(x) eps */
+void rexo_bias_std_moments(const double *s, int64_t n_elem, int n, const double *bias, const double *stdc,
+                           double *mean, double *sigma)
+{
+    for (int64_t i = 0; i < n_elem; i++) {
+        double x = rexo_orn_fwd(s[i], n);
+        mean[i] = x + poly5(bias, x);
+        sigma[i] = poly5(stdc, x);
+    }
+}
+void rexo_bias_std_bwd_array(const double *grad, const double *s, int64_t n_elem, int n, const double *bias,
+                             double *out)
+{
+    for (int64_t i = 0; i < n_elem; i++) {
+        double x = rexo_orn_fwd(s[i], n);
+        out[i] = grad[i] * (1.0 + dpoly5(bias, x)) * rexo_orn_bwd(s[i], n);
+    }
+}
+
+int rexo_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
