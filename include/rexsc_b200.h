@@ -1,0 +1,187 @@
+/*
+ * rexsc_b200.h -- C ABI of the B200 (sm_100a) implementation of the REX-SC stochastic-computing
+ * arithmetic: LFSR bit-stream generation, SC conv2d / linear forward with OR-n accumulation,
+ * the point-wise OR-n / calibration / error-injection kernels and the FXP saturating conv.
+ *
+ * Conventions
+ *   - every pointer named d_* is a DEVICE pointer on the current CUDA device;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises;
+ *   - functions return REXSC_OK (0) or a negative REXSC_E_* code and never throw;
+ *   - no global mutable state, no allocation: scratch is a caller-owned workspace whose size the
+ *     matching *_workspace_size() function reports (the reference keeps ~1.3 GiB of process-lifetime
+ *     scratch instead: torch_c/sc-extension/sc_cuda_kernel.cu:622-632, sc_device.cuh:711-714);
+ *   - each entry point cites the reference interface it replaces (paths inside nanocad-lab/rex-sc).
+ */
+#ifndef REXSC_B200_H
+#define REXSC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define REXSC_ABI_VERSION 1
+
+enum {
+    REXSC_OK = 0,
+    REXSC_E_BAD_ARG = -1,       /* null pointer, non-positive size, unknown enum value                  */
+    REXSC_E_UNSUPPORTED = -2,   /* valid in the reference but outside what this library implements      */
+    REXSC_E_WORKSPACE = -3,     /* workspace pointer null, misaligned or smaller than *_workspace_size  */
+    REXSC_E_TOO_LONG = -4,      /* dot product / stream longer than the accumulators can count          */
+    REXSC_E_CUDA = -5,          /* a CUDA runtime call or launch failed (see rexsc_last_cuda_error)     */
+    REXSC_E_DEVICE_TIMEOUT = -6 /* a bounded device-side wait gave up (reported by rexsc_workspace_status) */
+};
+
+enum { REXSC_F32 = 0, REXSC_F16 = 1, REXSC_BF16 = 2 };
+
+/* Which SC conv kernel to use.  AUTO picks the tiled shared-memory kernel when the shape fits it
+ * and the direct kernel otherwise; both give identical results. */
+enum { REXSC_KERNEL_AUTO = 0, REXSC_KERNEL_DIRECT = 1, REXSC_KERNEL_TILED = 2 };
+
+/*
+ * Shape / configuration of one SC conv2d (or, with h = w = kh = kw = 1, SC linear) forward.
+ * Field meanings follow the argument list of conv2d_generic_general_split_acc
+ * (torch_c/sc-extension/sc_cuda.cpp:87, bound at :124) so that a binding can fill it 1:1.
+ */
+typedef struct rexsc_sc_conv_desc {
+    int32_t batch, c_in, h_in, w_in; /* activation, logical NCHW extents before the op's own padding  */
+    int32_t c_out, kh, kw;           /* weight [c_out][c_in][kh][kw]                                   */
+    int32_t pad_h, pad_w;            /* zero padding added by the op (reference: padding[1], padding[0]) */
+    int32_t stride_h, stride_w;      /* reference: stride[0] on dim 2, stride[1] on dim 3              */
+    int32_t act_dtype, act_channels_last;  /* REXSC_F32/F16/BF16; 1 = dense NHWC memory, 0 = dense NCHW */
+    int32_t w_dtype, w_channels_last;      /* same for the weight (OHWI vs OIHW)                        */
+    int32_t out_channels_last;       /* memory format of the int16 outputs (reference: = activation's) */
+    int32_t bit_length;              /* stream length L                                                */
+    int32_t lfsr_length;             /* < 0: derived from bit_length as the reference does             */
+    int32_t bin_config;              /* OR-n with n = bin_config + 1; n >= dot-product length = plain count */
+    int32_t gen_config;              /* AND-g generator replication, 1 in every reference configuration */
+    int32_t xnor;                    /* XNOR-feedback LFSR and seed offset (conv only)                  */
+    int32_t prog_total_width, prog_load_width, prog_load_wait; /* progressive loading (7, 8, 1 = off)  */
+    int32_t linear_seeds;            /* 1: seeds depend on c_in only and xnor is ignored (SC linear)   */
+    int32_t kernel;                  /* REXSC_KERNEL_*                                                 */
+} rexsc_sc_conv_desc;
+
+/* Library identification. */
+int rexsc_abi_version(void);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char *rexsc_last_cuda_error(void);
+
+/*
+ * SC conv2d forward.  Replaces conv2d_generic_general_split_acc / conv2d_generic_general_acc
+ * (torch_c/sc-extension/sc_cuda.cpp:73-99) and everything below them:
+ * conv2d_generic_cuda_general_gemm (sc_cuda_kernel.cu:565-757), the stream generators
+ * (sc_cuda_conv.cu:3-166), im2col / GEMM / scatter kernels (sc_cuda_kernel.cu:367-562,
+ * sc_device.cu:186-386).  Pad + quantise + stream generation + OR-n accumulation in one call.
+ *   d_act     activation, dtype/layout per desc, [batch][c_in][h_in][w_in] logical
+ *   d_weight  weight, dtype/layout per desc
+ *   d_out_pos, d_out_neg  int16 [batch][c_out][oh][ow] in the layout desc->out_channels_last names;
+ *             either may alias nothing else; both are fully overwritten
+ */
+size_t rexsc_sc_conv2d_workspace_size(const rexsc_sc_conv_desc *desc);
+int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
+                        int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes,
+                        void *stream);
+
+/*
+ * SC linear forward.  Replaces linear_generic_general_acc (torch_c/sc-extension/sc_cuda.cpp:101-120)
+ * and linear_generic_cuda_general (sc_cuda_matmul.cu:584-747).  A convenience over the conv entry
+ * point: d_act is [batch][c_in], d_weight [c_out][c_in], outputs int16 [batch][c_out]; seeds depend
+ * on c_in only and the XOR LFSR is always used, as in the reference.
+ */
+size_t rexsc_sc_linear_workspace_size(int32_t batch, int32_t c_in, int32_t c_out, int32_t bit_length,
+                                      int32_t lfsr_length, int32_t gen_config);
+int rexsc_sc_linear_fwd(int32_t batch, int32_t c_in, int32_t c_out, int32_t act_dtype, int32_t w_dtype,
+                        int32_t bit_length, int32_t lfsr_length, int32_t bin_config, int32_t gen_config,
+                        int32_t prog_total_width, int32_t prog_load_width, int32_t prog_load_wait,
+                        const void *d_act, const void *d_weight, int16_t *d_out_pos, int16_t *d_out_neg,
+                        void *d_workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Reads the device status word of a workspace used by the call(s) above: synchronises `stream`,
+ * returns REXSC_OK or REXSC_E_DEVICE_TIMEOUT.  Optional (debug / tests); the forward calls
+ * themselves never synchronise.
+ */
+int rexsc_workspace_status(const void *d_workspace, void *stream);
+
+/*
+ * Stream words of the LFSR/comparator generator, for inspection and tests: fills
+ * d_lut[(phase * (1 << l) + value) * words + j] with bits 32j..32j+31 of the stream of an element
+ * whose seed index is congruent to `phase` modulo 2^l - 1 (bit t = time slot t).
+ * Restates the generation loops of torch_c/sc-extension/sc_cuda_conv.cu:70-92,149-163 and the
+ * LFSR formulas of sc_device.cuh:108-286.  words = ceil(bit_length * gen_config / 32).
+ */
+int rexsc_build_lfsr_lut(int32_t lfsr_length, int32_t bit_length, int32_t gen_config, int32_t xnor,
+                         int32_t prog_total_width, int32_t prog_load_width, int32_t prog_load_wait,
+                         int32_t is_weight, uint32_t *d_lut, void *stream);
+
+/*
+ * Point-wise OR-n activation.  Replaces or_approx_n_forward_acc / or_approx_n_backward_acc
+ * (torch_c/sc-extension/sc_cuda_pw.cu:708-746,767-811; kernels :15-69,86-144; scalar math
+ * sc_device.cuh:393-430,466-505).  or_n in 1..4.  Tensors are flat dense buffers of n_elem elements.
+ *   fwd: out_f32[i] = f_n(in[i])
+ *   bwd: grad_in_f32[i] = grad_out_f32[i] * f_n'(half(in[i]))   (the reference rounds the saved sum to fp16)
+ */
+int rexsc_orn_fwd(const void *d_in, int32_t in_dtype, float *d_out, int64_t n_elem, int32_t or_n, void *stream);
+int rexsc_orn_bwd(const float *d_grad_out, const void *d_in, int32_t in_dtype, float *d_grad_in,
+                  int64_t n_elem, int32_t or_n, void *stream);
+
+/*
+ * Fused OR-n(pos) - OR-n(neg) with 5th-order bias polynomial and std-polynomial * N(0,1) injection.
+ * Replaces or_approx_n_forward_bias_std_both_acc / or_approx_n_backward_bias_std_both_acc
+ * (torch_c/sc-extension/sc_cuda_pw.cu:863-927,952-1011; kernels :219-373,527-621; scalar math
+ * sc_device.cuh:507-657).  d_bias_coef / d_std_coef: fp32 device arrays with at least 6 entries.
+ * Noise: counter-based Philox4x32-10 keyed by `seed`, counter = (element index / 4, `offset`, sign);
+ * the caller advances `offset` per call (the reference keeps 320000 persistent cuRAND states instead,
+ * sc_cuda_pw.cu:699-706,878-882).  With all std coefficients zero the result does not depend on the noise.
+ */
+int rexsc_orn_bias_std_both_fwd(const void *d_pos, const void *d_neg, int32_t in_dtype, const float *d_bias_coef,
+                                const float *d_std_coef, float *d_out, int64_t n_elem, int32_t or_n,
+                                uint64_t seed, uint64_t offset, void *stream);
+int rexsc_orn_bias_std_both_bwd(const float *d_grad_out, const void *d_pos, const void *d_neg, int32_t in_dtype,
+                                const float *d_bias_coef, float *d_grad_pos, float *d_grad_neg, int64_t n_elem,
+                                int32_t or_n, void *stream);
+
+/*
+ * Single-sided variants.  Replace or_approx_n_forward_bias_std_acc / or_approx_n_backward_bias_std_acc
+ * (torch_c/sc-extension/sc_cuda_pw.cu:834-861,929-950; kernels :375-418,493-525).  The forward rounds
+ * its input to fp16 and returns fp16, as the reference does.
+ */
+int rexsc_orn_bias_std_fwd(const void *d_in, int32_t in_dtype, const float *d_bias_coef, const float *d_std_coef,
+                           void *d_out_f16, int64_t n_elem, int32_t or_n, uint64_t seed, uint64_t offset,
+                           void *stream);
+int rexsc_orn_bias_std_bwd(const float *d_grad_out, const void *d_in, int32_t in_dtype, const float *d_bias_coef,
+                           float *d_grad_in, int64_t n_elem, int32_t or_n, void *stream);
+
+/*
+ * FXP fixed-point conv with saturating accumulation.  Replaces conv2d_saturate_acc
+ * (torch_c/sc-extension/fixed_cuda.cpp:24-34) and conv2d_saturate_cuda / compute_saturate_general
+ * (fixed_cuda_kernel.cu:82-347).  Pad + quantise (round-half-even) + saturating accumulate.
+ * Activation and weight are dense NCHW / OIHW (the reference kernel indexes NCHW only,
+ * fixed_cuda_kernel.cu:125,179-182); output int32 NCHW [batch][c_out][oh][ow].
+ */
+typedef struct rexsc_fxp_conv_desc {
+    int32_t batch, c_in, h_in, w_in;
+    int32_t c_out, kh, kw;
+    int32_t pad_h, pad_w, stride_h, stride_w;
+    int32_t act_dtype, w_dtype;
+    int32_t add_config;    /* 0 fixed-point add, 1 simulated OR add, >= 2 simulated OR-2 pairs */
+    int32_t precision_in;  /* quantisation scale 2^precision_in                                */
+    int32_t precision_out; /* accumulator precision                                            */
+} rexsc_fxp_conv_desc;
+size_t rexsc_fxp_conv2d_workspace_size(const rexsc_fxp_conv_desc *desc);
+int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void *d_act, const void *d_weight,
+                         int32_t *d_out, void *d_workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Register-only LOP3 issue-rate probe used by the benchmark to measure the integer-ALU roofline the
+ * SC conv kernels are judged against.  Launches `blocks` x 256 threads doing `iters` x 64 dependent-free
+ * LOP3 per thread; d_sink receives one word per thread.  Total lane-ops = blocks*256*iters*64.
+ */
+int rexsc_alu_probe(int32_t blocks, int32_t iters, uint32_t *d_sink, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REXSC_B200_H */

@@ -1,0 +1,162 @@
+// extern "C" entry points of the SC conv / linear forward, plus library-wide helpers.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace rexsc {
+
+static thread_local char g_cuda_error[256] = "";
+
+void set_cuda_error(cudaError_t e, const char *where)
+{
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+static int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
+                        int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st)
+{
+    ConvPlan p;
+    int rc = make_conv_plan(desc, &p);
+    if (rc != REXSC_OK) return rc;
+    if (!d_act || !d_weight || !d_out_pos || !d_out_neg) return REXSC_E_BAD_ARG;
+    if (desc->kernel < REXSC_KERNEL_AUTO || desc->kernel > REXSC_KERNEL_TILED) return REXSC_E_BAD_ARG;
+    if (!d_workspace || workspace_bytes < p.total || (reinterpret_cast<uintptr_t>(d_workspace) & 255))
+        return REXSC_E_WORKSPACE;
+    uint8_t *ws = static_cast<uint8_t *>(d_workspace);
+    int *status = reinterpret_cast<int *>(ws + p.off_status);
+    uint32_t *lut_a = reinterpret_cast<uint32_t *>(ws + p.off_lut_a);
+    uint32_t *lut_w = reinterpret_cast<uint32_t *>(ws + p.off_lut_w);
+    uint32_t *A = reinterpret_cast<uint32_t *>(ws + p.off_A);
+    uint32_t *Wt = reinterpret_cast<uint32_t *>(ws + p.off_Wt);
+    uint32_t *S = reinterpret_cast<uint32_t *>(ws + p.off_S);
+
+    REXSC_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, st));
+    // The linear generators always use the XOR LFSR (torch_c/sc-extension/sc_cuda_matmul.cu:27-57).
+    const int xnor = desc->linear_seeds ? 0 : (desc->xnor ? 1 : 0);
+    rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
+                          desc->prog_load_width, desc->prog_load_wait, 0, lut_a, st);
+    if (rc != REXSC_OK) return rc;
+    rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
+                          desc->prog_load_width, desc->prog_load_wait, 1, lut_w, st);
+    if (rc != REXSC_OK) return rc;
+    rc = launch_expand_act(p, *desc, d_act, lut_a, A, st);
+    if (rc != REXSC_OK) return rc;
+    rc = launch_expand_weight(p, *desc, d_weight, lut_w, Wt, S, st);
+    if (rc != REXSC_OK) return rc;
+
+    const bool tiled_ok = conv_tiled_supported(p);
+    if (desc->kernel == REXSC_KERNEL_TILED && !tiled_ok) return REXSC_E_UNSUPPORTED;
+    if (desc->kernel != REXSC_KERNEL_DIRECT && tiled_ok)
+        return launch_conv_tiled(p, *desc, A, Wt, S, d_out_pos, d_out_neg, status, st);
+    return launch_conv_direct(p, *desc, A, Wt, S, d_out_pos, d_out_neg, st);
+}
+
+static void linear_desc(rexsc_sc_conv_desc *d, int32_t batch, int32_t c_in, int32_t c_out, int32_t act_dtype,
+                        int32_t w_dtype, int32_t bit_length, int32_t lfsr_length, int32_t bin_config,
+                        int32_t gen_config, int32_t tw, int32_t lw, int32_t lwait)
+{
+    memset(d, 0, sizeof(*d));
+    d->batch = batch; d->c_in = c_in; d->h_in = 1; d->w_in = 1;
+    d->c_out = c_out; d->kh = 1; d->kw = 1;
+    d->stride_h = 1; d->stride_w = 1;
+    d->act_dtype = act_dtype; d->w_dtype = w_dtype;
+    d->bit_length = bit_length; d->lfsr_length = lfsr_length; d->bin_config = bin_config;
+    d->gen_config = gen_config; d->xnor = 0;
+    d->prog_total_width = tw; d->prog_load_width = lw; d->prog_load_wait = lwait;
+    d->linear_seeds = 1;
+    d->kernel = REXSC_KERNEL_AUTO;
+}
+
+} // namespace rexsc
+
+using namespace rexsc;
+
+extern "C" int rexsc_abi_version(void) { return REXSC_ABI_VERSION; }
+
+extern "C" const char *rexsc_last_cuda_error(void) { return g_cuda_error; }
+
+extern "C" size_t rexsc_sc_conv2d_workspace_size(const rexsc_sc_conv_desc *desc)
+{
+    ConvPlan p;
+    if (make_conv_plan(desc, &p) != REXSC_OK) return 0;
+    return p.total;
+}
+
+extern "C" int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
+                                   int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace,
+                                   size_t workspace_bytes, void *stream)
+{
+    return conv_forward(desc, d_act, d_weight, d_out_pos, d_out_neg, d_workspace, workspace_bytes,
+                        (cudaStream_t)stream);
+}
+
+extern "C" size_t rexsc_sc_linear_workspace_size(int32_t batch, int32_t c_in, int32_t c_out, int32_t bit_length,
+                                                 int32_t lfsr_length, int32_t gen_config)
+{
+    rexsc_sc_conv_desc d;
+    linear_desc(&d, batch, c_in, c_out, REXSC_F32, REXSC_F32, bit_length, lfsr_length, 0, gen_config, 7, 8, 1);
+    return rexsc_sc_conv2d_workspace_size(&d);
+}
+
+extern "C" int rexsc_sc_linear_fwd(int32_t batch, int32_t c_in, int32_t c_out, int32_t act_dtype, int32_t w_dtype,
+                                   int32_t bit_length, int32_t lfsr_length, int32_t bin_config, int32_t gen_config,
+                                   int32_t prog_total_width, int32_t prog_load_width, int32_t prog_load_wait,
+                                   const void *d_act, const void *d_weight, int16_t *d_out_pos, int16_t *d_out_neg,
+                                   void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    rexsc_sc_conv_desc d;
+    linear_desc(&d, batch, c_in, c_out, act_dtype, w_dtype, bit_length, lfsr_length, bin_config, gen_config,
+                prog_total_width, prog_load_width, prog_load_wait);
+    return conv_forward(&d, d_act, d_weight, d_out_pos, d_out_neg, d_workspace, workspace_bytes,
+                        (cudaStream_t)stream);
+}
+
+extern "C" int rexsc_workspace_status(const void *d_workspace, void *stream)
+{
+    if (!d_workspace) return REXSC_E_BAD_ARG;
+    int host = 0;
+    REXSC_CUDA_CHECK(cudaMemcpyAsync(&host, d_workspace, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    REXSC_CUDA_CHECK(cudaStreamSynchronize((cudaStream_t)stream));
+    return host == 0 ? REXSC_OK : REXSC_E_DEVICE_TIMEOUT;
+}
+
+extern "C" int rexsc_build_lfsr_lut(int32_t lfsr_length, int32_t bit_length, int32_t gen_config, int32_t xnor,
+                                    int32_t prog_total_width, int32_t prog_load_width, int32_t prog_load_wait,
+                                    int32_t is_weight, uint32_t *d_lut, void *stream)
+{
+    if (!d_lut) return REXSC_E_BAD_ARG;
+    return launch_build_lut(lfsr_length, bit_length, gen_config, xnor ? 1 : 0, prog_total_width, prog_load_width,
+                            prog_load_wait, is_weight ? 1 : 0, d_lut, (cudaStream_t)stream);
+}
+
+// ---- ALU issue-rate probe ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) alu_probe_kernel(int iters, uint32_t *sink)
+{
+    // 16 accumulators, one three-input logic op each, four times per iteration = 64 LOP3 per iteration.
+    uint32_t r[16];
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < 16; i++) r[i] = t * 2654435761u + i;
+    uint32_t a = t ^ 0x9e3779b9u;
+    for (int it = 0; it < iters; it++) {
+#pragma unroll
+        for (int rep = 0; rep < 4; rep++) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) r[i] = (r[i] & a) ^ r[(i + 1) & 15];
+        }
+        a += 0x01010101u;
+    }
+    uint32_t x = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) x ^= r[i];
+    sink[t] = x;
+}
+
+extern "C" int rexsc_alu_probe(int32_t blocks, int32_t iters, uint32_t *d_sink, void *stream)
+{
+    if (blocks < 1 || iters < 1 || !d_sink) return REXSC_E_BAD_ARG;
+    alu_probe_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(iters, d_sink);
+    REXSC_LAUNCH_CHECK("alu_probe_kernel");
+    return REXSC_OK;
+}

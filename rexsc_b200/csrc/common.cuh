@@ -1,0 +1,104 @@
+// Shared declarations of the rexsc_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/rexsc_b200.h"
+
+namespace rexsc {
+
+// ---- error plumbing -------------------------------------------------------------------------
+void set_cuda_error(cudaError_t e, const char *where);
+#define REXSC_CUDA_CHECK(expr)                                  \
+    do {                                                        \
+        cudaError_t _e = (expr);                                \
+        if (_e != cudaSuccess) {                                \
+            ::rexsc::set_cuda_error(_e, #expr);                 \
+            return REXSC_E_CUDA;                                \
+        }                                                       \
+    } while (0)
+#define REXSC_LAUNCH_CHECK(what)                                \
+    do {                                                        \
+        cudaError_t _e = cudaGetLastError();                    \
+        if (_e != cudaSuccess) {                                \
+            ::rexsc::set_cuda_error(_e, what);                  \
+            return REXSC_E_CUDA;                                \
+        }                                                       \
+    } while (0)
+
+// ---- geometry of the tiled SC conv kernel (shared by the weight packer and the kernel) -------
+constexpr int kChunkC = 8;        // input channels staged per pipeline step
+constexpr int kTileN = 32;        // output channels per CTA
+constexpr int kWarpN = 4;         // output channels per warp (8 warps x 4 = kTileN)
+constexpr int kPlaneWords = 1536; // shared-memory words per staged channel plane (patch capacity)
+constexpr int kMaxKhw = 49;       // largest filter footprint the tiled kernel stages (7x7)
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Everything the kernels need to know about one SC conv call, derived on the host.
+struct ConvPlan {
+    // generator
+    int l;         // LFSR length in bits
+    int period;    // 2^l - 1
+    int nvals;     // 2^l
+    int slots;     // bit_length * gen_config
+    int words;     // ceil(slots / 32)
+    int n_or;      // OR-n limit (bin_config + 1)
+    // geometry
+    int N, C, H, W;       // activation before padding
+    int Hp, Wp;           // after the op's own padding
+    int Co, KH, KW, KHW;
+    int OH, OW;
+    int sh, sw, ph, pw;
+    long long NHW;        // N * Hp * Wp
+    long long NHWp;       // plane stride of the activation words (multiple of 4)
+    long long M;          // N * OH * OW
+    int Cpad, CCH;        // c_in padded to kChunkC, number of channel chunks
+    int NT;               // ceil(Co / kTileN)
+    long long Kdot;       // C * KH * KW, length of the dot product
+    // workspace layout (byte offsets)
+    size_t off_status, off_lut_a, off_lut_w, off_A, off_Wt, off_S, total;
+    // per-plane sizes in words
+    long long a_plane_words; // Cpad * NHWp  (one stream-word plane of activations)
+    long long w_plane_words; // NT * CCH * KHW * kChunkC * kTileN
+};
+
+int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p);
+
+// ---- host launchers (each enqueues on `st`, returns REXSC_*) -----------------------------------
+int launch_build_lut(int l, int bit_length, int gen_config, int xnor, int tw, int lw, int lwait, int is_weight,
+                     uint32_t *d_lut, cudaStream_t st);
+int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const uint32_t *d_lut,
+                      uint32_t *d_A, cudaStream_t st);
+int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_w, const uint32_t *d_lut,
+                         uint32_t *d_Wt, uint32_t *d_S, cudaStream_t st);
+int launch_conv_direct(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
+                       const uint32_t *d_S, int16_t *d_pos, int16_t *d_neg, cudaStream_t st);
+bool conv_tiled_supported(const ConvPlan &p);
+int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
+                      const uint32_t *d_S, int16_t *d_pos, int16_t *d_neg, int *d_status, cudaStream_t st);
+
+// ---- device helpers -----------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float load_as_float(const T *p, long long i);
+template <> __device__ __forceinline__ float load_as_float<float>(const float *p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float load_as_float<__half>(const __half *p, long long i)
+{
+    return __half2float(p[i]);
+}
+template <> __device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16 *p, long long i)
+{
+    return __bfloat162float(p[i]);
+}
+
+// ceil(clamp(x * scale, 0, scale - 1)); exact in fp32 because scale is a power of two.
+__device__ __forceinline__ int quant_ceil_unipolar(float x, float scale)
+{
+    float v = x * scale;
+    v = fminf(fmaxf(v, 0.f), scale - 1.f);
+    return (int)ceilf(v);
+}
+
+} // namespace rexsc

@@ -1,0 +1,368 @@
+// Tiled SC conv forward for sm_100a: implicit GEMM over time-packed stream words on the integer ALU.
+//
+//   M = N*OH*OW output pixels, N = Cout, K = Cin*KH*KW; one 32-bit word per (element, 32 time slots).
+//   CTA tile  = (32*TM) pixels x 32 output channels, 256 threads = 8 warps.
+//   Warp w owns output channels 4w..4w+3 for ALL rows of the tile; lane owns rows lane + 32*j, j < TM.
+//   Because every lane of a warp works on the same output channels at the same k, the sign of the weight
+//   (which of the reference's two weight streams is non-zero) is warp-uniform: the kernel branches on it
+//   and updates only the positive or only the negative accumulators, halving the LOP3 count.
+//
+//   Shared memory holds, per pipeline stage, the raw activation patch of 8 input channels
+//   ([c][P - P_lo], P the flattened padded pixel index; the filter taps are address offsets kh*Wp + kw into
+//   it, so nothing is im2col-expanded) plus the 8-channel weight block and its sign words.  Stages are
+//   filled by bulk async copies (cp.async.bulk, one per channel plane + two for the weights) issued by one
+//   thread and tracked by an mbarrier; every wait on it is bounded and reports through a status word.
+//
+//   OR-n accumulation (torch_c/sc-extension/sc_device.cu:127-151, sc_device.cuh:338-340,380-384) as a
+//   thermometer over 32 time slots at once:  x = a & w;  T_j |= T_{j-1} & x (j = n..2);  T_1 |= x;
+//   result = sum_j popc(T_j) = sum_t min(count_t, n).  One launch handles one 32-slot word plane; longer
+//   streams run one launch per plane and add into the int16 output.
+#include "common.cuh"
+
+namespace rexsc {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kStages = 2;
+constexpr uint32_t kWaitLimit = 1u << 22; // bounded mbarrier polling (each poll may itself block briefly)
+
+struct TiledArgs {
+    int Hp, Wp, OH, OW, sh, sw, KH, KW, KHW, CCH, Co;
+    long long M, NHWp;
+    int out_nhwc, accumulate;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and the caller records it) instead of spinning for ever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kWaitLimit; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int NOR> __device__ __forceinline__ void thermo_update(uint32_t (&t)[NOR], uint32_t a, uint32_t w)
+{
+    const uint32_t x = a & w;
+#pragma unroll
+    for (int j = NOR - 1; j >= 1; j--) t[j] |= t[j - 1] & x;
+    t[0] |= x;
+}
+
+template <int NOR, int TM>
+__global__ void __launch_bounds__(kThreads, 1)
+sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t *__restrict__ Wt,
+                     const uint32_t *__restrict__ S, int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg,
+                     int *__restrict__ status)
+{
+    constexpr int BM = 32 * TM;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t a_stage_bytes = kChunkC * kPlaneWords * 4;
+    const uint32_t b_stage_bytes = (uint32_t)a.KHW * kChunkC * kTileN * 4;
+    const uint32_t s_stage_bytes = (uint32_t)a.KHW * (kTileN / kWarpN) * 4;
+    uint8_t *a_base = smem;
+    uint8_t *b_base = a_base + kStages * a_stage_bytes;
+    uint8_t *s_base = b_base + kStages * b_stage_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_base + kStages * s_stage_bytes);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nt = blockIdx.x;                       // output-channel tile fastest: CTAs sharing a patch run together
+    const long long m0 = (long long)blockIdx.y * BM; // first output pixel of the tile
+
+    // flattened padded pixel of output pixel m at filter tap (0,0)
+    auto pix0 = [&](long long m) -> long long {
+        int ow = (int)(m % a.OW);
+        long long t = m / a.OW;
+        int oh = (int)(t % a.OH);
+        long long n = t / a.OH;
+        return (n * a.Hp + (long long)oh * a.sh) * a.Wp + (long long)ow * a.sw;
+    };
+    const long long m_last = (m0 + BM <= a.M ? m0 + BM : a.M) - 1;
+    const long long P_lo = pix0(m0) & ~3LL;
+    const long long P_hi = pix0(m_last) + (long long)(a.KH - 1) * a.Wp + (a.KW - 1);
+    const uint32_t patch_words = (uint32_t)(((P_hi - P_lo + 1) + 3) & ~3LL);
+
+    int off[TM];
+#pragma unroll
+    for (int j = 0; j < TM; j++) {
+        long long m = m0 + lane + 32 * j;
+        if (m > m_last) m = m_last;
+        off[j] = (int)(pix0(m) - P_lo);
+    }
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) mbar_init(smem_u32(&bars[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const bool patch_ok = patch_words <= (uint32_t)kPlaneWords;
+    bool failed = !patch_ok; // never true when the host-side fit check passed; guards the copies below
+
+    auto issue = [&](int it) {
+        const int s = it & 1;
+        const uint32_t bar = smem_u32(&bars[s]);
+        const uint32_t a_bytes = patch_words * 4;
+        mbar_expect_tx(bar, kChunkC * a_bytes + b_stage_bytes + s_stage_bytes);
+        const uint32_t *src = A + (size_t)it * kChunkC * a.NHWp + P_lo;
+        const uint32_t dst = smem_u32(a_base + s * a_stage_bytes);
+#pragma unroll
+        for (int cc = 0; cc < kChunkC; cc++)
+            bulk_g2s(dst + cc * kPlaneWords * 4, src + (size_t)cc * a.NHWp, a_bytes, bar);
+        const size_t blk = ((size_t)nt * a.CCH + it) * a.KHW;
+        bulk_g2s(smem_u32(b_base + s * b_stage_bytes), Wt + blk * (kChunkC * kTileN), b_stage_bytes, bar);
+        bulk_g2s(smem_u32(s_base + s * s_stage_bytes), S + blk * (kTileN / kWarpN), s_stage_bytes, bar);
+    };
+
+    int issued = 0;
+    if (tid == 0 && !failed) {
+        issue(0);
+        issued = 1;
+        if (a.CCH > 1) { issue(1); issued = 2; }
+    }
+
+    uint32_t tp[TM][kWarpN][NOR], tn[TM][kWarpN][NOR];
+#pragma unroll
+    for (int j = 0; j < TM; j++)
+#pragma unroll
+        for (int c = 0; c < kWarpN; c++)
+#pragma unroll
+            for (int q = 0; q < NOR; q++) { tp[j][c][q] = 0u; tn[j][c][q] = 0u; }
+
+    for (int it = 0; it < a.CCH; it++) {
+        const int s = it & 1;
+        if (!failed) {
+            if (!mbar_wait_bounded(smem_u32(&bars[s]), (uint32_t)((it >> 1) & 1))) failed = true;
+        }
+        // every thread must agree before touching the stage or re-arming it
+        failed = __syncthreads_or(failed ? 1 : 0) != 0;
+        if (failed) break;
+
+        const uint32_t *As = reinterpret_cast<const uint32_t *>(a_base + s * a_stage_bytes);
+        const uint32_t *Bs = reinterpret_cast<const uint32_t *>(b_base + s * b_stage_bytes) + warp * kWarpN;
+        const uint32_t *Ss = reinterpret_cast<const uint32_t *>(s_base + s * s_stage_bytes) + warp;
+
+        int kw = 0, koff = 0, krow = 0;
+#pragma unroll 1
+        for (int khw = 0; khw < a.KHW; khw++) {
+            const uint32_t sg = Ss[khw * (kTileN / kWarpN)];
+            const uint32_t *ap[TM];
+#pragma unroll
+            for (int j = 0; j < TM; j++) ap[j] = As + off[j] + koff;
+            const uint32_t *bp = Bs + khw * (kChunkC * kTileN);
+#pragma unroll
+            for (int cc = 0; cc < kChunkC; cc++) {
+                uint32_t av[TM];
+#pragma unroll
+                for (int j = 0; j < TM; j++) av[j] = ap[j][cc * kPlaneWords];
+                const uint4 w4 = *reinterpret_cast<const uint4 *>(bp + cc * kTileN);
+                const uint32_t wv[kWarpN] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int c = 0; c < kWarpN; c++) {
+                    if (sg & (1u << (cc * kWarpN + c))) {
+#pragma unroll
+                        for (int j = 0; j < TM; j++) thermo_update<NOR>(tn[j][c], av[j], wv[c]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < TM; j++) thermo_update<NOR>(tp[j][c], av[j], wv[c]);
+                    }
+                }
+            }
+            // next filter tap: offset kh*Wp + kw into the patch
+            if (++kw == a.KW) { kw = 0; krow += a.Wp; }
+            koff = krow + kw;
+        }
+        __syncthreads(); // stage s fully consumed
+        if (tid == 0 && it + kStages < a.CCH) { issue(it + kStages); issued = it + kStages + 1; }
+    }
+
+    if (failed) {
+        // report, then give copies that may still be in flight a bounded chance to land before exiting
+        if (tid == 0) {
+            atomicExch(status, patch_ok ? 1 : 2);
+            for (int it = 0; it < issued; it++)
+                (void)mbar_wait_bounded(smem_u32(&bars[it & 1]), (uint32_t)((it >> 1) & 1));
+        }
+        return;
+    }
+
+    // ---- epilogue: popcount the thermometers, store int16 in the requested layout -----------------
+    const int co0 = nt * kTileN + warp * kWarpN;
+    const size_t ohw = (size_t)a.OH * a.OW;
+#pragma unroll
+    for (int j = 0; j < TM; j++) {
+        const long long m = m0 + lane + 32 * j;
+        if (m > m_last) continue;
+        int rp[kWarpN], rn[kWarpN];
+#pragma unroll
+        for (int c = 0; c < kWarpN; c++) {
+            rp[c] = 0; rn[c] = 0;
+#pragma unroll
+            for (int q = 0; q < NOR; q++) { rp[c] += __popc(tp[j][c][q]); rn[c] += __popc(tn[j][c][q]); }
+        }
+        if (a.out_nhwc) {
+            const size_t base = (size_t)m * a.Co + co0;
+            if ((a.Co & 3) == 0 && co0 + kWarpN <= a.Co) {
+                uint2 *pp = reinterpret_cast<uint2 *>(out_pos + base);
+                uint2 *pn = reinterpret_cast<uint2 *>(out_neg + base);
+                if (a.accumulate) {
+                    const uint2 op = *pp, on = *pn;
+                    rp[0] += (int16_t)(op.x & 0xffff); rp[1] += (int16_t)(op.x >> 16);
+                    rp[2] += (int16_t)(op.y & 0xffff); rp[3] += (int16_t)(op.y >> 16);
+                    rn[0] += (int16_t)(on.x & 0xffff); rn[1] += (int16_t)(on.x >> 16);
+                    rn[2] += (int16_t)(on.y & 0xffff); rn[3] += (int16_t)(on.y >> 16);
+                }
+                uint2 vp, vn;
+                vp.x = (uint32_t)(rp[0] & 0xffff) | ((uint32_t)rp[1] << 16);
+                vp.y = (uint32_t)(rp[2] & 0xffff) | ((uint32_t)rp[3] << 16);
+                vn.x = (uint32_t)(rn[0] & 0xffff) | ((uint32_t)rn[1] << 16);
+                vn.y = (uint32_t)(rn[2] & 0xffff) | ((uint32_t)rn[3] << 16);
+                *pp = vp;
+                *pn = vn;
+            } else {
+#pragma unroll
+                for (int c = 0; c < kWarpN; c++) {
+                    if (co0 + c < a.Co) {
+                        if (a.accumulate) { rp[c] += out_pos[base + c]; rn[c] += out_neg[base + c]; }
+                        out_pos[base + c] = (int16_t)rp[c];
+                        out_neg[base + c] = (int16_t)rn[c];
+                    }
+                }
+            }
+        } else {
+            const size_t pixel = (size_t)(m % (long long)ohw);
+            const size_t img = (size_t)(m / (long long)ohw);
+#pragma unroll
+            for (int c = 0; c < kWarpN; c++) {
+                if (co0 + c < a.Co) {
+                    const size_t oi = (img * a.Co + co0 + c) * ohw + pixel;
+                    if (a.accumulate) { rp[c] += out_pos[oi]; rn[c] += out_neg[oi]; }
+                    out_pos[oi] = (int16_t)rp[c];
+                    out_neg[oi] = (int16_t)rn[c];
+                }
+            }
+        }
+    }
+}
+
+// Upper bound of the patch length (in words) any tile of BM output pixels can need.
+long long patch_bound(const ConvPlan &p, int BM)
+{
+    long long dR = (BM + p.OW - 2) / p.OW;         // output-row boundaries a tile can cross
+    long long dI = (dR + p.OH - 1) / p.OH;         // image boundaries among them
+    long long row_step = (long long)p.sh * p.Wp;
+    long long img_step = (long long)p.Wp * (p.Hp - (long long)(p.OH - 1) * p.sh);
+    long long extra = img_step > row_step ? img_step - row_step : 0;
+    long long delta = dR * row_step + dI * extra + (long long)(p.OW - 1) * p.sw;
+    return 3 + delta + (long long)(p.KH - 1) * p.Wp + (p.KW - 1) + 1 + 3;
+}
+
+size_t tiled_smem_bytes(const ConvPlan &p)
+{
+    return (size_t)kStages * ((size_t)kChunkC * kPlaneWords * 4 + (size_t)p.KHW * kChunkC * kTileN * 4 +
+                              (size_t)p.KHW * (kTileN / kWarpN) * 4) +
+           kStages * sizeof(uint64_t);
+}
+
+int pick_tm(const ConvPlan &p)
+{
+    const int pref = p.n_or <= 2 ? 8 : 4; // OR-3 / OR-4 thermometers need the smaller register tile
+    for (int tm = pref; tm >= 4; tm -= 4)
+        if (patch_bound(p, 32 * tm) <= kPlaneWords) return tm;
+    return 0;
+}
+
+template <int NOR, int TM>
+int launch_one(const ConvPlan &p, const TiledArgs &a, const uint32_t *A, const uint32_t *Wt, const uint32_t *S,
+               int16_t *pos, int16_t *neg, int *status, cudaStream_t st)
+{
+    const size_t smem = tiled_smem_bytes(p);
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+        REXSC_CUDA_CHECK(cudaFuncSetAttribute(sc_conv_tiled_kernel<NOR, TM>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
+        configured = 227 * 1024;
+    }
+    const long long tiles_m = (p.M + 32 * TM - 1) / (32 * TM);
+    if (tiles_m > 65535) {
+        // grid.y limit: fall back to the caller's other kernel
+        return REXSC_E_UNSUPPORTED;
+    }
+    dim3 grid((unsigned)p.NT, (unsigned)tiles_m);
+    sc_conv_tiled_kernel<NOR, TM><<<grid, kThreads, smem, st>>>(a, A, Wt, S, pos, neg, status);
+    REXSC_LAUNCH_CHECK("sc_conv_tiled_kernel");
+    return REXSC_OK;
+}
+
+} // namespace
+
+bool conv_tiled_supported(const ConvPlan &p)
+{
+    if (p.n_or < 1 || p.n_or > 4) return false;
+    if (p.KHW > kMaxKhw) return false;
+    if (tiled_smem_bytes(p) > 227 * 1024) return false;
+    int tm = pick_tm(p);
+    if (tm == 0) return false;
+    if ((p.M + 32 * tm - 1) / (32 * tm) > 65535) return false;
+    return true;
+}
+
+int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
+                      const uint32_t *d_S, int16_t *d_pos, int16_t *d_neg, int *d_status, cudaStream_t st)
+{
+    if (!conv_tiled_supported(p)) return REXSC_E_UNSUPPORTED;
+    TiledArgs a;
+    a.Hp = p.Hp; a.Wp = p.Wp; a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw;
+    a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.Co = p.Co;
+    a.M = p.M; a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
+    const int tm = pick_tm(p);
+    for (int wd = 0; wd < p.words; wd++) {
+        a.accumulate = wd > 0;
+        const uint32_t *A = d_A + (size_t)wd * p.a_plane_words;
+        const uint32_t *Wt = d_Wt + (size_t)wd * p.w_plane_words;
+        int rc = REXSC_E_UNSUPPORTED;
+        if (tm == 8) {
+            if (p.n_or == 1) rc = launch_one<1, 8>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st);
+            else rc = launch_one<2, 8>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st);
+        } else {
+            switch (p.n_or) {
+            case 1: rc = launch_one<1, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
+            case 2: rc = launch_one<2, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
+            case 3: rc = launch_one<3, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
+            case 4: rc = launch_one<4, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
+            }
+        }
+        if (rc != REXSC_OK) return rc;
+    }
+    return REXSC_OK;
+}
+
+} // namespace rexsc

@@ -1,0 +1,332 @@
+// LFSR/comparator bit-stream generation for the SC conv / linear forward.
+//
+// Design: the stream of an element depends only on (seed index mod (2^l - 1), quantised value), so
+// generation is a table lookup.  One small kernel builds the table of time-packed stream words
+// (bit t of the word = time slot t); the expand kernels quantise the float tensors and look the words
+// up, writing
+//   activations: A[word][c][P]            P = (n*Hp + h)*Wp + w over the zero-padded tensor
+//   weights:     Wt[word][nt][cch][khw][cc][nl]   (one contiguous block per CTA pipeline stage)
+//                S[nt][cch][khw][warp]    sign bits: bit (cc*4 + col) set = negative weight
+// Only one of the reference's positive / negative weight streams is ever non-zero for a given weight
+// (w_pos = ceil(clamp(w*L,0,L-1)), w_neg = ceil(-clamp(w*L,1-L,0)): torch_c/sc-extension/sc_cuda.cpp:92-93),
+// and a zero value gives an all-zero stream, so a single word plus a sign bit carries both.
+#include "common.cuh"
+
+namespace rexsc {
+
+// ---- LFSR step: torch_c/sc-extension/sc_device.cuh:108-248 ----------------------------------
+__host__ __device__ __forceinline__ int lfsr_next(int v, int l, int xnor)
+{
+    int fb;
+    switch (l) {
+    case 1: return 1 - v;
+    case 2: return (v + 1) & 3;
+    case 3: fb = ((v >> 2) ^ (v >> 1)) & 1; break;
+    case 4: fb = ((v >> 3) ^ (v >> 2)) & 1; break;
+    case 5: fb = ((v >> 4) ^ (v >> 2)) & 1; break;
+    case 6: fb = ((v >> 5) ^ (v >> 4)) & 1; break;
+    case 7: fb = ((v >> 6) ^ (v >> 5)) & 1; break;
+    default: fb = ((v >> 7) ^ (v >> 5) ^ (v >> 4) ^ (v >> 3)) & 1; break;
+    }
+    if (xnor) fb ^= 1;
+    return ((v << 1) & ((1 << l) - 1)) | fb;
+}
+
+// One thread per (phase, value): run the generator for bit_length steps.
+// Generation loop semantics: torch_c/sc-extension/sc_cuda_conv.cu:70-92 (weights), :149-163 (activations):
+// advance then compare; progressive-loading mask on the value; int8 storage of state and value; for
+// gen_config g the weight bit t lands in slots t*g..t*g+g-1 and the activation bit t in slots
+// (t/g)*g*g + j*g + t%g.
+__global__ void build_lut_kernel(int l, int bit_length, int g, int xnor, int tw, int lw, int lwait, int is_weight,
+                                 int words, uint32_t *__restrict__ lut)
+{
+    const int nvals = 1 << l;
+    const int period = nvals - 1;
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= period * nvals) return;
+    int phase = idx / nvals;
+    int value = idx - phase * nvals;
+    int state = (int)(int8_t)(phase + 1 - (xnor ? 1 : 0));
+    int val8 = (int)(int8_t)value;
+    uint32_t acc[32]; // words <= 32 (slots <= 1024)
+#pragma unroll 1
+    for (int j = 0; j < words; j++) acc[j] = 0u;
+#pragma unroll 1
+    for (int t = 0; t < bit_length; t++) {
+        int cur = (t / lwait + 1) * lw - 1;
+        if (cur > tw) cur = tw;
+        int sh = tw - cur;
+        int actual = (val8 >> sh) << sh;
+        state = (int)(int8_t)lfsr_next(state, l, xnor);
+        if (actual > state) {
+            for (int j = 0; j < g; j++) {
+                int slot = is_weight ? t * g + j : (t / g) * g * g + j * g + t % g;
+                acc[slot >> 5] |= 1u << (slot & 31);
+            }
+        }
+    }
+    for (int j = 0; j < words; j++) lut[(size_t)idx * words + j] = acc[j];
+}
+
+int launch_build_lut(int l, int bit_length, int gen_config, int xnor, int tw, int lw, int lwait, int is_weight,
+                     uint32_t *d_lut, cudaStream_t st)
+{
+    if (l < 1 || l > 8 || bit_length < 1 || gen_config < 1 || lwait < 1) return REXSC_E_BAD_ARG;
+    int slots = bit_length * gen_config;
+    if (slots > 1024) return REXSC_E_TOO_LONG;
+    int words = (slots + 31) / 32;
+    int total = ((1 << l) - 1) * (1 << l);
+    build_lut_kernel<<<(total + 127) / 128, 128, 0, st>>>(l, bit_length, gen_config, xnor, tw, lw, lwait, is_weight,
+                                                         words, d_lut);
+    REXSC_LAUNCH_CHECK("build_lut_kernel");
+    return REXSC_OK;
+}
+
+// ---- plan ---------------------------------------------------------------------------------
+static int lfsr_length_for(int bit_length)
+{
+    // torch_c/sc-extension/sc_cuda_kernel.cu:594-619 (2 and 4 fall through to 3)
+    switch (bit_length) {
+    case 2: case 4: case 8: return 3;
+    case 16: return 4;
+    case 32: return 5;
+    case 64: return 6;
+    case 128: return 7;
+    case 256: return 8;
+    default: return -1;
+    }
+}
+
+int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p)
+{
+    if (!d || !p) return REXSC_E_BAD_ARG;
+    if (d->batch < 1 || d->c_in < 1 || d->h_in < 1 || d->w_in < 1 || d->c_out < 1 || d->kh < 1 || d->kw < 1)
+        return REXSC_E_BAD_ARG;
+    if (d->pad_h < 0 || d->pad_w < 0 || d->stride_h < 1 || d->stride_w < 1) return REXSC_E_BAD_ARG;
+    if (d->act_dtype < 0 || d->act_dtype > 2 || d->w_dtype < 0 || d->w_dtype > 2) return REXSC_E_BAD_ARG;
+    if (d->bit_length < 1 || d->gen_config < 1 || d->prog_load_wait < 1) return REXSC_E_BAD_ARG;
+    if (d->bin_config < 0) return REXSC_E_UNSUPPORTED; // "exactly n" variants are not on the reference GEMM path
+    int l = d->lfsr_length > 0 ? d->lfsr_length : lfsr_length_for(d->bit_length);
+    // l = 8 is left out: the reference keeps LFSR state and value in int8 storage
+    // (torch_c/sc-extension/sc_cuda_conv.cu:37-40), which wraps negative for 8-bit values and makes a
+    // zero weight produce a non-zero stream; no reference configuration uses it.
+    if (l < 1 || l > 7) return REXSC_E_UNSUPPORTED;
+    p->l = l;
+    p->nvals = 1 << l;
+    p->period = p->nvals - 1;
+    p->slots = d->bit_length * d->gen_config;
+    if (p->slots > 1024) return REXSC_E_TOO_LONG;
+    p->words = (p->slots + 31) / 32;
+    p->n_or = d->bin_config + 1;
+    p->N = d->batch; p->C = d->c_in; p->H = d->h_in; p->W = d->w_in;
+    p->ph = d->pad_h; p->pw = d->pad_w; p->sh = d->stride_h; p->sw = d->stride_w;
+    p->Hp = d->h_in + 2 * d->pad_h;
+    p->Wp = d->w_in + 2 * d->pad_w;
+    p->Co = d->c_out; p->KH = d->kh; p->KW = d->kw; p->KHW = d->kh * d->kw;
+    if (p->Hp < p->KH || p->Wp < p->KW) return REXSC_E_BAD_ARG;
+    p->OH = (p->Hp - p->KH) / p->sh + 1;
+    p->OW = (p->Wp - p->KW) / p->sw + 1;
+    p->NHW = (long long)p->N * p->Hp * p->Wp;
+    p->NHWp = (p->NHW + 3) / 4 * 4;
+    p->M = (long long)p->N * p->OH * p->OW;
+    p->Cpad = (p->C + kChunkC - 1) / kChunkC * kChunkC;
+    p->CCH = p->Cpad / kChunkC;
+    p->NT = (p->Co + kTileN - 1) / kTileN;
+    p->Kdot = (long long)p->C * p->KHW;
+    // the per-slot counters of the generic path are 16 bits wide, like the reference's (sc_device.cuh:380-384)
+    if (p->Kdot > 65535) return REXSC_E_TOO_LONG;
+    if (p->NHWp > 0x7fffffffLL || p->M > 0x7fffffffLL) return REXSC_E_TOO_LONG;
+    p->a_plane_words = (long long)p->Cpad * p->NHWp;
+    p->w_plane_words = (long long)p->NT * p->CCH * p->KHW * kChunkC * kTileN;
+    size_t lut_bytes = (size_t)p->period * p->nvals * p->words * sizeof(uint32_t);
+    size_t off = 0;
+    p->off_status = off; off += 256;
+    p->off_lut_a = off; off += align_up(lut_bytes, 256);
+    p->off_lut_w = off; off += align_up(lut_bytes, 256);
+    p->off_A = off; off += align_up((size_t)p->words * p->a_plane_words * sizeof(uint32_t), 256);
+    p->off_Wt = off; off += align_up((size_t)p->words * p->w_plane_words * sizeof(uint32_t), 256);
+    p->off_S = off; off += align_up((size_t)p->NT * p->CCH * p->KHW * (kTileN / kWarpN) * sizeof(uint32_t), 256);
+    p->total = off;
+    return REXSC_OK;
+}
+
+// ---- activation expansion -------------------------------------------------------------------
+// Seed index of an activation element: c*Hp*Wp + h*Wp + w on the PADDED tensor, offset 0
+// (torch_c/sc-extension/sc_cuda_conv.cu:133,139); linear: c only (sc_cuda_matmul.cu:177).
+struct ExpandActArgs {
+    int N, C, H, W, Hp, Wp, ph, pw, Cpad;
+    long long NHW, NHWp, a_plane_words;
+    int period, nvals, words, linear_seeds;
+    float scale;
+};
+
+template <typename T, bool NHWC>
+__global__ void __launch_bounds__(256) expand_act_kernel(ExpandActArgs a, const T *__restrict__ x,
+                                                         const uint32_t *__restrict__ lut, uint32_t *__restrict__ A)
+{
+    // block: 32 consecutive P x 8 channels (one channel chunk); thread (tx = P lane, ty = channel)
+    __shared__ int q_s[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const long long P0 = (long long)blockIdx.x * 32;
+    const int c0 = blockIdx.y * 8;
+    if (NHWC) {
+        // read with channels fastest: thread (rx = channel 0..7, ry = P 0..31)
+        const int rx = threadIdx.x & 7, ry = threadIdx.x >> 3;
+        long long P = P0 + ry;
+        int c = c0 + rx;
+        int q = 0;
+        if (P < a.NHW && c < a.C) {
+            int w = (int)(P % a.Wp);
+            long long t = P / a.Wp;
+            int h = (int)(t % a.Hp);
+            int n = (int)(t / a.Hp);
+            int hi = h - a.ph, wi = w - a.pw;
+            if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W) {
+                long long xi = (((long long)n * a.H + hi) * a.W + wi) * a.C + c;
+                q = quant_ceil_unipolar(load_as_float<T>(x, xi), a.scale);
+            }
+        }
+        q_s[rx][ry] = q;
+        __syncthreads();
+    }
+    long long P = P0 + tx;
+    int c = c0 + ty;
+    if (P >= a.NHWp) return;
+    bool live = (P < a.NHW && c < a.C);
+    int w = 0, h = 0;
+    int q = 0;
+    if (live) {
+        w = (int)(P % a.Wp);
+        long long t = P / a.Wp;
+        h = (int)(t % a.Hp);
+        if (NHWC) {
+            q = q_s[ty][tx];
+        } else {
+            int n = (int)(t / a.Hp);
+            int hi = h - a.ph, wi = w - a.pw;
+            if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W) {
+                long long xi = (((long long)n * a.C + c) * a.H + hi) * a.W + wi;
+                q = quant_ceil_unipolar(load_as_float<T>(x, xi), a.scale);
+            }
+        }
+    }
+    long long seed_ind = a.linear_seeds ? (long long)c : ((long long)c * a.Hp + h) * a.Wp + w;
+    int phase = (int)(seed_ind % a.period);
+    const uint32_t *row = lut + ((size_t)phase * a.nvals + q) * a.words;
+    for (int j = 0; j < a.words; j++) {
+        uint32_t v = (live && q > 0) ? __ldg(row + j) : 0u;
+        A[(size_t)j * a.a_plane_words + (size_t)c * a.NHWp + P] = v;
+    }
+}
+
+template <typename T>
+static int expand_act_dispatch(const ExpandActArgs &a, bool nhwc, const void *x, const uint32_t *lut, uint32_t *A,
+                               cudaStream_t st)
+{
+    dim3 grid((unsigned)((a.NHWp + 31) / 32), (unsigned)(a.Cpad / 8));
+    if (grid.y > 65535) return REXSC_E_TOO_LONG;
+    if (nhwc)
+        expand_act_kernel<T, true><<<grid, 256, 0, st>>>(a, (const T *)x, lut, A);
+    else
+        expand_act_kernel<T, false><<<grid, 256, 0, st>>>(a, (const T *)x, lut, A);
+    REXSC_LAUNCH_CHECK("expand_act_kernel");
+    return REXSC_OK;
+}
+
+int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const uint32_t *d_lut,
+                      uint32_t *d_A, cudaStream_t st)
+{
+    ExpandActArgs a;
+    a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
+    a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
+    a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
+    a.scale = (float)p.nvals;
+    bool nhwc = d.act_channels_last != 0;
+    switch (d.act_dtype) {
+    case REXSC_F32: return expand_act_dispatch<float>(a, nhwc, d_act, d_lut, d_A, st);
+    case REXSC_F16: return expand_act_dispatch<__half>(a, nhwc, d_act, d_lut, d_A, st);
+    case REXSC_BF16: return expand_act_dispatch<__nv_bfloat16>(a, nhwc, d_act, d_lut, d_A, st);
+    }
+    return REXSC_E_BAD_ARG;
+}
+
+// ---- weight expansion -----------------------------------------------------------------------
+// Seed index of a weight element: c*KH*KW + kh*KW + kw, offset 13 for both signs
+// (torch_c/sc-extension/sc_cuda_conv.cu:45,55-56; sc_device.cuh:33-34); linear: c only.
+struct ExpandWArgs {
+    int C, Co, KH, KW, KHW, CCH, NT;
+    int period, nvals, words, linear_seeds, ohwi;
+    long long w_plane_words;
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) expand_weight_kernel(ExpandWArgs a, const T *__restrict__ wt,
+                                                            const uint32_t *__restrict__ lut,
+                                                            uint32_t *__restrict__ Wt, uint32_t *__restrict__ S)
+{
+    // one warp per (nt, cch, khw, warp8); lane = cc*4 + col
+    long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    long long total_warps = (long long)a.NT * a.CCH * a.KHW * 8;
+    if (gw >= total_warps) return;
+    int w8 = (int)(gw & 7);
+    long long t = gw >> 3;
+    int khw = (int)(t % a.KHW);
+    t /= a.KHW;
+    int cch = (int)(t % a.CCH);
+    int nt = (int)(t / a.CCH);
+    int cc = lane >> 2, col = lane & 3;
+    int ci = cch * kChunkC + cc;
+    int nl = w8 * kWarpN + col;
+    int co = nt * kTileN + nl;
+    int kh = khw / a.KW, kw = khw - kh * a.KW;
+    int mag = 0;
+    bool neg = false;
+    if (ci < a.C && co < a.Co) {
+        long long wi = a.ohwi ? (((long long)co * a.KH + kh) * a.KW + kw) * a.C + ci
+                              : (((long long)co * a.C + ci) * a.KH + kh) * a.KW + kw;
+        float v = load_as_float<T>(wt, wi) * a.scale;
+        // w_pos = ceil(clamp(v, 0, L-1)); w_neg = ceil(-clamp(v, 1-L, 0))  (sc_cuda.cpp:92-93)
+        int qp = (int)ceilf(fminf(fmaxf(v, 0.f), a.scale - 1.f));
+        int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - a.scale), 0.f));
+        if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
+    }
+    long long seed_ind = a.linear_seeds ? (long long)ci : ((long long)ci * a.KH + kh) * a.KW + kw;
+    int phase = (int)((13 + seed_ind) % a.period);
+    const uint32_t *row = lut + ((size_t)phase * a.nvals + mag) * a.words;
+    size_t base = ((((size_t)nt * a.CCH + cch) * a.KHW + khw) * kChunkC + cc) * kTileN + nl;
+    for (int j = 0; j < a.words; j++) {
+        uint32_t v = mag > 0 ? __ldg(row + j) : 0u;
+        Wt[(size_t)j * a.w_plane_words + base] = v;
+    }
+    unsigned mask = __ballot_sync(0xffffffffu, neg);
+    if (lane == 0) S[gw] = mask;
+}
+
+int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_w, const uint32_t *d_lut,
+                         uint32_t *d_Wt, uint32_t *d_S, cudaStream_t st)
+{
+    ExpandWArgs a;
+    a.C = p.C; a.Co = p.Co; a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.NT = p.NT;
+    a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
+    a.ohwi = d.w_channels_last; a.w_plane_words = p.w_plane_words; a.scale = (float)p.nvals;
+    long long total_threads = (long long)p.NT * p.CCH * p.KHW * 8 * 32;
+    unsigned blocks = (unsigned)((total_threads + 255) / 256);
+    switch (d.w_dtype) {
+    case REXSC_F32:
+        expand_weight_kernel<float><<<blocks, 256, 0, st>>>(a, (const float *)d_w, d_lut, d_Wt, d_S);
+        break;
+    case REXSC_F16:
+        expand_weight_kernel<__half><<<blocks, 256, 0, st>>>(a, (const __half *)d_w, d_lut, d_Wt, d_S);
+        break;
+    case REXSC_BF16:
+        expand_weight_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(a, (const __nv_bfloat16 *)d_w, d_lut, d_Wt, d_S);
+        break;
+    default: return REXSC_E_BAD_ARG;
+    }
+    REXSC_LAUNCH_CHECK("expand_weight_kernel");
+    return REXSC_OK;
+}
+
+} // namespace rexsc

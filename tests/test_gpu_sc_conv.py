@@ -1,0 +1,229 @@
+"""GPU parity of the SC conv2d / linear forward (through the C-ABI) against the CPU oracle and against the
+golden vectors produced by the reference's own CPU extension.  Bit-exact: integer work."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import conv_inputs, from128, golden_cases, load_golden
+
+pytestmark = pytest.mark.gpu
+
+PROG = (7, 8, 1)
+
+
+def run_ours(ops, x, w, L, pad, stride, or_n, xnor, kernel="auto", gen=1, prog=PROG, lfsr=-1, dtype=None):
+    ops.set_conv_kernel(kernel)
+    try:
+        xd, wd = x.cuda(), w.cuda()
+        if dtype is not None:
+            xd, wd = xd.to(dtype), wd.to(dtype)
+        if x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous():
+            xd = xd.contiguous(memory_format=torch.channels_last)
+        if w.is_contiguous(memory_format=torch.channels_last) and not w.is_contiguous():
+            wd = wd.contiguous(memory_format=torch.channels_last)
+        p, n = ops.conv2d_generic_general_split_acc(xd, wd, L, lfsr, 16, (pad, pad), (stride, stride), prog,
+                                                    or_n - 1, gen, xnor, False)
+        assert ops.workspace_status() == 0
+        return p, n
+    finally:
+        ops.set_conv_kernel("auto")
+
+
+def assert_same(ours, ref, what):
+    p, n = ours
+    rp, rn = ref
+    assert p.dtype == torch.int16 and n.dtype == torch.int16
+    assert p.shape == rp.shape
+    assert p.stride() == rp.stride(), f"{what}: memory format differs"
+    assert torch.equal(p.cpu(), rp), f"{what}: pos differs ({(p.cpu() != rp).sum().item()} elements)"
+    assert torch.equal(n.cpu(), rn), f"{what}: neg differs ({(n.cpu() != rn).sum().item()} elements)"
+
+
+@pytest.mark.parametrize("kernel", ["direct", "tiled"])
+def test_golden_reference_cpu_vectors(ops, kernel):
+    """xnor=False: pos - neg must equal what the reference's CPU extension returned."""
+    g = load_golden("sc_conv_ref_cpu.npz")
+    for name in golden_cases(g):
+        N, Cin, H, W, Cout, K, pad, stride, L, or_n, cl = (int(v) for v in g[name + "/args"])
+        if kernel == "tiled" and or_n > 4:
+            continue
+        x, w = from128(g[name + "/x128"]), from128(g[name + "/w128"])
+        if cl:
+            x = x.contiguous(memory_format=torch.channels_last)
+            w = w.contiguous(memory_format=torch.channels_last)
+        p, n = run_ours(ops, x, w, L, pad, stride, or_n, False, kernel)
+        y = (p - n).contiguous().cpu().numpy()
+        assert int(y.astype(np.int64).sum()) == int(g[name + "/sum"][0]), name
+        if name + "/y" in g.files:
+            assert np.array_equal(y, g[name + "/y"]), name
+        else:
+            assert np.array_equal(y.reshape(-1)[:4096], g[name + "/y_head"]), name
+
+
+CASES = [
+    # N, Cin, H, W, Cout, K, pad, stride, L, or_n, channels_last
+    (2, 3, 12, 12, 8, 5, 2, 1, 32, 1, False),
+    (2, 32, 10, 10, 16, 3, 1, 1, 32, 2, True),
+    (3, 64, 9, 9, 70, 3, 1, 1, 32, 2, True),      # Cout not a multiple of 32
+    (2, 70, 9, 9, 40, 3, 1, 2, 32, 2, False),     # stride 2, Cin not a multiple of 8
+    (3, 64, 8, 8, 24, 1, 0, 2, 64, 3, True),      # 1x1 stride 2, two word planes
+    (2, 16, 4, 4, 10, 4, 0, 1, 128, 1, False),    # 4x4 -> 1x1 output, four word planes
+    (1, 5, 12, 7, 7, 5, 2, 1, 32, 4, False),      # non-square, OR-4
+    (5, 24, 7, 7, 33, 3, 1, 1, 32, 3, True),      # tile spans several images
+    (2, 8, 6, 6, 5, 3, 1, 1, 16, 1, False),       # L < 32
+    (1, 130, 5, 5, 4, 3, 1, 1, 32, 2, False),     # many channel chunks, tiny tile
+    (2, 16, 20, 20, 12, 7, 3, 2, 32, 2, True),    # 7x7 stride 2
+]
+
+
+@pytest.mark.parametrize("xnor", [False, True])
+@pytest.mark.parametrize("kernel", ["direct", "tiled"])
+@pytest.mark.parametrize("case", CASES)
+def test_parity_vs_oracle(ops, oracle, case, kernel, xnor):
+    N, Cin, H, W, Cout, K, pad, stride, L, or_n, cl = case
+    x, w = conv_inputs(N, Cin, H, W, Cout, K, prec=7, seed=hash(case) % 1000)
+    if cl:
+        x = x.contiguous(memory_format=torch.channels_last)
+        w = w.contiguous(memory_format=torch.channels_last)
+    ref = oracle.conv2d_generic_general_split(x, w, L, -1, 16, (pad, pad), (stride, stride), PROG, or_n - 1, 1,
+                                              xnor, False)
+    ours = run_ours(ops, x, w, L, pad, stride, or_n, xnor, kernel)
+    assert_same(ours, ref, f"{case} {kernel} xnor={xnor}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_half_precision_inputs(ops, oracle, dtype):
+    x, w = conv_inputs(2, 16, 9, 9, 12, 3, prec=5, seed=11)
+    xq, wq = x.to(dtype).float(), w.to(dtype).float()
+    ref = oracle.conv2d_generic_general_split(xq, wq, 32, -1, 16, (1, 1), (1, 1), PROG, 1, 1, True, False)
+    ours = run_ours(ops, x, w, 32, 1, 1, 2, True, "auto", dtype=dtype)
+    assert_same(ours, ref, str(dtype))
+
+
+def test_mixed_layouts(ops, oracle):
+    """channels_last activation with OIHW weight and the reverse: layout only changes addressing."""
+    x, w = conv_inputs(2, 16, 8, 8, 8, 3, seed=5)
+    ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (1, 1), (1, 1), PROG, 1, 1, True, False)
+    xc = x.contiguous(memory_format=torch.channels_last)
+    wc = w.contiguous(memory_format=torch.channels_last)
+    p, n = run_ours(ops, xc, w, 32, 1, 1, 2, True)
+    assert torch.equal(p.cpu().contiguous(), ref[0]) and torch.equal(n.cpu().contiguous(), ref[1])
+    assert p.is_contiguous(memory_format=torch.channels_last)
+    p, n = run_ours(ops, x, wc, 32, 1, 1, 2, True)
+    assert torch.equal(p.cpu(), ref[0]) and torch.equal(n.cpu(), ref[1])
+    assert p.is_contiguous()
+
+
+def test_combined_output_op(ops, oracle):
+    x, w = conv_inputs(2, 8, 8, 8, 8, 3, seed=6)
+    ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (1, 1), (1, 1), PROG, 0, 1, True, False)
+    y = ops.conv2d_generic_general_acc(x.cuda(), w.cuda(), 32, -1, 16, (1, 1), (1, 1), PROG, 0, 1, True, False)
+    assert y.dtype == torch.int16 and torch.equal(y.cpu(), ref[0] - ref[1])
+
+
+@pytest.mark.parametrize("or_n", [7, 51201])
+def test_large_n_and_plain_count(ops, oracle, or_n):
+    x, w = conv_inputs(1, 40, 6, 6, 9, 3, prec=5, seed=7)
+    ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (1, 1), (1, 1), PROG, or_n - 1, 1, True, False)
+    ours = run_ours(ops, x, w, 32, 1, 1, or_n, True)
+    assert_same(ours, ref, f"or_n={or_n}")
+
+
+def test_generator_options(ops, oracle):
+    """AND-2 generator replication, progressive loading and an explicit lfsr_length."""
+    x, w = conv_inputs(2, 12, 7, 7, 6, 3, seed=8)
+    for gen, prog, lfsr, L in [(2, PROG, -1, 32), (1, (7, 2, 4), -1, 32), (1, PROG, 7, 32), (3, (7, 3, 2), -1, 16)]:
+        for xnor in (False, True):
+            ref = oracle.conv2d_generic_general_split(x, w, L, lfsr, 16, (1, 1), (1, 1), prog, 1, gen, xnor, False)
+            for kernel in ("direct", "tiled"):
+                ours = run_ours(ops, x, w, L, 1, 1, 2, xnor, kernel, gen=gen, prog=prog, lfsr=lfsr)
+                assert_same(ours, ref, f"gen={gen} prog={prog} lfsr={lfsr} {kernel} xnor={xnor}")
+
+
+def test_asymmetric_padding_and_stride(ops, oracle):
+    x, w = conv_inputs(2, 8, 9, 11, 6, 3, seed=9)
+    ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (2, 1), (2, 1), PROG, 1, 1, True, False)
+    p, n = ops.conv2d_generic_general_split_acc(x.cuda(), w.cuda(), 32, -1, 16, (2, 1), (2, 1), PROG, 1, 1, True,
+                                                False)
+    assert torch.equal(p.cpu(), ref[0]) and torch.equal(n.cpu(), ref[1])
+
+
+def test_edge_values(ops, oracle):
+    """0, 1-eps, 1, >1 and negative activations; weights at +-1 and 0 (quantiser clamps, zero streams)."""
+    x = torch.tensor([0.0, 1 / 128, 0.5, 1 - 1 / 128, 1.0, 1.5, -0.25, 31 / 32]).repeat(8 * 8 * 2)[:8 * 8 * 8]
+    x = x.reshape(1, 8, 8, 8).contiguous()
+    w = torch.tensor([0.0, 1.0, -1.0, 1 / 128, -1 / 128, 0.5, -0.5, 0.999]).repeat(4 * 8 * 9)[:4 * 8 * 9]
+    w = w.reshape(4, 8, 3, 3).contiguous()
+    for xnor in (False, True):
+        ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (1, 1), (1, 1), PROG, 1, 1, xnor, False)
+        assert_same(run_ours(ops, x, w, 32, 1, 1, 2, xnor), ref, f"edge xnor={xnor}")
+
+
+def test_linear_golden_and_oracle(ops, oracle):
+    g = load_golden("sc_linear_ref_cpu.npz")
+    for name in golden_cases(g):
+        B, Cin, Cout, L, or_n = (int(v) for v in g[name + "/args"])
+        x, w = from128(g[name + "/x128"]), from128(g[name + "/w128"])
+        p, n = ops.linear_generic_general_acc(x.cuda(), w.cuda(), PROG, L, -1, or_n - 1, 1, True, False)
+        assert np.array_equal(p.cpu().numpy(), g[name + "/pos"]), name
+        assert np.array_equal(n.cpu().numpy(), g[name + "/neg"]), name
+    # ragged sizes only the oracle covers
+    gen = torch.Generator().manual_seed(3)
+    x = torch.rand(37, 45, generator=gen)
+    w = (torch.randn(19, 45, generator=gen) * 0.2).clamp(-1, 1)
+    rp, rn = oracle.linear_generic_general(x, w, PROG, 64, -1, 2, 1, True, False)
+    p, n = ops.linear_generic_general_acc(x.cuda(), w.cuda(), PROG, 64, -1, 2, 1, True, False)
+    assert torch.equal(p.cpu(), rp) and torch.equal(n.cpu(), rn)
+
+
+def test_lut_matches_oracle_streams(ops, oracle):
+    for l, L, xnor in [(5, 32, True), (5, 32, False), (6, 64, True), (7, 128, False), (3, 8, True)]:
+        lut = ops.build_lfsr_lut(l, L, 1, xnor).cpu().numpy().astype(np.uint32)
+        period = (1 << l) - 1
+        for phase in (0, 1, period // 2, period - 1):
+            for value in (0, 1, (1 << l) // 2, (1 << l) - 1):
+                bits = oracle.stream_bits(value, phase + 1 - int(xnor), l, xnor, L)
+                words = np.zeros(lut.shape[2], dtype=np.uint32)
+                for t, b in enumerate(bits):
+                    if b:
+                        words[t // 32] |= np.uint32(1 << (t % 32))
+                assert np.array_equal(lut[phase, value], words), (l, L, xnor, phase, value)
+
+
+def test_rejects_bad_arguments(ops):
+    x = torch.rand(1, 4, 6, 6).cuda()
+    w = torch.rand(4, 4, 3, 3).cuda()
+    with pytest.raises(ValueError):
+        ops.conv2d_generic_general_split_acc(x, w, 48, -1, 16, (0, 0), (1, 1), PROG, 0, 1, True, False)  # L not 2^k
+    with pytest.raises(ValueError):
+        ops.conv2d_generic_general_split_acc(x, w, 32, -1, 16, (0, 0), (1, 1), PROG, -2, 1, True, False)
+    with pytest.raises(RuntimeError):
+        ops.conv2d_generic_general_split_acc(x.cpu(), w.cpu(), 32, -1, 16, (0, 0), (1, 1), PROG, 0, 1, True, False)
+
+
+def test_full_size_properties(ops):
+    """ResNet-18 layer-1 shape at batch 32 (too large for the oracle): direct == tiled, determinism, bounds,
+    zero weights give zero, and a batch permutation permutes the output (samples are independent)."""
+    g = torch.Generator().manual_seed(1)
+    x = torch.rand(32, 64, 56, 56, generator=g).cuda().contiguous(memory_format=torch.channels_last)
+    w = (torch.randn(64, 64, 3, 3, generator=g) * 0.05).clamp(-1, 1).cuda().contiguous(
+        memory_format=torch.channels_last)
+    args = (32, -1, 16, (1, 1), (1, 1), PROG, 1, 1, True, False)
+    ops.set_conv_kernel("tiled")
+    p1, n1 = ops.conv2d_generic_general_split_acc(x, w, *args)
+    p2, n2 = ops.conv2d_generic_general_split_acc(x, w, *args)
+    ops.set_conv_kernel("direct")
+    p3, n3 = ops.conv2d_generic_general_split_acc(x, w, *args)
+    ops.set_conv_kernel("auto")
+    assert ops.workspace_status() == 0
+    assert torch.equal(p1, p2) and torch.equal(n1, n2)
+    assert torch.equal(p1, p3) and torch.equal(n1, n3)
+    assert int(p1.min()) >= 0 and int(p1.max()) <= 64 and int(n1.min()) >= 0 and int(n1.max()) <= 64
+    pz, nz = ops.conv2d_generic_general_split_acc(x, torch.zeros_like(w), *args)
+    assert int(pz.abs().max()) == 0 and int(nz.abs().max()) == 0
+    perm = torch.randperm(32, generator=g).cuda()
+    pp, _ = ops.conv2d_generic_general_split_acc(x[perm].contiguous(memory_format=torch.channels_last), w, *args)
+    assert torch.equal(pp, p1[perm])
+    # negating the weights swaps the two outputs
+    ps, ns = ops.conv2d_generic_general_split_acc(x, -w, *args)
+    assert torch.equal(ps, n1) and torch.equal(ns, p1)
