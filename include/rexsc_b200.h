@@ -80,9 +80,28 @@ const char *rexsc_last_cuda_error(void);
  *             either may alias nothing else; both are fully overwritten
  */
 size_t rexsc_sc_conv2d_workspace_size(const rexsc_sc_conv_desc *desc);
+/* Which kernel a forward call with this descriptor runs: REXSC_KERNEL_DIRECT or REXSC_KERNEL_TILED, or a
+ * negative REXSC_E_* code (REXSC_E_UNSUPPORTED when desc->kernel forces the tiled kernel on a shape whose
+ * activation patch does not fit its shared-memory stage).  Host-only, launches nothing. */
+int rexsc_sc_conv2d_kernel_choice(const rexsc_sc_conv_desc *desc);
 int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                         int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes,
                         void *stream);
+
+/*
+ * The two stages of rexsc_sc_conv2d_fwd as separate calls (same descriptor, same workspace):
+ *   expand      pad + quantise + stream generation of activations and weights into the workspace
+ *               (replaces the reference's K1/K2 generators, sc_cuda_conv.cu:3-166, and the libtorch
+ *               quantisation passes of sc_cuda.cpp:88-94);
+ *   accumulate  OR-n accumulation of the stream words into the int16 outputs (replaces im2col + GEMM +
+ *               scatter, sc_cuda_kernel.cu:367-562 and sc_device.cu:186-386).
+ * fwd == expand followed by accumulate on the same stream.  Splitting lets a caller time the stages or keep
+ * expanded streams across calls while the tensors they came from are unchanged.
+ */
+int rexsc_sc_conv2d_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
+                           void *d_workspace, size_t workspace_bytes, void *stream);
+int rexsc_sc_conv2d_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, int16_t *d_out_neg,
+                               void *d_workspace, size_t workspace_bytes, void *stream);
 
 /*
  * SC linear forward.  Replaces linear_generic_general_acc (torch_c/sc-extension/sc_cuda.cpp:101-120)

@@ -39,7 +39,10 @@ SYMBOLS = {
     "rexsc_abi_version": (C.c_int, []),
     "rexsc_last_cuda_error": (C.c_char_p, []),
     "rexsc_sc_conv2d_workspace_size": (_sz, [C.POINTER(ScConvDesc)]),
+    "rexsc_sc_conv2d_kernel_choice": (C.c_int, [C.POINTER(ScConvDesc)]),
     "rexsc_sc_conv2d_fwd": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "rexsc_sc_conv2d_expand": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
+    "rexsc_sc_conv2d_accumulate": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_linear_workspace_size": (_sz, [_i32] * 6),
     "rexsc_sc_linear_fwd": (C.c_int, [_i32] * 12 + [_vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rexsc_workspace_status": (C.c_int, [_vp, _vp]),

@@ -13,43 +13,79 @@ void set_cuda_error(cudaError_t e, const char *where)
     snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
 }
 
-static int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
-                        int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st)
+struct ConvBuffers {
+    int *status;
+    uint32_t *lut_a, *lut_w, *A, *Wt, *S;
+};
+
+static int conv_buffers(const rexsc_sc_conv_desc *desc, void *d_workspace, size_t workspace_bytes, ConvPlan *p,
+                        ConvBuffers *b)
 {
-    ConvPlan p;
-    int rc = make_conv_plan(desc, &p);
+    int rc = make_conv_plan(desc, p);
     if (rc != REXSC_OK) return rc;
-    if (!d_act || !d_weight || !d_out_pos || !d_out_neg) return REXSC_E_BAD_ARG;
     if (desc->kernel < REXSC_KERNEL_AUTO || desc->kernel > REXSC_KERNEL_TILED) return REXSC_E_BAD_ARG;
-    if (!d_workspace || workspace_bytes < p.total || (reinterpret_cast<uintptr_t>(d_workspace) & 255))
+    if (!d_workspace || workspace_bytes < p->total || (reinterpret_cast<uintptr_t>(d_workspace) & 255))
         return REXSC_E_WORKSPACE;
     uint8_t *ws = static_cast<uint8_t *>(d_workspace);
-    int *status = reinterpret_cast<int *>(ws + p.off_status);
-    uint32_t *lut_a = reinterpret_cast<uint32_t *>(ws + p.off_lut_a);
-    uint32_t *lut_w = reinterpret_cast<uint32_t *>(ws + p.off_lut_w);
-    uint32_t *A = reinterpret_cast<uint32_t *>(ws + p.off_A);
-    uint32_t *Wt = reinterpret_cast<uint32_t *>(ws + p.off_Wt);
-    uint32_t *S = reinterpret_cast<uint32_t *>(ws + p.off_S);
+    b->status = reinterpret_cast<int *>(ws + p->off_status);
+    b->lut_a = reinterpret_cast<uint32_t *>(ws + p->off_lut_a);
+    b->lut_w = reinterpret_cast<uint32_t *>(ws + p->off_lut_w);
+    b->A = reinterpret_cast<uint32_t *>(ws + p->off_A);
+    b->Wt = reinterpret_cast<uint32_t *>(ws + p->off_Wt);
+    b->S = reinterpret_cast<uint32_t *>(ws + p->off_S);
+    return REXSC_OK;
+}
 
-    REXSC_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, st));
+// stage 1: stream generation (LUTs, activation words, weight words + signs) into the workspace
+static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, void *d_workspace,
+                       size_t workspace_bytes, cudaStream_t st)
+{
+    ConvPlan p;
+    ConvBuffers b;
+    int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
+    if (rc != REXSC_OK) return rc;
+    if (!d_act || !d_weight) return REXSC_E_BAD_ARG;
+    REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
     // The linear generators always use the XOR LFSR (torch_c/sc-extension/sc_cuda_matmul.cu:27-57).
     const int xnor = desc->linear_seeds ? 0 : (desc->xnor ? 1 : 0);
     rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
-                          desc->prog_load_width, desc->prog_load_wait, 0, lut_a, st);
+                          desc->prog_load_width, desc->prog_load_wait, 0, b.lut_a, st);
     if (rc != REXSC_OK) return rc;
     rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
-                          desc->prog_load_width, desc->prog_load_wait, 1, lut_w, st);
+                          desc->prog_load_width, desc->prog_load_wait, 1, b.lut_w, st);
     if (rc != REXSC_OK) return rc;
-    rc = launch_expand_act(p, *desc, d_act, lut_a, A, st);
+    rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
     if (rc != REXSC_OK) return rc;
-    rc = launch_expand_weight(p, *desc, d_weight, lut_w, Wt, S, st);
-    if (rc != REXSC_OK) return rc;
+    return launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
+}
 
+// stage 2: OR-n accumulation over the stream words of the workspace
+static int conv_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, int16_t *d_out_neg,
+                           void *d_workspace, size_t workspace_bytes, cudaStream_t st)
+{
+    ConvPlan p;
+    ConvBuffers b;
+    int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
+    if (rc != REXSC_OK) return rc;
+    if (!d_out_pos || !d_out_neg) return REXSC_E_BAD_ARG;
     const bool tiled_ok = conv_tiled_supported(p);
     if (desc->kernel == REXSC_KERNEL_TILED && !tiled_ok) return REXSC_E_UNSUPPORTED;
     if (desc->kernel != REXSC_KERNEL_DIRECT && tiled_ok)
-        return launch_conv_tiled(p, *desc, A, Wt, S, d_out_pos, d_out_neg, status, st);
-    return launch_conv_direct(p, *desc, A, Wt, S, d_out_pos, d_out_neg, st);
+        return launch_conv_tiled(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, b.status, st);
+    return launch_conv_direct(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, st);
+}
+
+static int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
+                        int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st)
+{
+    if (!d_act || !d_weight || !d_out_pos || !d_out_neg) {
+        ConvPlan p;
+        int rc = make_conv_plan(desc, &p);
+        return rc != REXSC_OK ? rc : REXSC_E_BAD_ARG;
+    }
+    int rc = conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, st);
+    if (rc != REXSC_OK) return rc;
+    return conv_accumulate(desc, d_out_pos, d_out_neg, d_workspace, workspace_bytes, st);
 }
 
 static void linear_desc(rexsc_sc_conv_desc *d, int32_t batch, int32_t c_in, int32_t c_out, int32_t act_dtype,
@@ -83,12 +119,34 @@ extern "C" size_t rexsc_sc_conv2d_workspace_size(const rexsc_sc_conv_desc *desc)
     return p.total;
 }
 
+extern "C" int rexsc_sc_conv2d_kernel_choice(const rexsc_sc_conv_desc *desc)
+{
+    ConvPlan p;
+    int rc = make_conv_plan(desc, &p);
+    if (rc != REXSC_OK) return rc;
+    const bool tiled_ok = conv_tiled_supported(p);
+    if (desc->kernel == REXSC_KERNEL_TILED && !tiled_ok) return REXSC_E_UNSUPPORTED;
+    return (desc->kernel != REXSC_KERNEL_DIRECT && tiled_ok) ? REXSC_KERNEL_TILED : REXSC_KERNEL_DIRECT;
+}
+
 extern "C" int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                                    int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace,
                                    size_t workspace_bytes, void *stream)
 {
     return conv_forward(desc, d_act, d_weight, d_out_pos, d_out_neg, d_workspace, workspace_bytes,
                         (cudaStream_t)stream);
+}
+
+extern "C" int rexsc_sc_conv2d_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
+                                      void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    return conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int rexsc_sc_conv2d_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, int16_t *d_out_neg,
+                                          void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    return conv_accumulate(desc, d_out_pos, d_out_neg, d_workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 extern "C" size_t rexsc_sc_linear_workspace_size(int32_t batch, int32_t c_in, int32_t c_out, int32_t bit_length,
@@ -143,7 +201,8 @@ __global__ void __launch_bounds__(256) alu_probe_kernel(int iters, uint32_t *sin
 #pragma unroll
         for (int rep = 0; rep < 4; rep++) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) r[i] = (r[i] & a) ^ r[(i + 1) & 15];
+            for (int i = 0; i < 16; i++)
+                asm volatile("lop3.b32 %0, %0, %1, %2, 0x6a;" : "+r"(r[i]) : "r"(a), "r"(r[(i + 1) & 15]));
         }
         a += 0x01010101u;
     }

@@ -1,8 +1,8 @@
 // Tiled SC conv forward for sm_100a: implicit GEMM over time-packed stream words on the integer ALU.
 //
 //   M = N*OH*OW output pixels, N = Cout, K = Cin*KH*KW; one 32-bit word per (element, 32 time slots).
-//   CTA tile  = (32*TM) pixels x 32 output channels, 256 threads = 8 warps.
-//   Warp w owns output channels 4w..4w+3 for ALL rows of the tile; lane owns rows lane + 32*j, j < TM.
+//   CTA tile  = (32*TM) pixels x 32 output channels, NW warps (8 or 16).
+//   Warp w owns TN = 32/NW output channels for ALL rows of the tile; lane owns rows lane + 32*j, j < TM.
 //   Because every lane of a warp works on the same output channels at the same k, the sign of the weight
 //   (which of the reference's two weight streams is non-zero) is warp-uniform: the kernel branches on it
 //   and updates only the positive or only the negative accumulators, halving the LOP3 count.
@@ -23,7 +23,6 @@ namespace rexsc {
 
 namespace {
 
-constexpr int kThreads = 256;
 constexpr int kStages = 2;
 constexpr uint32_t kWaitLimit = 1u << 22; // bounded mbarrier polling (each poll may itself block briefly)
 
@@ -77,13 +76,15 @@ template <int NOR> __device__ __forceinline__ void thermo_update(uint32_t (&t)[N
     t[0] |= x;
 }
 
-template <int NOR, int TM>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int NOR, int TM, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t *__restrict__ Wt,
                      const uint32_t *__restrict__ S, int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg,
                      int *__restrict__ status)
 {
     constexpr int BM = 32 * TM;
+    constexpr int TN = kTileN / NW; // output channels per warp: 4 (8 warps) or 2 (16 warps)
+    static_assert(TN == 2 || TN == 4, "warp tile is 2 or 4 output channels");
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t a_stage_bytes = kChunkC * kPlaneWords * 4;
     const uint32_t b_stage_bytes = (uint32_t)a.KHW * kChunkC * kTileN * 4;
@@ -149,11 +150,11 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         if (a.CCH > 1) { issue(1); issued = 2; }
     }
 
-    uint32_t tp[TM][kWarpN][NOR], tn[TM][kWarpN][NOR];
+    uint32_t tp[TM][TN][NOR], tn[TM][TN][NOR];
 #pragma unroll
     for (int j = 0; j < TM; j++)
 #pragma unroll
-        for (int c = 0; c < kWarpN; c++)
+        for (int c = 0; c < TN; c++)
 #pragma unroll
             for (int q = 0; q < NOR; q++) { tp[j][c][q] = 0u; tn[j][c][q] = 0u; }
 
@@ -167,13 +168,14 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         if (failed) break;
 
         const uint32_t *As = reinterpret_cast<const uint32_t *>(a_base + s * a_stage_bytes);
-        const uint32_t *Bs = reinterpret_cast<const uint32_t *>(b_base + s * b_stage_bytes) + warp * kWarpN;
-        const uint32_t *Ss = reinterpret_cast<const uint32_t *>(s_base + s * s_stage_bytes) + warp;
+        const uint32_t *Bs = reinterpret_cast<const uint32_t *>(b_base + s * b_stage_bytes) + warp * TN;
+        const uint32_t *Ss = reinterpret_cast<const uint32_t *>(s_base + s * s_stage_bytes) + (warp * TN) / kWarpN;
+        const int sign_base = (warp * TN) % kWarpN; // first channel of this warp inside its 4-channel sign group
 
         int kw = 0, koff = 0, krow = 0;
 #pragma unroll 1
         for (int khw = 0; khw < a.KHW; khw++) {
-            const uint32_t sg = Ss[khw * (kTileN / kWarpN)];
+            const uint32_t sgw = Ss[khw * (kTileN / kWarpN)] >> sign_base;
             const uint32_t *ap[TM];
 #pragma unroll
             for (int j = 0; j < TM; j++) ap[j] = As + off[j] + koff;
@@ -183,11 +185,17 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
                 uint32_t av[TM];
 #pragma unroll
                 for (int j = 0; j < TM; j++) av[j] = ap[j][cc * kPlaneWords];
-                const uint4 w4 = *reinterpret_cast<const uint4 *>(bp + cc * kTileN);
-                const uint32_t wv[kWarpN] = {w4.x, w4.y, w4.z, w4.w};
+                uint32_t wv[TN];
+                if (TN == 4) {
+                    const uint4 w4 = *reinterpret_cast<const uint4 *>(bp + cc * kTileN);
+                    wv[0] = w4.x; wv[1] = w4.y; wv[TN - 2] = w4.z; wv[TN - 1] = w4.w;
+                } else {
+                    const uint2 w2 = *reinterpret_cast<const uint2 *>(bp + cc * kTileN);
+                    wv[0] = w2.x; wv[1] = w2.y;
+                }
 #pragma unroll
-                for (int c = 0; c < kWarpN; c++) {
-                    if (sg & (1u << (cc * kWarpN + c))) {
+                for (int c = 0; c < TN; c++) {
+                    if (sgw & (1u << (cc * kWarpN + c))) {
 #pragma unroll
                         for (int j = 0; j < TM; j++) thermo_update<NOR>(tn[j][c], av[j], wv[c]);
                     } else {
@@ -215,41 +223,48 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
     }
 
     // ---- epilogue: popcount the thermometers, store int16 in the requested layout -----------------
-    const int co0 = nt * kTileN + warp * kWarpN;
+    const int co0 = nt * kTileN + warp * TN;
     const size_t ohw = (size_t)a.OH * a.OW;
 #pragma unroll
     for (int j = 0; j < TM; j++) {
         const long long m = m0 + lane + 32 * j;
         if (m > m_last) continue;
-        int rp[kWarpN], rn[kWarpN];
+        int rp[TN], rn[TN];
 #pragma unroll
-        for (int c = 0; c < kWarpN; c++) {
+        for (int c = 0; c < TN; c++) {
             rp[c] = 0; rn[c] = 0;
 #pragma unroll
             for (int q = 0; q < NOR; q++) { rp[c] += __popc(tp[j][c][q]); rn[c] += __popc(tn[j][c][q]); }
         }
         if (a.out_nhwc) {
             const size_t base = (size_t)m * a.Co + co0;
-            if ((a.Co & 3) == 0 && co0 + kWarpN <= a.Co) {
-                uint2 *pp = reinterpret_cast<uint2 *>(out_pos + base);
-                uint2 *pn = reinterpret_cast<uint2 *>(out_neg + base);
-                if (a.accumulate) {
-                    const uint2 op = *pp, on = *pn;
-                    rp[0] += (int16_t)(op.x & 0xffff); rp[1] += (int16_t)(op.x >> 16);
-                    rp[2] += (int16_t)(op.y & 0xffff); rp[3] += (int16_t)(op.y >> 16);
-                    rn[0] += (int16_t)(on.x & 0xffff); rn[1] += (int16_t)(on.x >> 16);
-                    rn[2] += (int16_t)(on.y & 0xffff); rn[3] += (int16_t)(on.y >> 16);
+            if ((a.Co & 3) == 0 && co0 + TN <= a.Co) {
+                // TN consecutive int16 per row: one 4- or 8-byte store per output tensor
+                uint32_t *pp = reinterpret_cast<uint32_t *>(out_pos + base);
+                uint32_t *pn = reinterpret_cast<uint32_t *>(out_neg + base);
+#pragma unroll
+                for (int c = 0; c < TN; c += 2) {
+                    if (a.accumulate) {
+                        const uint32_t op = pp[c / 2], on = pn[c / 2];
+                        rp[c] += (int16_t)(op & 0xffff); rp[c + 1] += (int16_t)(op >> 16);
+                        rn[c] += (int16_t)(on & 0xffff); rn[c + 1] += (int16_t)(on >> 16);
+                    }
                 }
-                uint2 vp, vn;
-                vp.x = (uint32_t)(rp[0] & 0xffff) | ((uint32_t)rp[1] << 16);
-                vp.y = (uint32_t)(rp[2] & 0xffff) | ((uint32_t)rp[3] << 16);
-                vn.x = (uint32_t)(rn[0] & 0xffff) | ((uint32_t)rn[1] << 16);
-                vn.y = (uint32_t)(rn[2] & 0xffff) | ((uint32_t)rn[3] << 16);
-                *pp = vp;
-                *pn = vn;
+                if (TN == 4) {
+                    uint2 vp, vn;
+                    vp.x = (uint32_t)(rp[0] & 0xffff) | ((uint32_t)rp[1] << 16);
+                    vp.y = (uint32_t)(rp[TN - 2] & 0xffff) | ((uint32_t)rp[TN - 1] << 16);
+                    vn.x = (uint32_t)(rn[0] & 0xffff) | ((uint32_t)rn[1] << 16);
+                    vn.y = (uint32_t)(rn[TN - 2] & 0xffff) | ((uint32_t)rn[TN - 1] << 16);
+                    *reinterpret_cast<uint2 *>(pp) = vp;
+                    *reinterpret_cast<uint2 *>(pn) = vn;
+                } else {
+                    pp[0] = (uint32_t)(rp[0] & 0xffff) | ((uint32_t)rp[1] << 16);
+                    pn[0] = (uint32_t)(rn[0] & 0xffff) | ((uint32_t)rn[1] << 16);
+                }
             } else {
 #pragma unroll
-                for (int c = 0; c < kWarpN; c++) {
+                for (int c = 0; c < TN; c++) {
                     if (co0 + c < a.Co) {
                         if (a.accumulate) { rp[c] += out_pos[base + c]; rn[c] += out_neg[base + c]; }
                         out_pos[base + c] = (int16_t)rp[c];
@@ -261,7 +276,7 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
             const size_t pixel = (size_t)(m % (long long)ohw);
             const size_t img = (size_t)(m / (long long)ohw);
 #pragma unroll
-            for (int c = 0; c < kWarpN; c++) {
+            for (int c = 0; c < TN; c++) {
                 if (co0 + c < a.Co) {
                     const size_t oi = (img * a.Co + co0 + c) * ohw + pixel;
                     if (a.accumulate) { rp[c] += out_pos[oi]; rn[c] += out_neg[oi]; }
@@ -276,6 +291,7 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
 // Upper bound of the patch length (in words) any tile of BM output pixels can need.
 long long patch_bound(const ConvPlan &p, int BM)
 {
+    if ((long long)BM > p.M) BM = (int)p.M;        // a tile never holds more pixels than exist
     long long dR = (BM + p.OW - 2) / p.OW;         // output-row boundaries a tile can cross
     long long dI = (dR + p.OH - 1) / p.OH;         // image boundaries among them
     long long row_step = (long long)p.sh * p.Wp;
@@ -292,32 +308,42 @@ size_t tiled_smem_bytes(const ConvPlan &p)
            kStages * sizeof(uint64_t);
 }
 
-int pick_tm(const ConvPlan &p)
+// Tile shapes, best first, per OR-n.  16 warps x 2 channels keeps four warps per scheduler resident (the
+// thermometer accumulators cap a 512-thread CTA at 128 registers per thread); OR-1 has so few LOP3 per loaded
+// activation word that it keeps 4 channels per warp.
+struct TileCfg { int tm, nw; };
+int tile_candidates(int n_or, TileCfg (&out)[2])
 {
-    const int pref = p.n_or <= 2 ? 8 : 4; // OR-3 / OR-4 thermometers need the smaller register tile
-    for (int tm = pref; tm >= 4; tm -= 4)
-        if (patch_bound(p, 32 * tm) <= kPlaneWords) return tm;
-    return 0;
+    switch (n_or) {
+    case 1: out[0] = {8, 8}; out[1] = {4, 8}; return 2;
+    case 2: out[0] = {8, 16}; out[1] = {4, 16}; return 2;
+    default: out[0] = {4, 16}; return 1;
+    }
 }
 
-template <int NOR, int TM>
+bool pick_tile(const ConvPlan &p, TileCfg *cfg)
+{
+    TileCfg c[2];
+    const int n = tile_candidates(p.n_or, c);
+    for (int i = 0; i < n; i++)
+        if (patch_bound(p, 32 * c[i].tm) <= kPlaneWords && (p.M + 32 * c[i].tm - 1) / (32 * c[i].tm) <= 65535) {
+            *cfg = c[i];
+            return true;
+        }
+    return false;
+}
+
+template <int NOR, int TM, int NW>
 int launch_one(const ConvPlan &p, const TiledArgs &a, const uint32_t *A, const uint32_t *Wt, const uint32_t *S,
                int16_t *pos, int16_t *neg, int *status, cudaStream_t st)
 {
     const size_t smem = tiled_smem_bytes(p);
-    static thread_local size_t configured = 0;
-    if (smem > configured) {
-        REXSC_CUDA_CHECK(cudaFuncSetAttribute(sc_conv_tiled_kernel<NOR, TM>,
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
-        configured = 227 * 1024;
-    }
+    // per device and cheap: set on every launch rather than caching per process
+    REXSC_CUDA_CHECK(cudaFuncSetAttribute(sc_conv_tiled_kernel<NOR, TM, NW>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const long long tiles_m = (p.M + 32 * TM - 1) / (32 * TM);
-    if (tiles_m > 65535) {
-        // grid.y limit: fall back to the caller's other kernel
-        return REXSC_E_UNSUPPORTED;
-    }
     dim3 grid((unsigned)p.NT, (unsigned)tiles_m);
-    sc_conv_tiled_kernel<NOR, TM><<<grid, kThreads, smem, st>>>(a, A, Wt, S, pos, neg, status);
+    sc_conv_tiled_kernel<NOR, TM, NW><<<grid, NW * 32, smem, st>>>(a, A, Wt, S, pos, neg, status);
     REXSC_LAUNCH_CHECK("sc_conv_tiled_kernel");
     return REXSC_OK;
 }
@@ -329,10 +355,8 @@ bool conv_tiled_supported(const ConvPlan &p)
     if (p.n_or < 1 || p.n_or > 4) return false;
     if (p.KHW > kMaxKhw) return false;
     if (tiled_smem_bytes(p) > 227 * 1024) return false;
-    int tm = pick_tm(p);
-    if (tm == 0) return false;
-    if ((p.M + 32 * tm - 1) / (32 * tm) > 65535) return false;
-    return true;
+    TileCfg cfg;
+    return pick_tile(p, &cfg);
 }
 
 int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
@@ -343,23 +367,23 @@ int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint
     a.Hp = p.Hp; a.Wp = p.Wp; a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw;
     a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.Co = p.Co;
     a.M = p.M; a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
-    const int tm = pick_tm(p);
+    TileCfg cfg;
+    pick_tile(p, &cfg);
     for (int wd = 0; wd < p.words; wd++) {
         a.accumulate = wd > 0;
         const uint32_t *A = d_A + (size_t)wd * p.a_plane_words;
         const uint32_t *Wt = d_Wt + (size_t)wd * p.w_plane_words;
         int rc = REXSC_E_UNSUPPORTED;
-        if (tm == 8) {
-            if (p.n_or == 1) rc = launch_one<1, 8>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st);
-            else rc = launch_one<2, 8>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st);
-        } else {
-            switch (p.n_or) {
-            case 1: rc = launch_one<1, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
-            case 2: rc = launch_one<2, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
-            case 3: rc = launch_one<3, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
-            case 4: rc = launch_one<4, 4>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st); break;
-            }
-        }
+#define REXSC_TILED_CASE(NOR, TM, NW)                                                        \
+    if (p.n_or == NOR && cfg.tm == TM && cfg.nw == NW)                                       \
+        rc = launch_one<NOR, TM, NW>(p, a, A, Wt, d_S, d_pos, d_neg, d_status, st);
+        REXSC_TILED_CASE(1, 8, 8)
+        REXSC_TILED_CASE(1, 4, 8)
+        REXSC_TILED_CASE(2, 8, 16)
+        REXSC_TILED_CASE(2, 4, 16)
+        REXSC_TILED_CASE(3, 4, 16)
+        REXSC_TILED_CASE(4, 4, 16)
+#undef REXSC_TILED_CASE
         if (rc != REXSC_OK) return rc;
     }
     return REXSC_OK;
