@@ -1,0 +1,478 @@
+#!/usr/bin/env python
+"""Benchmark of the SC arithmetic hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (config.workload): the SC forward hot path of SC ResNet-18 at 224x224, channels_last, OR-2 with
+32-bit streams, batch 256 per GPU -- for each of the 19 SC conv layers one call of
+conv2d_generic_general_split_acc (pad + quantise + LFSR streams + OR-n accumulation) exactly as
+utils_functional.py:1179 of the reference calls it, followed by the OR-n activation of the float guide
+(or_approx_n_forward_acc on the pos and the neg sum).  Synthetic inputs: activations uniform in [0,1) quantised
+to 7 bits (what the reference's Hardtanh + QuantizeGrad feed the op), weights N(0, 0.1) clipped to [-1, 1].
+
+One JSON line is printed by rank 0:
+  value      images/s with inputs resident in HBM, CUDA-event time, max over ranks, whole job
+  e2e        the same through the op-level API with HOST (pinned) buffers: H2D of every layer's activation and
+             D2H of every layer's int16 outputs inside the timed region
+  roofline   dominant kernel (tiled SC conv): issued LOP3 lane-ops per second against the LOP3 rate measured
+             live by a register-only probe (integer ALU pipe; the path is bitwise, not HBM- or tensor-bound)
+  cpu_baseline  the reference's own CPU extension (oracle/_ref) on a bounded sample, N=1 only
+`--impl reference` times that CPU extension alone (all host threads) on the same layer list at a reduced batch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROG = (7, 8, 1)
+BATCH = 256
+BIT_LENGTH = 32
+OR_N = 2
+
+# (c_in, spatial size of the UNPADDED input, c_out, kernel, stride, pad, repeats)  -- resnet_sc.py BasicBlock layout
+RESNET18_SC_LAYERS = [
+    (64, 56, 64, 3, 1, 1, 4),
+    (64, 56, 128, 3, 2, 1, 1), (64, 56, 128, 1, 2, 0, 1), (128, 28, 128, 3, 1, 1, 3),
+    (128, 28, 256, 3, 2, 1, 1), (128, 28, 256, 1, 2, 0, 1), (256, 14, 256, 3, 1, 1, 3),
+    (256, 14, 512, 3, 2, 1, 1), (256, 14, 512, 1, 2, 0, 1), (512, 7, 512, 3, 1, 1, 3),
+]
+
+
+def layer_out(h, k, s, p):
+    return (h + 2 * p - k) // s + 1
+
+
+def bitops_per_image(L=BIT_LENGTH):
+    """2 * L * OH*OW * Cout * Cin*KH*KW summed over the SC layers (pos and neg streams, useful channels)."""
+    tot = 0
+    for cin, h, cout, k, s, p, rep in RESNET18_SC_LAYERS:
+        o = layer_out(h, k, s, p)
+        tot += rep * 2 * L * o * o * cout * cin * k * k
+    return tot
+
+
+def products_per_image():
+    tot = 0
+    for cin, h, cout, k, s, p, rep in RESNET18_SC_LAYERS:
+        o = layer_out(h, k, s, p)
+        tot += rep * o * o * cout * cin * k * k
+    return tot
+
+
+# ------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.gpu),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(c for c in clocks if mx is None or c > 0.5 * mx) or sorted(clocks)
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def make_layers(device, batch, seed):
+    """Per distinct layer shape: padded channels_last activation, channels_last weight, stride."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    layers = []
+    for cin, h, cout, k, s, p, rep in RESNET18_SC_LAYERS:
+        x = torch.rand(batch, cin, h, h, generator=g)
+        x = (x * 128).round().clamp(0, 127) / 128
+        x = torch.nn.functional.pad(x, (p, p, p, p)).contiguous(memory_format=torch.channels_last)
+        w = (torch.randn(cout, cin, k, k, generator=g) * 0.1).clamp(-1, 1)
+        w = ((w * 128).round().clamp(-127, 127) / 128).contiguous(memory_format=torch.channels_last)
+        layers.append({"x_host": x, "w_host": w, "stride": s, "rep": rep, "shape": (cin, h, cout, k, s, p)})
+    return layers
+
+
+def run_ours(args, rank, world, local_rank):
+    from rexsc_b200 import _lib, ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    lib = _lib.load()  # fails loudly if the CUDA library is missing
+    layers = make_layers(dev, BATCH, seed=1000 + rank)
+    for l in layers:
+        l["x"] = l["x_host"].to(dev).contiguous(memory_format=torch.channels_last)
+        l["w"] = l["w_host"].to(dev).contiguous(memory_format=torch.channels_last)
+        l["x_pin"] = l["x_host"].pin_memory()
+    # float guide sums for the point-wise kernels: synthetic conv sums of the right shape (fp16 as under autocast)
+    launches = {"n": 0}
+
+    def conv(l, x):
+        launches["n"] += 5  # 2 LUT builds, activation expand, weight expand, tiled accumulate
+        return ops.conv2d_generic_general_split_acc(x, l["w"], BIT_LENGTH, -1, 16, (0, 0), (l["stride"],) * 2, PROG,
+                                                    OR_N - 1, 1, True, False)
+
+    guides = {}
+    for i, l in enumerate(layers):
+        p, n = conv(l, l["x"])
+        g = torch.Generator(device=dev).manual_seed(7 + i)
+        guides[i] = (torch.rand(p.shape, device=dev, generator=g, dtype=torch.float32).to(torch.float16)
+                     .contiguous(memory_format=torch.channels_last) * 4)
+
+    def step_resident():
+        for i, l in enumerate(layers):
+            for _ in range(l["rep"]):
+                conv(l, l["x"])
+                ops.or_approx_n_forward_acc(guides[i], OR_N)
+                ops.or_approx_n_forward_acc(guides[i], OR_N)
+                launches["n"] += 2
+
+    # host-facing step: every call takes pinned host tensors and returns host tensors
+    out_pin = {}
+    for i, l in enumerate(layers):
+        p, n = conv(l, l["x"])
+        out_pin[i] = (torch.empty(p.shape, dtype=p.dtype).contiguous(memory_format=torch.channels_last).pin_memory(),
+                      torch.empty(n.shape, dtype=n.dtype).contiguous(memory_format=torch.channels_last).pin_memory())
+    h2d = sum(l["x_pin"].numel() * 4 * l["rep"] for l in layers)
+    d2h = sum(out_pin[i][0].numel() * 2 * 2 * l["rep"] for i, l in enumerate(layers))
+
+    def step_e2e():
+        for i, l in enumerate(layers):
+            for _ in range(l["rep"]):
+                xd = l["x_pin"].to(dev, non_blocking=True)
+                p, n = conv(l, xd)
+                out_pin[i][0].copy_(p, non_blocking=True)
+                out_pin[i][1].copy_(n, non_blocking=True)
+                ops.or_approx_n_forward_acc(guides[i], OR_N)
+                ops.or_approx_n_forward_acc(guides[i], OR_N)
+                launches["n"] += 2
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, warmup):
+        for _ in range(warmup):
+            step_fn()
+        barrier()
+        launches["n"] = 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step_fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches["n"]
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, n_launch = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _ = timed(step_e2e, max(1, min(args.steps, 5)), 1)
+    e2e_steps = max(1, min(args.steps, 5))
+
+    # ---- dominant kernel: tiled SC conv accumulate, timed alone per layer with CUDA events -----------------
+    import ctypes as C
+    acc_ms = 0.0
+    acc_products = 0
+    exp_ms = 0.0
+    for l in layers:
+        x, w = l["x"], l["w"]
+        d = _lib.ScConvDesc()
+        d.batch, d.c_in, d.h_in, d.w_in = x.shape
+        d.c_out, _, d.kh, d.kw = w.shape
+        d.stride_h = d.stride_w = l["stride"]
+        d.act_dtype, d.act_channels_last, d.w_dtype, d.w_channels_last, d.out_channels_last = 0, 1, 0, 1, 1
+        d.bit_length, d.lfsr_length, d.bin_config, d.gen_config, d.xnor = BIT_LENGTH, -1, OR_N - 1, 1, 1
+        d.prog_total_width, d.prog_load_width, d.prog_load_wait = PROG
+        nbytes = lib.rexsc_sc_conv2d_workspace_size(C.byref(d))
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        oh = (d.h_in - d.kh) // d.stride_h + 1
+        pos = torch.empty((d.batch, d.c_out, oh, oh), dtype=torch.int16, device=dev, memory_format=torch.channels_last)
+        neg = torch.empty_like(pos)
+        st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        vp = lambda t: C.c_void_p(t.data_ptr())
+        for which in ("expand", "accumulate"):
+            best = None
+            for it in range(4):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                if which == "expand":
+                    rc = lib.rexsc_sc_conv2d_expand(C.byref(d), vp(x), vp(w), vp(ws), nbytes, st)
+                else:
+                    rc = lib.rexsc_sc_conv2d_accumulate(C.byref(d), vp(pos), vp(neg), vp(ws), nbytes, st)
+                e1.record()
+                torch.cuda.synchronize()
+                _lib.check(rc, which)
+                t = e0.elapsed_time(e1)
+                if it > 0:
+                    best = t if best is None else min(best, t)
+            if which == "expand":
+                exp_ms += best * l["rep"]
+            else:
+                acc_ms += best * l["rep"]
+        o = oh
+        acc_products += l["rep"] * BATCH * o * o * d.c_out * d.c_in * d.kh * d.kw
+        del ws, pos, neg
+
+    # ---- live LOP3 peak (register-only probe) ------------------------------------------------------------
+    blocks, iters = 148 * 8, 20000
+    ops.alu_probe(blocks, 200, dev)
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.alu_probe(blocks, iters, dev)
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1)
+        best = t if best is None else min(best, t)
+    lop3_peak = blocks * 256 * iters * 64 / (best * 1e-3)  # lane-ops / s
+
+    # ---- point-wise kernel bandwidth (largest layer's guide tensor, > L2) ----------------------------------
+    gbig = guides[0]
+    nbytes_pw = gbig.numel() * (2 + 4)
+    for _ in range(2):
+        ops.or_approx_n_forward_acc(gbig, OR_N)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        ops.or_approx_n_forward_acc(gbig, OR_N)
+    e1.record()
+    torch.cuda.synchronize()
+    pw_gbs = nbytes_pw * 5 / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+    return {
+        "ms": ms, "launches": n_launch, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "h2d": h2d, "d2h": d2h,
+        "clocks": clocks, "acc_ms": acc_ms, "acc_products": acc_products, "exp_ms": exp_ms, "lop3_peak": lop3_peak,
+        "pw_gbs": pw_gbs,
+    }
+
+
+# ------------------------------------------------------------------------------------------------------
+def load_reference_cpu():
+    """The reference's own CPU extension from oracle/_ref (built by oracle/build_ref.py); None if it cannot run
+    on this host."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import build_ref
+
+    so = os.path.join(ROOT, "oracle", "_ref", "sc_extension_ref.so")
+    if not os.path.exists(so):
+        return None
+    # the extension was compiled with -march=native elsewhere: prove in a child process that it runs here
+    probe = ("import sys, torch; sys.path.insert(0, %r); import build_ref; m = build_ref.load(); "
+             "x = torch.rand(1, 8, 6, 6); w = torch.rand(8, 8, 3, 3) - 0.5; "
+             "m[0].conv2d_generic_general(x, w, 32, -1, 16, (1, 1), (1, 1), (7, 8, 1), 1, 1, False, False)"
+             % os.path.join(ROOT, "oracle"))
+    try:
+        if subprocess.run([sys.executable, "-c", probe], capture_output=True, timeout=300).returncode != 0:
+            return None
+        return build_ref.load()
+    except Exception:
+        return None
+
+
+def cpu_reference_time(batch, layers_spec, threads, reps=1):
+    """Seconds for one pass of the SC conv layers at `batch` through the reference CPU extension
+    (conv2d_generic_general, XOR-LFSR semantics: the only ones that code has)."""
+    mods = load_reference_cpu()
+    kind = "reference"
+    if mods is None:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import oracle as port
+
+        kind = "port"
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(5)
+    total = 0.0
+    for cin, h, cout, k, s, p, rep in layers_spec:
+        x = torch.rand(batch, cin, h, h, generator=g).contiguous(memory_format=torch.channels_last)
+        w = (torch.randn(cout, cin, k, k, generator=g) * 0.1).clamp(-1, 1).contiguous(memory_format=torch.channels_last)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if kind == "reference":
+                mods[0].conv2d_generic_general(x, w, BIT_LENGTH, -1, 16, (p, p), (s, s), PROG, OR_N - 1, 1, False, False)
+            else:
+                port.conv2d_generic_general_split(x, w, BIT_LENGTH, -1, 16, (p, p), (s, s), PROG, OR_N - 1, 1, False,
+                                                  False)
+        total += (time.perf_counter() - t0) / reps * rep
+    return total, kind
+
+
+def cpu_baseline_block(sample_batch=4):
+    threads = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    secs, kind = cpu_reference_time(sample_batch, RESNET18_SC_LAYERS, threads)
+    return {
+        "value": sample_batch / secs, "unit": "img/s", "cores": threads, "kind": kind,
+        "sample": f"all 19 SC conv layers of the workload at batch {sample_batch} (of {BATCH}), xnor=False "
+                  f"(the CPU code has no XNOR generator), one pass, {secs:.1f} s",
+    }
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    threads = os.cpu_count() or 1
+    os.environ.setdefault("OMP_NUM_THREADS", str(threads))
+    sample_batch = 4
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_time(sample_batch, RESNET18_SC_LAYERS[:1], threads)
+    t0 = time.perf_counter()
+    kind = "reference"
+    for _ in range(args.steps):
+        _, kind = cpu_reference_time(sample_batch, RESNET18_SC_LAYERS, threads)
+    dt = time.perf_counter() - t0
+    value = sample_batch * args.steps / dt
+    return {
+        "impl": "reference", "metric": "sc_resnet18_or2_L32_sc_forward_img_per_s", "value": value, "unit": "img/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32 bit-streams / int16",
+        "data": "synthetic",
+        "config": {"workload": f"SC ResNet-18 224x224 OR-2 L=32 SC-conv forward, CPU reference at batch {sample_batch} "
+                               f"per step (bounded sample of the batch-{BATCH} workload)"},
+        "cpu_baseline": {"value": value, "unit": "img/s", "cores": threads, "kind": kind,
+                         "sample": f"19 SC conv layers at batch {sample_batch} per step, xnor=False"},
+        "e2e": {"value": value, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 2
+        args.warmup = args.warmup if args.warmup is not None else 1
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    args.steps = args.steps if args.steps is not None else 10
+    args.warmup = max(3, args.warmup if args.warmup is not None else 3)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the rexsc_b200 hot path has no CPU fallback")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    r = run_ours(args, rank, world, local_rank)
+    if world > 1:
+        torch.distributed.barrier()
+    if rank == 0:
+        imgs = BATCH * world * args.steps
+        value = imgs / (r["ms"] * 1e-3)
+        e2e_value = BATCH * world * r["e2e_steps"] / (r["ms_e2e"] * 1e-3)
+        lop3_per_product = 3  # OR-2 thermometer on the non-zero weight stream: x = a&w, T2 |= T1&x, T1 |= x
+        achieved = r["acc_products"] * lop3_per_product / (r["acc_ms"] * 1e-3)
+        line = {
+            "metric": "sc_resnet18_or2_L32_sc_forward_img_per_s", "value": value, "unit": "img/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms"] / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32 bit-streams / int16", "data": "synthetic",
+            "config": {
+                "workload": "SC ResNet-18 224x224 channels_last OR-2 L=32 batch 256/GPU: 19 SC conv2d forwards "
+                            "(fp32 padded activations in, int16 pos/neg out) + 38 OR-n activation forwards (fp16 in)",
+                "batch_per_gpu": BATCH, "parallelism": f"batch-sharded x{world}, no data-path collective",
+                "l2_policy": "inputs larger than L2 (layer activations 13-220 MB, 1.3 GB per step)",
+            },
+            "tbitops_per_s": bitops_per_image() * value / 1e12,
+            "e2e": {"value": e2e_value, "unit": "img/s", "h2d_bytes_per_step": r["h2d"],
+                    "d2h_bytes_per_step": r["d2h"]},
+            "gpu_launches": r["launches"],
+            "clocks": r["clocks"],
+            "roofline": {
+                "bound": "alu", "kernel": "sc_conv_tiled_kernel (OR-n accumulate, all 19 layers)",
+                "achieved": achieved / 1e12, "peak": r["lop3_peak"] / 1e12, "unit": "T lane-LOP3/s",
+                "frac": achieved / r["lop3_peak"], "traffic": None,
+                "peak_source": "measured live: register-only LOP3 probe on this GPU (integer ALU pipe)",
+                "kernel_ms_per_step": r["acc_ms"], "expand_ms_per_step": r["exp_ms"],
+                "tbitops_per_s_kernel": 64 * r["acc_products"] / (r["acc_ms"] * 1e-3) / 1e12,
+            },
+            "roofline_pointwise": {
+                "bound": "hbm", "kernel": "pw_kernel<OrnFwd<half,2>>", "achieved": r["pw_gbs"], "unit": "GB/s",
+                "peak": _hbm_peak(), "frac": r["pw_gbs"] / _hbm_peak(), "peak_source": _hbm_peak_source(),
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_block()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def _hbm_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def _hbm_peak_source():
+    return "MEASURED_PEAKS.json (of measured)" if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) \
+        else "6.65 TB/s (of fallback)"
+
+
+if __name__ == "__main__":
+    main()
