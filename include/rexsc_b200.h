@@ -31,7 +31,8 @@ enum {
     REXSC_E_WORKSPACE = -3,     /* workspace pointer null, misaligned or smaller than *_workspace_size  */
     REXSC_E_TOO_LONG = -4,      /* dot product / stream longer than the accumulators can count          */
     REXSC_E_CUDA = -5,          /* a CUDA runtime call or launch failed (see rexsc_last_cuda_error)     */
-    REXSC_E_DEVICE_TIMEOUT = -6 /* a bounded device-side wait gave up (reported by rexsc_workspace_status) */
+    REXSC_E_DEVICE_TIMEOUT = -6, /* a bounded device-side wait gave up (reported by rexsc_workspace_status) */
+    REXSC_E_STATIC_SCRATCH = -7  /* the call needs more scratch than the library's built-in array holds      */
 };
 
 enum { REXSC_F32 = 0, REXSC_F16 = 1, REXSC_BF16 = 2 };
@@ -87,6 +88,23 @@ int rexsc_sc_conv2d_kernel_choice(const rexsc_sc_conv_desc *desc);
 int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                         int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes,
                         void *stream);
+
+/*
+ * SC conv2d forward without a caller workspace and without any allocation.  No counterpart in the reference
+ * (its kernels cudaMalloc their scratch on first use, torch_c/sc-extension/sc_cuda_kernel.cu:622-632).
+ * Meant for callers that cannot allocate device memory: a plugin inside an application whose own pool owns
+ * the device memory, or a loop that bans allocation calls once it is running because they synchronise the
+ * device.  Same arguments and bit-identical results as rexsc_sc_conv2d_fwd, with the scratch taken from a
+ * fixed 32 MiB array inside the library (rexsc_sc_conv2d_static_scratch_bytes), which every GPU that loads
+ * the library holds until the process ends.  Returns REXSC_E_STATIC_SCRATCH, launching nothing, when
+ * rexsc_sc_conv2d_workspace_size(desc) is larger than that.  The first call on a device resolves the array's
+ * device address: make it before any stream capture starts.  All calls share the array (each call rewrites
+ * what it reads and clears its status word), so calls that overlap on the GPU race: serialise them.
+ * rexsc_workspace_status does not apply; the status word is internal.
+ */
+size_t rexsc_sc_conv2d_static_scratch_bytes(void);
+int rexsc_sc_conv2d_fwd_static(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
+                               int16_t *d_out_pos, int16_t *d_out_neg, void *stream);
 
 /*
  * The two stages of rexsc_sc_conv2d_fwd as separate calls (same descriptor, same workspace):

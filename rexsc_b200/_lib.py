@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(HERE, "librexsc_b200.so")
 OK = 0
 ERRORS = {
     -1: "REXSC_E_BAD_ARG", -2: "REXSC_E_UNSUPPORTED", -3: "REXSC_E_WORKSPACE", -4: "REXSC_E_TOO_LONG",
-    -5: "REXSC_E_CUDA", -6: "REXSC_E_DEVICE_TIMEOUT",
+    -5: "REXSC_E_CUDA", -6: "REXSC_E_DEVICE_TIMEOUT", -7: "REXSC_E_STATIC_SCRATCH",
 }
 F32, F16, BF16 = 0, 1, 2
 KERNEL_AUTO, KERNEL_DIRECT, KERNEL_TILED = 0, 1, 2
@@ -41,6 +41,8 @@ SYMBOLS = {
     "rexsc_sc_conv2d_workspace_size": (_sz, [C.POINTER(ScConvDesc)]),
     "rexsc_sc_conv2d_kernel_choice": (C.c_int, [C.POINTER(ScConvDesc)]),
     "rexsc_sc_conv2d_fwd": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "rexsc_sc_conv2d_static_scratch_bytes": (_sz, []),
+    "rexsc_sc_conv2d_fwd_static": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _vp, _vp]),
     "rexsc_sc_conv2d_expand": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_conv2d_accumulate": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_linear_workspace_size": (_sz, [_i32] * 6),

@@ -75,8 +75,8 @@ static int conv_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, i
     return launch_conv_direct(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, st);
 }
 
-static int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
-                        int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st)
+int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
+                 int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st)
 {
     if (!d_act || !d_weight || !d_out_pos || !d_out_neg) {
         ConvPlan p;

@@ -81,6 +81,10 @@ bool conv_tiled_supported(const ConvPlan &p);
 int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
                       const uint32_t *d_S, int16_t *d_pos, int16_t *d_neg, int *d_status, cudaStream_t st);
 
+// pad + quantise + stream generation + OR-n accumulation with the scratch at d_workspace (capi.cu)
+int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
+                 int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st);
+
 // ---- device helpers -----------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float load_as_float(const T *p, long long i);
 template <> __device__ __forceinline__ float load_as_float<float>(const float *p, long long i) { return p[i]; }
