@@ -137,7 +137,7 @@ def make_layers(device, batch, seed):
 
 
 def run_ours(args, rank, world, local_rank):
-    from rexsc_b200 import _lib, ops
+    from rexsc_b200 import _lib, ops, sharding
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -179,13 +179,21 @@ def run_ours(args, rank, world, local_rank):
     h2d = sum(l["x_pin"].numel() * 4 * l["rep"] for l in layers)
     d2h = sum(out_pin[i][0].numel() * 2 * 2 * l["rep"] for i, l in enumerate(layers))
 
+    from rexsc_b200.host_pipeline import HostConvCall, HostConvPipeline
+
+    pipe = HostConvPipeline(dev)
+    host_calls = []
+    for i, l in enumerate(layers):
+        for _ in range(l["rep"]):
+            host_calls.append(HostConvCall(l["x_pin"], l["w"], out_pin[i][0], out_pin[i][1], BIT_LENGTH,
+                                           (l["stride"],) * 2, OR_N - 1))
+
     def step_e2e():
+        # host buffers in, host buffers out: H2D / compute / D2H of consecutive calls overlap on three streams
+        pipe.run(host_calls)
+        launches["n"] += 5 * len(host_calls)
         for i, l in enumerate(layers):
             for _ in range(l["rep"]):
-                xd = l["x_pin"].to(dev, non_blocking=True)
-                p, n = conv(l, xd)
-                out_pin[i][0].copy_(p, non_blocking=True)
-                out_pin[i][1].copy_(n, non_blocking=True)
                 ops.or_approx_n_forward_acc(guides[i], OR_N)
                 ops.or_approx_n_forward_acc(guides[i], OR_N)
                 launches["n"] += 2
@@ -206,11 +214,7 @@ def run_ours(args, rank, world, local_rank):
             step_fn()
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = sharding.max_over_ranks(e0.elapsed_time(e1), device=dev)
         return ms, launches["n"]
 
     sampler = ClockSampler(local_rank)

@@ -53,7 +53,15 @@ struct ConvPlan {
     int Co, KH, KW, KHW;
     int OH, OW;
     int sh, sw, ph, pw;
-    long long NHW;        // N * Hp * Wp
+    // Stored pixel grid of the activation words.  Only rows / columns a filter tap can touch are kept, and
+    // columns are grouped by their residue modulo the stride so that consecutive output pixels read
+    // consecutive words for every tap (stride 1: the plain padded grid):
+    //   row'  = (h / sh) * nrh + h % sh      kept iff h % sh < nrh = min(sh, KH)
+    //   col'  = (w % sw) * Wq + w / sw       kept iff w % sw < nrw = min(sw, KW),  Wq = ceil(Wp / sw)
+    //   P     = (n * Hrows + row') * Wrow + col',   Hrows = ceil(Hp / sh) * nrh,  Wrow = Wq * nrw
+    int nrh, nrw, Wq, Hrows, Wrow;
+    int max_tap;          // largest tap offset (see tap_offset)
+    long long NHW;        // N * Hrows * Wrow
     long long NHWp;       // plane stride of the activation words (multiple of 4)
     long long M;          // N * OH * OW
     int Cpad, CCH;        // c_in padded to kChunkC, number of channel chunks
@@ -67,6 +75,12 @@ struct ConvPlan {
 };
 
 int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p);
+
+// Word offset of filter tap (kh, kw) relative to the word of tap (0, 0) of the same output pixel.
+__host__ __device__ __forceinline__ int tap_offset(int kh, int kw, int sh, int sw, int nrh, int Wrow, int Wq)
+{
+    return ((kh / sh) * nrh + kh % sh) * Wrow + (kw % sw) * Wq + kw / sw;
+}
 
 // ---- host launchers (each enqueues on `st`, returns REXSC_*) -----------------------------------
 int launch_build_lut(int l, int bit_length, int gen_config, int xnor, int tw, int lw, int lwait, int is_weight,

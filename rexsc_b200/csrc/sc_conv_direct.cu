@@ -13,7 +13,8 @@
 namespace rexsc {
 
 struct DirectArgs {
-    int Hp, Wp, OH, OW, sh, sw, KH, KW, KHW, CCH, NT, Co, words, n_or;
+    int OH, OW, sh, sw, KH, KW, KHW, CCH, NT, Co, words, n_or;
+    int nrh, Wq, Hrows, Wrow;
     long long M, NHWp, a_plane_words, w_plane_words;
     int out_nhwc;
 };
@@ -36,7 +37,7 @@ __global__ void __launch_bounds__(256) sc_conv_direct_kernel(DirectArgs a, const
     const long long t = m / a.OW;
     const int oh = (int)(t % a.OH);
     const int n = (int)(t / a.OH);
-    const long long P0 = ((long long)n * a.Hp + (long long)oh * a.sh) * a.Wp + (long long)ow * a.sw;
+    const long long P0 = ((long long)n * a.Hrows + (long long)oh * a.nrh) * a.Wrow + ow;
     const int w8 = nl >> 2, col = nl & 3;
 
     int res_pos = 0, res_neg = 0;
@@ -49,12 +50,13 @@ __global__ void __launch_bounds__(256) sc_conv_direct_kernel(DirectArgs a, const
         for (int cch = 0; cch < a.CCH; cch++) {
             for (int khw = 0; khw < a.KHW; khw++) {
                 const int kh = khw / a.KW, kw = khw - kh * a.KW;
+                const int tap = tap_offset(kh, kw, a.sh, a.sw, a.nrh, a.Wrow, a.Wq);
                 const size_t blk = ((size_t)nt * a.CCH + cch) * a.KHW + khw;
                 const uint32_t sg = __ldg(S + blk * 8 + w8);
 #pragma unroll
                 for (int cc = 0; cc < kChunkC; cc++) {
                     const int c = cch * kChunkC + cc;
-                    const uint32_t av = __ldg(Aw + (size_t)c * a.NHWp + P0 + (long long)kh * a.Wp + kw);
+                    const uint32_t av = __ldg(Aw + (size_t)c * a.NHWp + P0 + tap);
                     const uint32_t wv = __ldg(Ww + (blk * kChunkC + cc) * kTileN + nl);
                     uint32_t x = av & wv;
                     const bool neg = (sg >> (cc * 4 + col)) & 1u;
@@ -113,7 +115,8 @@ int launch_conv_direct(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uin
                        const uint32_t *d_S, int16_t *d_pos, int16_t *d_neg, cudaStream_t st)
 {
     DirectArgs a;
-    a.Hp = p.Hp; a.Wp = p.Wp; a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw;
+    a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw;
+    a.nrh = p.nrh; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
     a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.NT = p.NT; a.Co = p.Co;
     a.words = p.words; a.n_or = p.n_or; a.M = p.M; a.NHWp = p.NHWp;
     a.a_plane_words = p.a_plane_words; a.w_plane_words = p.w_plane_words;

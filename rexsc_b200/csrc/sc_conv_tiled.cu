@@ -8,8 +8,9 @@
 //   and updates only the positive or only the negative accumulators, halving the LOP3 count.
 //
 //   Shared memory holds, per pipeline stage, the raw activation patch of 8 input channels
-//   ([c][P - P_lo], P the flattened padded pixel index; the filter taps are address offsets kh*Wp + kw into
-//   it, so nothing is im2col-expanded) plus the 8-channel weight block and its sign words.  Stages are
+//   ([c][P - P_lo], P the stored pixel index of ConvPlan; the filter taps are address offsets into it, so
+//   nothing is im2col-expanded, and columns are stored grouped by residue modulo the stride so that the lanes
+//   of a warp read consecutive words for every tap at any stride) plus the 8-channel weight block and its sign words.  Stages are
 //   filled by bulk async copies (cp.async.bulk, one per channel plane + two for the weights) issued by one
 //   thread and tracked by an mbarrier; every wait on it is bounded and reports through a status word.
 //
@@ -27,7 +28,8 @@ constexpr int kStages = 2;
 constexpr uint32_t kWaitLimit = 1u << 22; // bounded mbarrier polling (each poll may itself block briefly)
 
 struct TiledArgs {
-    int Hp, Wp, OH, OW, sh, sw, KH, KW, KHW, CCH, Co;
+    int OH, OW, sh, sw, KH, KW, KHW, CCH, Co;
+    int nrh, Wq, Hrows, Wrow, max_tap;
     long long M, NHWp;
     int out_nhwc, accumulate;
 };
@@ -93,6 +95,7 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
     uint8_t *b_base = a_base + kStages * a_stage_bytes;
     uint8_t *s_base = b_base + kStages * b_stage_bytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(s_base + kStages * s_stage_bytes);
+    int *tap_s = reinterpret_cast<int *>(bars + kStages); // word offset of every filter tap
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nt = blockIdx.x;                       // output-channel tile fastest: CTAs sharing a patch run together
@@ -104,11 +107,11 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         long long t = m / a.OW;
         int oh = (int)(t % a.OH);
         long long n = t / a.OH;
-        return (n * a.Hp + (long long)oh * a.sh) * a.Wp + (long long)ow * a.sw;
+        return (n * a.Hrows + (long long)oh * a.nrh) * a.Wrow + ow;
     };
     const long long m_last = (m0 + BM <= a.M ? m0 + BM : a.M) - 1;
     const long long P_lo = pix0(m0) & ~3LL;
-    const long long P_hi = pix0(m_last) + (long long)(a.KH - 1) * a.Wp + (a.KW - 1);
+    const long long P_hi = pix0(m_last) + a.max_tap;
     const uint32_t patch_words = (uint32_t)(((P_hi - P_lo + 1) + 3) & ~3LL);
 
     int off[TM];
@@ -119,6 +122,10 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         off[j] = (int)(pix0(m) - P_lo);
     }
 
+    if (tid < a.KHW) {
+        const int kh = tid / a.KW, kw = tid - kh * a.KW;
+        tap_s[tid] = tap_offset(kh, kw, a.sh, a.sw, a.nrh, a.Wrow, a.Wq);
+    }
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) mbar_init(smem_u32(&bars[s]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -172,9 +179,9 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         const uint32_t *Ss = reinterpret_cast<const uint32_t *>(s_base + s * s_stage_bytes) + (warp * TN) / kWarpN;
         const int sign_base = (warp * TN) % kWarpN; // first channel of this warp inside its 4-channel sign group
 
-        int kw = 0, koff = 0, krow = 0;
 #pragma unroll 1
         for (int khw = 0; khw < a.KHW; khw++) {
+            const int koff = tap_s[khw];
             const uint32_t sgw = Ss[khw * (kTileN / kWarpN)] >> sign_base;
             const uint32_t *ap[TM];
 #pragma unroll
@@ -204,9 +211,6 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
                     }
                 }
             }
-            // next filter tap: offset kh*Wp + kw into the patch
-            if (++kw == a.KW) { kw = 0; krow += a.Wp; }
-            koff = krow + kw;
         }
         __syncthreads(); // stage s fully consumed
         if (tid == 0 && it + kStages < a.CCH) { issue(it + kStages); issued = it + kStages + 1; }
@@ -294,18 +298,18 @@ long long patch_bound(const ConvPlan &p, int BM)
     if ((long long)BM > p.M) BM = (int)p.M;        // a tile never holds more pixels than exist
     long long dR = (BM + p.OW - 2) / p.OW;         // output-row boundaries a tile can cross
     long long dI = (dR + p.OH - 1) / p.OH;         // image boundaries among them
-    long long row_step = (long long)p.sh * p.Wp;
-    long long img_step = (long long)p.Wp * (p.Hp - (long long)(p.OH - 1) * p.sh);
+    long long row_step = (long long)p.nrh * p.Wrow;
+    long long img_step = (long long)p.Hrows * p.Wrow - (long long)(p.OH - 1) * row_step;
     long long extra = img_step > row_step ? img_step - row_step : 0;
-    long long delta = dR * row_step + dI * extra + (long long)(p.OW - 1) * p.sw;
-    return 3 + delta + (long long)(p.KH - 1) * p.Wp + (p.KW - 1) + 1 + 3;
+    long long delta = dR * row_step + dI * extra + (long long)(p.OW - 1);
+    return 3 + delta + p.max_tap + 1 + 3;
 }
 
 size_t tiled_smem_bytes(const ConvPlan &p)
 {
     return (size_t)kStages * ((size_t)kChunkC * kPlaneWords * 4 + (size_t)p.KHW * kChunkC * kTileN * 4 +
                               (size_t)p.KHW * (kTileN / kWarpN) * 4) +
-           kStages * sizeof(uint64_t);
+           kStages * sizeof(uint64_t) + kMaxKhw * sizeof(int);
 }
 
 // Tile shapes, best first, per OR-n.  16 warps x 2 channels keeps four warps per scheduler resident (the
@@ -364,7 +368,8 @@ int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint
 {
     if (!conv_tiled_supported(p)) return REXSC_E_UNSUPPORTED;
     TiledArgs a;
-    a.Hp = p.Hp; a.Wp = p.Wp; a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw;
+    a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw;
+    a.nrh = p.nrh; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow; a.max_tap = p.max_tap;
     a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.Co = p.Co;
     a.M = p.M; a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
     TileCfg cfg;

@@ -4,7 +4,7 @@
 // generation is a table lookup.  One small kernel builds the table of time-packed stream words
 // (bit t of the word = time slot t); the expand kernels quantise the float tensors and look the words
 // up, writing
-//   activations: A[word][c][P]            P = (n*Hp + h)*Wp + w over the zero-padded tensor
+//   activations: A[word][c][P]            P = stored pixel index over the zero-padded tensor (ConvPlan)
 //   weights:     Wt[word][nt][cch][khw][cc][nl]   (one contiguous block per CTA pipeline stage)
 //                S[nt][cch][khw][warp]    sign bits: bit (cc*4 + col) set = negative weight
 // Only one of the reference's positive / negative weight streams is ever non-zero for a given weight
@@ -126,7 +126,18 @@ int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p)
     if (p->Hp < p->KH || p->Wp < p->KW) return REXSC_E_BAD_ARG;
     p->OH = (p->Hp - p->KH) / p->sh + 1;
     p->OW = (p->Wp - p->KW) / p->sw + 1;
-    p->NHW = (long long)p->N * p->Hp * p->Wp;
+    p->nrh = p->sh < p->KH ? p->sh : p->KH;
+    p->nrw = p->sw < p->KW ? p->sw : p->KW;
+    p->Wq = (p->Wp + p->sw - 1) / p->sw;
+    p->Hrows = (p->Hp + p->sh - 1) / p->sh * p->nrh;
+    p->Wrow = p->Wq * p->nrw;
+    p->max_tap = 0;
+    for (int kh = 0; kh < p->KH; kh++)
+        for (int kw = 0; kw < p->KW; kw++) {
+            int t = tap_offset(kh, kw, p->sh, p->sw, p->nrh, p->Wrow, p->Wq);
+            if (t > p->max_tap) p->max_tap = t;
+        }
+    p->NHW = (long long)p->N * p->Hrows * p->Wrow;
     p->NHWp = (p->NHW + 3) / 4 * 4;
     p->M = (long long)p->N * p->OH * p->OW;
     p->Cpad = (p->C + kChunkC - 1) / kChunkC * kChunkC;
@@ -155,67 +166,82 @@ int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p)
 // (torch_c/sc-extension/sc_cuda_conv.cu:133,139); linear: c only (sc_cuda_matmul.cu:177).
 struct ExpandActArgs {
     int N, C, H, W, Hp, Wp, ph, pw, Cpad;
+    int sh, sw, nrh, nrw, Wq, Hrows, Wrow;
     long long NHW, NHWp, a_plane_words;
     int period, nvals, words, linear_seeds;
     float scale;
 };
 
+// stored pixel index -> (n, h, w) of the padded tensor; false for slots that hold no pixel (they stay zero)
+__device__ __forceinline__ bool decode_pixel(const ExpandActArgs &a, long long P, int &n, int &h, int &w)
+{
+    int col = (int)(P % a.Wrow);
+    long long t = P / a.Wrow;
+    int row = (int)(t % a.Hrows);
+    n = (int)(t / a.Hrows);
+    h = (row / a.nrh) * a.sh + row % a.nrh;
+    w = (col % a.Wq) * a.sw + col / a.Wq;
+    return h < a.Hp && w < a.Wp;
+}
+
+// One CTA expands a tile of 32 stored pixels x 32 channels.  NHWC inputs are read with the channel index
+// fastest (one 128-byte row per pixel and warp), quantised, transposed through shared memory and written with
+// the pixel index fastest (one 128-byte run per channel and warp); NCHW inputs need no transpose.
 template <typename T, bool NHWC>
 __global__ void __launch_bounds__(256) expand_act_kernel(ExpandActArgs a, const T *__restrict__ x,
                                                          const uint32_t *__restrict__ lut, uint32_t *__restrict__ A)
 {
-    // block: 32 consecutive P x 8 channels (one channel chunk); thread (tx = P lane, ty = channel)
-    __shared__ int q_s[8][33];
+    __shared__ uint8_t q_s[32][36]; // [channel][pixel], padded
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const long long P0 = (long long)blockIdx.x * 32;
-    const int c0 = blockIdx.y * 8;
+    const int c0 = blockIdx.y * 32;
     if (NHWC) {
-        // read with channels fastest: thread (rx = channel 0..7, ry = P 0..31)
-        const int rx = threadIdx.x & 7, ry = threadIdx.x >> 3;
-        long long P = P0 + ry;
-        int c = c0 + rx;
-        int q = 0;
-        if (P < a.NHW && c < a.C) {
-            int w = (int)(P % a.Wp);
-            long long t = P / a.Wp;
-            int h = (int)(t % a.Hp);
-            int n = (int)(t / a.Hp);
-            int hi = h - a.ph, wi = w - a.pw;
-            if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W) {
-                long long xi = (((long long)n * a.H + hi) * a.W + wi) * a.C + c;
-                q = quant_ceil_unipolar(load_as_float<T>(x, xi), a.scale);
+        const int c = c0 + tx;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int pl = ty + 8 * i;
+            const long long P = P0 + pl;
+            int q = 0;
+            int n, h, w;
+            if (P < a.NHW && c < a.C && decode_pixel(a, P, n, h, w)) {
+                const int hi = h - a.ph, wi = w - a.pw;
+                if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W) {
+                    const long long xi = (((long long)n * a.H + hi) * a.W + wi) * a.C + c;
+                    q = quant_ceil_unipolar(load_as_float<T>(x, xi), a.scale);
+                }
             }
+            q_s[tx][pl] = (uint8_t)q;
         }
-        q_s[rx][ry] = q;
         __syncthreads();
     }
-    long long P = P0 + tx;
-    int c = c0 + ty;
+    const long long P = P0 + tx;
     if (P >= a.NHWp) return;
-    bool live = (P < a.NHW && c < a.C);
-    int w = 0, h = 0;
-    int q = 0;
-    if (live) {
-        w = (int)(P % a.Wp);
-        long long t = P / a.Wp;
-        h = (int)(t % a.Hp);
-        if (NHWC) {
-            q = q_s[ty][tx];
-        } else {
-            int n = (int)(t / a.Hp);
-            int hi = h - a.ph, wi = w - a.pw;
-            if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W) {
-                long long xi = (((long long)n * a.C + c) * a.H + hi) * a.W + wi;
+    int n = 0, h = 0, w = 0;
+    const bool pixel_live = P < a.NHW && decode_pixel(a, P, n, h, w);
+    const int hi = h - a.ph, wi = w - a.pw;
+    const bool inside = pixel_live && hi >= 0 && hi < a.H && wi >= 0 && wi < a.W;
+    const long long hw_seed = (long long)h * a.Wp + w;
+    const long long plane_seed = (long long)a.Hp * a.Wp;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int c = c0 + ty + 8 * i;
+        if (c >= a.Cpad) break;
+        int q = 0;
+        if (inside && c < a.C) {
+            if (NHWC) {
+                q = q_s[ty + 8 * i][tx];
+            } else {
+                const long long xi = (((long long)n * a.C + c) * a.H + hi) * a.W + wi;
                 q = quant_ceil_unipolar(load_as_float<T>(x, xi), a.scale);
             }
         }
-    }
-    long long seed_ind = a.linear_seeds ? (long long)c : ((long long)c * a.Hp + h) * a.Wp + w;
-    int phase = (int)(seed_ind % a.period);
-    const uint32_t *row = lut + ((size_t)phase * a.nvals + q) * a.words;
-    for (int j = 0; j < a.words; j++) {
-        uint32_t v = (live && q > 0) ? __ldg(row + j) : 0u;
-        A[(size_t)j * a.a_plane_words + (size_t)c * a.NHWp + P] = v;
+        const long long seed_ind = a.linear_seeds ? (long long)c : (long long)c * plane_seed + hw_seed;
+        const int phase = (int)(seed_ind % a.period);
+        const uint32_t *row = lut + ((size_t)phase * a.nvals + q) * a.words;
+        for (int j = 0; j < a.words; j++) {
+            const uint32_t v = q > 0 ? __ldg(row + j) : 0u;
+            A[(size_t)j * a.a_plane_words + (size_t)c * a.NHWp + P] = v;
+        }
     }
 }
 
@@ -223,7 +249,7 @@ template <typename T>
 static int expand_act_dispatch(const ExpandActArgs &a, bool nhwc, const void *x, const uint32_t *lut, uint32_t *A,
                                cudaStream_t st)
 {
-    dim3 grid((unsigned)((a.NHWp + 31) / 32), (unsigned)(a.Cpad / 8));
+    dim3 grid((unsigned)((a.NHWp + 31) / 32), (unsigned)((a.Cpad + 31) / 32));
     if (grid.y > 65535) return REXSC_E_TOO_LONG;
     if (nhwc)
         expand_act_kernel<T, true><<<grid, 256, 0, st>>>(a, (const T *)x, lut, A);
@@ -239,6 +265,7 @@ int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void
     ExpandActArgs a;
     a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
     a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
+    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.scale = (float)p.nvals;
     bool nhwc = d.act_channels_last != 0;

@@ -90,9 +90,10 @@ def _flat_dense(t: torch.Tensor) -> torch.Tensor:
 def conv2d_generic_general_split_acc(input: torch.Tensor, weight: torch.Tensor, bit_length: int, lfsr_length: int,
                                      z_units: int, padding: Sequence[int], stride: Sequence[int],
                                      prog_load: Sequence[int], bin_config: int, gen_config: int, xnor: bool,
-                                     mux: bool) -> List[torch.Tensor]:
+                                     mux: bool, out=None) -> List[torch.Tensor]:
     """SC conv2d forward, returns [pos, neg] int16 (sc_cuda.cpp:87-99).  ``z_units`` and ``mux`` are accepted
-    and unused, as on the reference GPU path (sc_cuda_kernel.cu:565-578)."""
+    and unused, as on the reference GPU path (sc_cuda_kernel.cu:565-578).  ``out`` (not in the reference) lets a
+    caller supply the two int16 output tensors, in the activation's memory format, instead of fresh ones."""
     _require_cuda(input, "conv2d_generic_general_split_acc")
     _require_cuda(weight, "conv2d_generic_general_split_acc")
     if input.dim() != 4 or weight.dim() != 4 or input.size(1) != weight.size(1):
@@ -123,8 +124,16 @@ def conv2d_generic_general_split_acc(input: torch.Tensor, weight: torch.Tensor, 
         oh = (d.h_in + 2 * d.pad_h - d.kh) // d.stride_h + 1
         ow = (d.w_in + 2 * d.pad_w - d.kw) // d.stride_w + 1
         fmt = torch.channels_last if a_cl else torch.contiguous_format
-        pos = torch.empty((d.batch, d.c_out, oh, ow), dtype=torch.int16, device=dev, memory_format=fmt)
-        neg = torch.empty((d.batch, d.c_out, oh, ow), dtype=torch.int16, device=dev, memory_format=fmt)
+        if out is None:
+            pos = torch.empty((d.batch, d.c_out, oh, ow), dtype=torch.int16, device=dev, memory_format=fmt)
+            neg = torch.empty((d.batch, d.c_out, oh, ow), dtype=torch.int16, device=dev, memory_format=fmt)
+        else:
+            pos, neg = out
+            for t in (pos, neg):
+                if (t.dtype != torch.int16 or t.device != dev or tuple(t.shape) != (d.batch, d.c_out, oh, ow)
+                        or not t.is_contiguous(memory_format=fmt)):
+                    raise ValueError("conv2d_generic_general_split_acc: `out` tensors must be int16 "
+                                     f"[{d.batch},{d.c_out},{oh},{ow}] in the activation's memory format")
         ws = _workspace(dev, nbytes)
         rc = lib.rexsc_sc_conv2d_fwd(C.byref(d), _ptr(x), _ptr(w), _ptr(pos), _ptr(neg), _ptr(ws), ws.numel(),
                                      _stream(dev))
