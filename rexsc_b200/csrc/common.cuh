@@ -95,6 +95,21 @@ bool conv_tiled_supported(const ConvPlan &p);
 int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
                       const uint32_t *d_S, int16_t *d_pos, int16_t *d_neg, int *d_status, cudaStream_t st);
 
+// Upper bound of the activation patch (in words per channel plane) a tile of BM output pixels can need in the
+// tiled kernel's shared-memory stage, for a given stored-grid geometry.
+static inline long long patch_bound_words(long long BM, long long M, int OW, int OH, int nrh, int Hrows, int Wrow,
+                                          int max_tap)
+{
+    if (BM > M) BM = M;                              // a tile never holds more pixels than exist
+    const long long dR = (BM + OW - 2) / OW;         // output-row boundaries a tile can cross
+    const long long dI = (dR + OH - 1) / OH;         // image boundaries among them
+    const long long row_step = (long long)nrh * Wrow;
+    const long long img_step = (long long)Hrows * Wrow - (long long)(OH - 1) * row_step;
+    const long long extra = img_step > row_step ? img_step - row_step : 0;
+    const long long delta = dR * row_step + dI * extra + (OW - 1);
+    return 3 + delta + max_tap + 1 + 3;
+}
+
 // pad + quantise + stream generation + OR-n accumulation with the scratch at d_workspace (capi.cu)
 int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
                  int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st);

@@ -98,29 +98,21 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
     int *tap_s = reinterpret_cast<int *>(bars + kStages); // word offset of every filter tap
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nt = blockIdx.x;                       // output-channel tile fastest: CTAs sharing a patch run together
-    const long long m0 = (long long)blockIdx.y * BM; // first output pixel of the tile
+    const int nt = blockIdx.x;                 // output-channel tile fastest: CTAs sharing a patch run together
+    const uint32_t m0 = blockIdx.y * (uint32_t)BM; // first output pixel of the tile (M < 2^31, checked on the host)
 
-    // flattened padded pixel of output pixel m at filter tap (0,0)
-    auto pix0 = [&](long long m) -> long long {
-        int ow = (int)(m % a.OW);
-        long long t = m / a.OW;
-        int oh = (int)(t % a.OH);
-        long long n = t / a.OH;
-        return (n * a.Hrows + (long long)oh * a.nrh) * a.Wrow + ow;
+    // stored pixel index of output pixel m at filter tap (0,0); fits 31 bits (NHWp < 2^31)
+    auto pix0 = [&](uint32_t m) -> uint32_t {
+        const uint32_t ow = m % (uint32_t)a.OW;
+        const uint32_t t = m / (uint32_t)a.OW;
+        const uint32_t oh = t % (uint32_t)a.OH;
+        const uint32_t n = t / (uint32_t)a.OH;
+        return (n * (uint32_t)a.Hrows + oh * (uint32_t)a.nrh) * (uint32_t)a.Wrow + ow;
     };
-    const long long m_last = (m0 + BM <= a.M ? m0 + BM : a.M) - 1;
-    const long long P_lo = pix0(m0) & ~3LL;
-    const long long P_hi = pix0(m_last) + a.max_tap;
-    const uint32_t patch_words = (uint32_t)(((P_hi - P_lo + 1) + 3) & ~3LL);
-
-    int off[TM];
-#pragma unroll
-    for (int j = 0; j < TM; j++) {
-        long long m = m0 + lane + 32 * j;
-        if (m > m_last) m = m_last;
-        off[j] = (int)(pix0(m) - P_lo);
-    }
+    const uint32_t m_last = (m0 + BM <= (uint32_t)a.M ? m0 + BM : (uint32_t)a.M) - 1;
+    const uint32_t P_lo = pix0(m0) & ~3u;
+    const uint32_t P_hi = pix0(m_last) + (uint32_t)a.max_tap;
+    const uint32_t patch_words = ((P_hi - P_lo + 1) + 3) & ~3u;
 
     if (tid < a.KHW) {
         const int kh = tid / a.KW, kw = tid - kh * a.KW;
@@ -150,11 +142,19 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         bulk_g2s(smem_u32(s_base + s * s_stage_bytes), S + blk * (kTileN / kWarpN), s_stage_bytes, bar);
     };
 
+    // first stage in flight while the per-row offsets are worked out
     int issued = 0;
     if (tid == 0 && !failed) {
         issue(0);
         issued = 1;
-        if (a.CCH > 1) { issue(1); issued = 2; }
+    }
+
+    int off[TM];
+#pragma unroll
+    for (int j = 0; j < TM; j++) {
+        uint32_t m = m0 + lane + 32 * j;
+        if (m > m_last) m = m_last;
+        off[j] = (int)(pix0(m) - P_lo);
     }
 
     uint32_t tp[TM][TN][NOR], tn[TM][TN][NOR];
@@ -170,9 +170,11 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
         if (!failed) {
             if (!mbar_wait_bounded(smem_u32(&bars[s]), (uint32_t)((it >> 1) & 1))) failed = true;
         }
-        // every thread must agree before touching the stage or re-arming it
+        // One barrier per step: every thread agrees on success, and everyone has finished reading the other
+        // stage (step it-1), so it can be refilled for step it+1 while step it is computed.
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
         if (failed) break;
+        if (tid == 0 && it + 1 < a.CCH) { issue(it + 1); issued = it + 2; }
 
         const uint32_t *As = reinterpret_cast<const uint32_t *>(a_base + s * a_stage_bytes);
         const uint32_t *Bs = reinterpret_cast<const uint32_t *>(b_base + s * b_stage_bytes) + warp * TN;
@@ -212,15 +214,14 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
                 }
             }
         }
-        __syncthreads(); // stage s fully consumed
-        if (tid == 0 && it + kStages < a.CCH) { issue(it + kStages); issued = it + kStages + 1; }
     }
 
     if (failed) {
         // report, then give copies that may still be in flight a bounded chance to land before exiting
         if (tid == 0) {
             atomicExch(status, patch_ok ? 1 : 2);
-            for (int it = 0; it < issued; it++)
+            // only the two most recent copies can still be in flight (one per stage)
+            for (int it = issued > 2 ? issued - 2 : 0; it < issued; it++)
                 (void)mbar_wait_bounded(smem_u32(&bars[it & 1]), (uint32_t)((it >> 1) & 1));
         }
         return;
@@ -231,7 +232,7 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
     const size_t ohw = (size_t)a.OH * a.OW;
 #pragma unroll
     for (int j = 0; j < TM; j++) {
-        const long long m = m0 + lane + 32 * j;
+        const uint32_t m = m0 + lane + 32 * j;
         if (m > m_last) continue;
         int rp[TN], rn[TN];
 #pragma unroll
@@ -277,8 +278,8 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
                 }
             }
         } else {
-            const size_t pixel = (size_t)(m % (long long)ohw);
-            const size_t img = (size_t)(m / (long long)ohw);
+            const size_t pixel = (size_t)(m % (uint32_t)ohw);
+            const size_t img = (size_t)(m / (uint32_t)ohw);
 #pragma unroll
             for (int c = 0; c < TN; c++) {
                 if (co0 + c < a.Co) {
@@ -292,17 +293,9 @@ sc_conv_tiled_kernel(TiledArgs a, const uint32_t *__restrict__ A, const uint32_t
     }
 }
 
-// Upper bound of the patch length (in words) any tile of BM output pixels can need.
 long long patch_bound(const ConvPlan &p, int BM)
 {
-    if ((long long)BM > p.M) BM = (int)p.M;        // a tile never holds more pixels than exist
-    long long dR = (BM + p.OW - 2) / p.OW;         // output-row boundaries a tile can cross
-    long long dI = (dR + p.OH - 1) / p.OH;         // image boundaries among them
-    long long row_step = (long long)p.nrh * p.Wrow;
-    long long img_step = (long long)p.Hrows * p.Wrow - (long long)(p.OH - 1) * row_step;
-    long long extra = img_step > row_step ? img_step - row_step : 0;
-    long long delta = dR * row_step + dI * extra + (long long)(p.OW - 1);
-    return 3 + delta + p.max_tap + 1 + 3;
+    return patch_bound_words(BM, p.M, p.OW, p.OH, p.nrh, p.Hrows, p.Wrow, p.max_tap);
 }
 
 size_t tiled_smem_bytes(const ConvPlan &p)

@@ -10,6 +10,8 @@
 // Only one of the reference's positive / negative weight streams is ever non-zero for a given weight
 // (w_pos = ceil(clamp(w*L,0,L-1)), w_neg = ceil(-clamp(w*L,1-L,0)): torch_c/sc-extension/sc_cuda.cpp:92-93),
 // and a zero value gives an all-zero stream, so a single word plus a sign bit carries both.
+#include <string.h>
+
 #include "common.cuh"
 
 namespace rexsc {
@@ -97,7 +99,35 @@ static int lfsr_length_for(int bit_length)
     }
 }
 
+static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p);
+
+// Plans are pure functions of the descriptor; a call derives its plan several times (size query, expand,
+// accumulate) and a network repeats a handful of descriptors, so the last few are kept per host thread.
 int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p)
+{
+    if (!d || !p) return REXSC_E_BAD_ARG;
+    struct Entry { rexsc_sc_conv_desc key; ConvPlan plan; bool used; };
+    constexpr int kEntries = 64;
+    static thread_local Entry cache[kEntries];
+    static thread_local int next = 0;
+    rexsc_sc_conv_desc key = *d;
+    key.kernel = 0; // the kernel choice does not enter the plan
+    for (int i = 0; i < kEntries; i++)
+        if (cache[i].used && memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
+            *p = cache[i].plan;
+            return REXSC_OK;
+        }
+    int rc = make_conv_plan_uncached(d, p);
+    if (rc != REXSC_OK) return rc;
+    Entry &e = cache[next];
+    next = (next + 1) % kEntries;
+    e.key = key;
+    e.plan = *p;
+    e.used = true;
+    return REXSC_OK;
+}
+
+static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
 {
     if (!d || !p) return REXSC_E_BAD_ARG;
     if (d->batch < 1 || d->c_in < 1 || d->h_in < 1 || d->w_in < 1 || d->c_out < 1 || d->kh < 1 || d->kw < 1)
@@ -131,6 +161,54 @@ int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p)
     p->Wq = (p->Wp + p->sw - 1) / p->sw;
     p->Hrows = (p->Hp + p->sh - 1) / p->sh * p->nrh;
     p->Wrow = p->Wq * p->nrw;
+    p->M = (long long)p->N * p->OH * p->OW;
+    {
+        // Row pitch: the 32 lanes of a warp read the words of 32 consecutive output pixels; when a warp spans
+        // several output rows (narrow feature maps) the pitch decides how many of those words share a
+        // shared-memory bank.  Pick the padding (< 32 words) with the fewest bank passes per load, weighing
+        // passes against the memory the padding costs.
+        const int base = p->Wrow;
+        double best_cost = 1e30;
+        int best_pitch = base;
+        auto max_tap_for = [&](int pitch) {
+            int mt = 0;
+            for (int kh = 0; kh < p->KH; kh++)
+                for (int kw = 0; kw < p->KW; kw++) {
+                    int t = tap_offset(kh, kw, p->sh, p->sw, p->nrh, pitch, p->Wq);
+                    if (t > mt) mt = t;
+                }
+            return mt;
+        };
+        // largest tile (256, else 128 pixels) whose patch fits the tiled kernel's stage at the unpadded pitch;
+        // padding must not push that tile out of the stage
+        int fit_bm = 0;
+        for (int bm = 256; bm >= 128 && !fit_bm; bm -= 128)
+            if (patch_bound_words(bm, p->M, p->OW, p->OH, p->nrh, p->Hrows, base, max_tap_for(base)) <= kPlaneWords)
+                fit_bm = bm;
+        for (int pad = 0; pad < 32; pad++) {
+            const int pitch = base + pad;
+            if (pad > 0 && fit_bm &&
+                patch_bound_words(fit_bm, p->M, p->OW, p->OH, p->nrh, p->Hrows, pitch, max_tap_for(pitch)) > kPlaneWords)
+                continue;
+            const long long img = (long long)p->Hrows * pitch;
+            double passes = 0;
+            int samples = 0;
+            for (long long m0 = 0; m0 < p->M && samples < 64; m0 += 32, samples++) {
+                int cnt[32] = {0};
+                int worst = 0;
+                for (int lane = 0; lane < 32 && m0 + lane < p->M; lane++) {
+                    const long long m = m0 + lane;
+                    const long long ow = m % p->OW, t = m / p->OW, oh = t % p->OH, n = t / p->OH;
+                    const int bank = (int)((n * img + oh * (long long)p->nrh * pitch + ow) & 31);
+                    if (++cnt[bank] > worst) worst = cnt[bank];
+                }
+                passes += worst;
+            }
+            const double cost = passes / samples * (1.0 + 1.0 * pad / base);
+            if (cost < best_cost - 1e-9) { best_cost = cost; best_pitch = pitch; }
+        }
+        p->Wrow = best_pitch;
+    }
     p->max_tap = 0;
     for (int kh = 0; kh < p->KH; kh++)
         for (int kw = 0; kw < p->KW; kw++) {
@@ -139,7 +217,6 @@ int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p)
         }
     p->NHW = (long long)p->N * p->Hrows * p->Wrow;
     p->NHWp = (p->NHW + 3) / 4 * 4;
-    p->M = (long long)p->N * p->OH * p->OW;
     p->Cpad = (p->C + kChunkC - 1) / kChunkC * kChunkC;
     p->CCH = p->Cpad / kChunkC;
     p->NT = (p->Co + kTileN - 1) / kTileN;
@@ -181,7 +258,7 @@ __device__ __forceinline__ bool decode_pixel(const ExpandActArgs &a, long long P
     n = (int)(t / a.Hrows);
     h = (row / a.nrh) * a.sh + row % a.nrh;
     w = (col % a.Wq) * a.sw + col / a.Wq;
-    return h < a.Hp && w < a.Wp;
+    return col < a.Wq * a.nrw && h < a.Hp && w < a.Wp; // pitch padding holds no pixel
 }
 
 // One CTA expands a tile of 32 stored pixels x 32 channels.  NHWC inputs are read with the channel index
