@@ -314,6 +314,7 @@ int tile_candidates(int n_or, TileCfg (&out)[2])
     switch (n_or) {
     case 1: out[0] = {8, 8}; out[1] = {4, 8}; return 2;
     case 2: out[0] = {8, 16}; out[1] = {4, 16}; return 2;
+    case 3: out[0] = {8, 16}; out[1] = {4, 16}; return 2; // 128 registers, a few bytes of spill
     default: out[0] = {4, 16}; return 1;
     }
 }
@@ -379,6 +380,7 @@ int launch_conv_tiled(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint
         REXSC_TILED_CASE(1, 4, 8)
         REXSC_TILED_CASE(2, 8, 16)
         REXSC_TILED_CASE(2, 4, 16)
+        REXSC_TILED_CASE(3, 8, 16)
         REXSC_TILED_CASE(3, 4, 16)
         REXSC_TILED_CASE(4, 4, 16)
 #undef REXSC_TILED_CASE

@@ -244,18 +244,20 @@ static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
 struct ExpandActArgs {
     int N, C, H, W, Hp, Wp, ph, pw, Cpad;
     int sh, sw, nrh, nrw, Wq, Hrows, Wrow;
+    uint32_t plane_mod; // (Hp * Wp) mod period
     long long NHW, NHWp, a_plane_words;
     int period, nvals, words, linear_seeds;
     float scale;
 };
 
 // stored pixel index -> (n, h, w) of the padded tensor; false for slots that hold no pixel (they stay zero)
-__device__ __forceinline__ bool decode_pixel(const ExpandActArgs &a, long long P, int &n, int &h, int &w)
+__device__ __forceinline__ bool decode_pixel(const ExpandActArgs &a, long long P64, int &n, int &h, int &w)
 {
-    int col = (int)(P % a.Wrow);
-    long long t = P / a.Wrow;
-    int row = (int)(t % a.Hrows);
-    n = (int)(t / a.Hrows);
+    const uint32_t P = (uint32_t)P64; // stored pixel indices fit 31 bits (checked when the plan is made)
+    const int col = (int)(P % (uint32_t)a.Wrow);
+    const uint32_t t = P / (uint32_t)a.Wrow;
+    const int row = (int)(t % (uint32_t)a.Hrows);
+    n = (int)(t / (uint32_t)a.Hrows);
     h = (row / a.nrh) * a.sh + row % a.nrh;
     w = (col % a.Wq) * a.sw + col / a.Wq;
     return col < a.Wq * a.nrw && h < a.Hp && w < a.Wp; // pitch padding holds no pixel
@@ -297,8 +299,8 @@ __global__ void __launch_bounds__(256) expand_act_kernel(ExpandActArgs a, const 
     const bool pixel_live = P < a.NHW && decode_pixel(a, P, n, h, w);
     const int hi = h - a.ph, wi = w - a.pw;
     const bool inside = pixel_live && hi >= 0 && hi < a.H && wi >= 0 && wi < a.W;
-    const long long hw_seed = (long long)h * a.Wp + w;
-    const long long plane_seed = (long long)a.Hp * a.Wp;
+    // seed index c*Hp*Wp + h*Wp + w reduced modulo the LFSR period with 32-bit arithmetic
+    const uint32_t hw_mod = ((uint32_t)h * (uint32_t)a.Wp + (uint32_t)w) % (uint32_t)a.period;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int c = c0 + ty + 8 * i;
@@ -312,8 +314,8 @@ __global__ void __launch_bounds__(256) expand_act_kernel(ExpandActArgs a, const 
                 q = quant_ceil_unipolar(load_as_float<T>(x, xi), a.scale);
             }
         }
-        const long long seed_ind = a.linear_seeds ? (long long)c : (long long)c * plane_seed + hw_seed;
-        const int phase = (int)(seed_ind % a.period);
+        const uint32_t phase = a.linear_seeds ? (uint32_t)c % (uint32_t)a.period
+                                              : ((uint32_t)c * a.plane_mod + hw_mod) % (uint32_t)a.period;
         const uint32_t *row = lut + ((size_t)phase * a.nvals + q) * a.words;
         for (int j = 0; j < a.words; j++) {
             const uint32_t v = q > 0 ? __ldg(row + j) : 0u;
@@ -343,6 +345,7 @@ int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void
     a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
     a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
     a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.scale = (float)p.nvals;
     bool nhwc = d.act_channels_last != 0;
