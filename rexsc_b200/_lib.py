@@ -30,7 +30,7 @@ class FxpConvDesc(C.Structure):
     """Mirror of rexsc_fxp_conv_desc (include/rexsc_b200.h)."""
     _fields_ = [(n, C.c_int32) for n in (
         "batch", "c_in", "h_in", "w_in", "c_out", "kh", "kw", "pad_h", "pad_w", "stride_h", "stride_w",
-        "act_dtype", "w_dtype", "add_config", "precision_in", "precision_out")]
+        "act_dtype", "w_dtype", "add_config", "precision_in", "precision_out", "kernel")]
 
 
 # name -> (restype, argtypes); every symbol include/rexsc_b200.h declares

@@ -7,7 +7,7 @@
 //     sat_shift(v)   = ((min(v, max) >> d) + ((min(v, max) >> max(0, d-1)) & 1)) << d,
 // d = max(0, 2p - p_out), max = ((2^min(31, max(2p, p_out)) - 1) >> d) << d, and the output is pos - neg.
 //
-// Two kernels:
+// Three kernels (the closed form also has a tensor-core implementation, fxp_conv_umma.cu, used by default):
 //   * closed form (add_config 0, d = 0 -- every configuration the reference front end uses): with d = 0 the
 //     accumulator is always even after an add, so each add contributes prod + (prod & 1) until the cap:
 //         pos = min( sum a*w+ + sum (a&1)(w+&1), 2^pmax ),  all addends >= 0, hence order-free.
@@ -235,11 +235,17 @@ __global__ void __launch_bounds__(128) fxp_conv_closed_kernel(FxpArgs a, const i
 
 } // namespace
 
+size_t fxp_umma_workspace_bytes(int N, int C, int Hp, int Wp, int Co, long long K);
+bool fxp_umma_supported(int C, int Hp, int Wp, long long K);
+int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
+                         const int32_t *qa, const int32_t *qp, const int32_t *qn, void *ws, int32_t *out, int *status,
+                         cudaStream_t st);
+
 struct FxpPlan {
     FxpArgs a;
-    bool closed;
+    bool closed, umma;
     int Kw, Cop, cap;
-    size_t off_qa, off_qp, off_qn, off_pk, total;
+    size_t off_status, off_qa, off_qp, off_qn, off_pk, off_umma, total;
 };
 
 static int make_fxp_plan(const rexsc_fxp_conv_desc *d, FxpPlan *p)
@@ -278,11 +284,17 @@ static int make_fxp_plan(const rexsc_fxp_conv_desc *d, FxpPlan *p)
     p->cap = p->closed ? (1 << pm) : 0;
     p->Kw = (int)((a.K + 3) / 4);
     p->Cop = (a.Co + kFxpCo - 1) / kFxpCo * kFxpCo;
+    if (d->kernel < 0 || d->kernel > 2) return REXSC_E_BAD_ARG;
+    p->umma = p->closed && d->kernel != 1 && fxp_umma_supported(a.C, a.Hp, a.Wp, a.K);
+    if (d->kernel == 2 && !p->umma) return REXSC_E_UNSUPPORTED;
     size_t off = 0;
+    p->off_status = off; off += 256;
     p->off_qa = off; off += align_up((size_t)n_act * 4, 256);
     p->off_qp = off; off += align_up((size_t)a.Co * a.K * 4, 256);
     p->off_qn = off; off += align_up((size_t)a.Co * a.K * 4, 256);
     p->off_pk = off; off += align_up((size_t)p->Kw * 4 * p->Cop * 4, 256);
+    p->off_umma = off;
+    if (p->umma) off += fxp_umma_workspace_bytes(a.N, a.C, a.Hp, a.Wp, a.Co, a.K);
     p->total = off;
     return REXSC_OK;
 }
@@ -311,7 +323,9 @@ extern "C" int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void 
     uint8_t *ws = (uint8_t *)d_workspace;
     int32_t *qa = (int32_t *)(ws + p.off_qa), *qp = (int32_t *)(ws + p.off_qp), *qn = (int32_t *)(ws + p.off_qn);
     uint32_t *pk = (uint32_t *)(ws + p.off_pk);
+    int *status = (int *)(ws + p.off_status);
     const FxpArgs &a = p.a;
+    REXSC_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, st));
     long long n_act = (long long)a.N * a.C * a.Hp * a.Wp;
     unsigned gb = (unsigned)((n_act + 255) / 256 < 148 * 32 ? (n_act + 255) / 256 : 148 * 32);
     switch (desc->act_dtype) {
@@ -328,6 +342,10 @@ extern "C" int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void 
     default: fxp_quant_w_kernel<__nv_bfloat16><<<wb, 256, 0, st>>>(a, (const __nv_bfloat16 *)d_weight, qp, qn); break;
     }
     REXSC_LAUNCH_CHECK("fxp_quant_w_kernel");
+    if (p.umma) {
+        return launch_fxp_conv_umma(a.N, a.C, a.Hp, a.Wp, a.Co, a.KH, a.KW, a.OH, a.OW, a.sh, a.sw, p.cap, qa, qp, qn,
+                                    ws + p.off_umma, d_out, status, st);
+    }
     if (p.closed) {
         long long tot = (long long)p.Kw * p.Cop;
         fxp_pack_w_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(a, qp, qn, p.Kw, p.Cop, pk);

@@ -1,0 +1,325 @@
+// FXP saturating conv, closed form, on the 5th-generation tensor cores (tcgen05, int8 -> int32 in TMEM).
+//
+// Valid exactly where fxp_conv.cu's closed form is (plain add, no shift, operands <= 127): per sign the
+// reference's sequential saturating adder equals  min( sum a*w + sum (a&1)(w&1), 2^pmax ), every addend is
+// non-negative, so splitting K into MMA steps cannot change where the sum saturates -- the cap is applied once to
+// the finished int32 accumulator (the host checks that K*127*127 + K cannot overflow it).
+//
+// Implicit GEMM:  D[m][n'] = sum_k' A[m][k'] * B[n'][k'],  k' runs over the K = Cin*KH*KW products twice
+// (values, then parity bits), n' over the output channels of the CTA's chunk twice (positive weights, then
+// negative weights).  CTA = 128 output pixels (TMEM lanes) x up to 256 columns.
+//   * producers (all 128 threads): gather the int8 activation slab (128 rows x 128 bytes of k') through a
+//     k' -> tensor-offset table and copy the prepacked weight slab, both written to shared memory in the
+//     128-byte swizzled K-major layout the MMA's shared-memory descriptors name;
+//   * one thread issues tcgen05.mma.kind::i8 (M=128, N=N', K=32) four times per slab and commits to an mbarrier;
+//   * epilogue: tcgen05.ld 32 lanes x 32 columns per warp, min(., cap), pos - neg, coalesced NCHW int32 stores.
+// Every mbarrier wait is bounded; on a time-out the CTA records it, frees its TMEM and returns.
+#include "common.cuh"
+
+namespace rexsc {
+
+namespace {
+
+constexpr int kUmmaM = 128;          // output pixels per CTA = TMEM lanes
+constexpr int kSlabBytes = 128;      // k' bytes per pipeline step (one 128-byte swizzle row)
+constexpr int kUmmaK = 32;           // int8 elements per MMA instruction
+constexpr uint32_t kUmmaWaitLimit = 1u << 22;
+
+struct UmmaArgs {
+    int N, C, Hp, Wp, Co, OH, OW, sh, sw;
+    int Kp;          // k' extent padded to kSlabBytes (values + parity)
+    int CB, CBp;     // output channels per CTA chunk, padded to 8
+    int CBq;         // first MMA column of the negative-weight block (CBp rounded up to 32: aligned TMEM reads)
+    int NP;          // MMA N: positive block [0, CBp), negative block [CBq, CBq + CBp), padded to 16
+    int tmem_cols;   // power of two >= NP, >= 32
+    int cap;
+    long long M;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t saddr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fff);       // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                       // layout type: 128-byte swizzle
+    return d;
+}
+
+// byte offset of 16-byte chunk `c` (0..7) of row `r` inside a [rows][128 B] tile with 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kUmmaWaitLimit; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(128, 1)
+fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *__restrict__ wpk,
+                     const int32_t *__restrict__ koff, int32_t *__restrict__ out, int *__restrict__ status)
+{
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    // the swizzled operand tiles must start on a 1024-byte boundary of the shared window
+    uint8_t *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    uint8_t *a_s = smem;                                   // 128 rows x 128 B
+    uint8_t *b_s = smem + kUmmaM * kSlabBytes;             // NP rows x 128 B (1024-byte aligned: 16 KB offset)
+    uint64_t *bar = reinterpret_cast<uint64_t *>(b_s + 256 * kSlabBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const long long m = (long long)blockIdx.x * kUmmaM + tid;
+    const int chunk = blockIdx.y;
+    const bool row_live = m < a.M;
+    long long abase = 0;
+    int ow = 0, oh = 0, n = 0;
+    if (row_live) {
+        ow = (int)(m % a.OW);
+        long long t = m / a.OW;
+        oh = (int)(t % a.OH);
+        n = (int)(t / a.OH);
+        abase = (((long long)n * a.C) * a.Hp + (long long)oh * a.sh) * a.Wp + (long long)ow * a.sw;
+    }
+
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)),
+                     "r"((uint32_t)a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // instruction descriptor: int32 accumulate, signed int8 A and B, both K-major, N = NP, M = 128
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.NP >> 3) << 17) | ((uint32_t)(kUmmaM >> 4) << 24);
+    const int8_t *wchunk = wpk + (size_t)chunk * a.NP * a.Kp;
+    const int n_slabs = a.Kp / kSlabBytes;
+    bool failed = false;
+
+    for (int slab = 0; slab < n_slabs; slab++) {
+        // ---- A slab: row = this thread's output pixel, 8 chunks of 16 k' each --------------------------------
+#pragma unroll 1
+        for (int c = 0; c < 8; c++) {
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            if (row_live) {
+#pragma unroll
+                for (int b = 0; b < 16; b++) {
+                    const int kp = slab * kSlabBytes + c * 16 + b;
+                    const int off = __ldg(koff + kp);           // < 0: padding; bit 30 set: parity operand
+                    if (off >= 0) {
+                        int v = (int)__ldg(act + abase + (off & 0x3fffffff));
+                        if (off & 0x40000000) v &= 1;
+                        w[b >> 2] |= (uint32_t)(v & 0xff) << (8 * (b & 3));
+                    }
+                }
+            }
+            *reinterpret_cast<uint4 *>(a_s + sw128_offset(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        // ---- B slab: NP rows x 8 chunks, straight copy of the prepacked weights ------------------------------
+        for (int i = tid; i < a.NP * 8; i += blockDim.x) {
+            const int r = i >> 3, c = i & 7;
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(wchunk + (size_t)r * a.Kp + slab * kSlabBytes) + c);
+            *reinterpret_cast<uint4 *>(b_s + sw128_offset(r, c)) = v;
+        }
+        // generic-proxy writes must be visible to the tensor core's async-proxy reads
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint64_t da = umma_desc_k_sw128(smem_addr(a_s));
+            const uint64_t db = umma_desc_k_sw128(smem_addr(b_s));
+#pragma unroll
+            for (int kk = 0; kk < kSlabBytes / kUmmaK; kk++) {
+                const uint32_t accumulate = (slab > 0 || kk > 0) ? 1u : 0u;
+                // advancing K inside the swizzle row: +32 bytes = +2 in the descriptor's 16-byte address units
+                const uint64_t dak = da + (uint64_t)(kk * (kUmmaK >> 4));
+                const uint64_t dbk = db + (uint64_t)(kk * (kUmmaK >> 4));
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "setp.ne.b32 p, %4, 0;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                    ::"r"(tmem_base), "l"(dak), "l"(dbk), "r"(idesc), "r"(accumulate), "r"(0u)
+                    : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_addr(bar))
+                         : "memory");
+        }
+        // the slab buffers are reused next step: wait until the MMAs that read them have completed
+        if (!mbar_wait(smem_addr(bar), (uint32_t)(slab & 1))) failed = true;
+        failed = __syncthreads_or(failed ? 1 : 0) != 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (failed) break;
+    }
+
+    if (!failed) {
+        // ---- epilogue: this warp reads its 32 TMEM lanes, 32 columns at a time ---------------------------------
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const size_t ohw = (size_t)a.OH * a.OW;
+        for (int c0 = 0; c0 < a.CBp; c0 += 32) {
+            uint32_t vp[32], vn[32];
+            const uint32_t tp = tmem_base + lane_base + (uint32_t)c0;
+            const uint32_t tn = tmem_base + lane_base + (uint32_t)(a.CBq + c0);
+            // both reads start on a multiple of 32 columns and stay inside the allocation (tmem_cols >= 2 * CBq);
+            // columns at or past CB carry zero weights and are masked below
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(vp[0]), "=r"(vp[1]), "=r"(vp[2]), "=r"(vp[3]), "=r"(vp[4]), "=r"(vp[5]), "=r"(vp[6]), "=r"(vp[7]),
+                  "=r"(vp[8]), "=r"(vp[9]), "=r"(vp[10]), "=r"(vp[11]), "=r"(vp[12]), "=r"(vp[13]), "=r"(vp[14]),
+                  "=r"(vp[15]), "=r"(vp[16]), "=r"(vp[17]), "=r"(vp[18]), "=r"(vp[19]), "=r"(vp[20]), "=r"(vp[21]),
+                  "=r"(vp[22]), "=r"(vp[23]), "=r"(vp[24]), "=r"(vp[25]), "=r"(vp[26]), "=r"(vp[27]), "=r"(vp[28]),
+                  "=r"(vp[29]), "=r"(vp[30]), "=r"(vp[31])
+                : "r"(tp) : "memory");
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(vn[0]), "=r"(vn[1]), "=r"(vn[2]), "=r"(vn[3]), "=r"(vn[4]), "=r"(vn[5]), "=r"(vn[6]), "=r"(vn[7]),
+                  "=r"(vn[8]), "=r"(vn[9]), "=r"(vn[10]), "=r"(vn[11]), "=r"(vn[12]), "=r"(vn[13]), "=r"(vn[14]),
+                  "=r"(vn[15]), "=r"(vn[16]), "=r"(vn[17]), "=r"(vn[18]), "=r"(vn[19]), "=r"(vn[20]), "=r"(vn[21]),
+                  "=r"(vn[22]), "=r"(vn[23]), "=r"(vn[24]), "=r"(vn[25]), "=r"(vn[26]), "=r"(vn[27]), "=r"(vn[28]),
+                  "=r"(vn[29]), "=r"(vn[30]), "=r"(vn[31])
+                : "r"(tn) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row_live) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int cl = c0 + j;
+                    const int co = chunk * a.CB + cl;
+                    if (cl < a.CB && co < a.Co) {
+                        const int p = min((int)vp[j], a.cap), q = min((int)vn[j], a.cap);
+                        out[((size_t)n * a.Co + co) * ohw + (size_t)oh * a.OW + ow] = p - q;
+                    }
+                }
+            }
+        }
+    } else if (tid == 0) {
+        atomicExch(status, 3);
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)a.tmem_cols)
+                     : "memory");
+    }
+}
+
+// ---- operand preparation ------------------------------------------------------------------------------------
+__global__ void fxp_umma_pack_kernel(UmmaArgs a, int K, int KH, int KW, int n_chunks, const int32_t *__restrict__ qp,
+                                     const int32_t *__restrict__ qn, int8_t *__restrict__ wpk,
+                                     int32_t *__restrict__ koff)
+{
+    // weights: wpk[chunk][row n' in 0..NP)[k' in 0..Kp), row = sign * CBq + local channel
+    const long long total = (long long)n_chunks * a.NP * a.Kp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int kp = (int)(i % a.Kp);
+        const long long r = i / a.Kp;
+        const int row = (int)(r % a.NP);
+        const int chunk = (int)(r / a.NP);
+        const int sign = row >= a.CBq ? 1 : 0, cl = row - sign * a.CBq;
+        const int co = chunk * a.CB + cl;
+        int v = 0;
+        if (cl < a.CB && co < a.Co && kp < 2 * K) {
+            const int k = kp < K ? kp : kp - K;
+            v = sign ? qn[(long long)co * K + k] : qp[(long long)co * K + k];
+            if (kp >= K) v &= 1;
+        }
+        wpk[i] = (int8_t)v;
+    }
+    // k' -> offset of the activation element inside one image, relative to the tap (0,0) of the output pixel
+    for (int kp = blockIdx.x * blockDim.x + threadIdx.x; kp < a.Kp; kp += gridDim.x * blockDim.x) {
+        int off = -1;
+        if (kp < 2 * K) {
+            const int k = kp < K ? kp : kp - K;
+            const int ci = k / (KH * KW), r = k - ci * KH * KW, kh = r / KW, kw = r - kh * KW;
+            off = (ci * a.Hp + kh) * a.Wp + kw;
+            if (kp >= K) off |= 0x40000000;
+        }
+        koff[kp] = off;
+    }
+}
+
+__global__ void fxp_umma_act_kernel(long long total, const int32_t *__restrict__ q, int8_t *__restrict__ q8)
+{
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x)
+        q8[i] = (int8_t)q[i];
+}
+
+} // namespace
+
+size_t fxp_umma_workspace_bytes(int N, int C, int Hp, int Wp, int Co, long long K)
+{
+    const int CB = Co < 128 ? Co : 128;
+    const int n_chunks = (Co + CB - 1) / CB;
+    const long long Kp = (2 * K + kSlabBytes - 1) / kSlabBytes * kSlabBytes;
+    return align_up((size_t)N * C * Hp * Wp, 256) + align_up((size_t)n_chunks * 256 * Kp, 256) +
+           align_up((size_t)Kp * 4, 256);
+}
+
+bool fxp_umma_supported(int C, int Hp, int Wp, long long K)
+{
+    // the offset table keeps an in-image offset in 30 bits
+    return (long long)C * Hp * Wp < (1LL << 30) && 2 * K <= (1 << 20);
+}
+
+int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
+                         const int32_t *qa, const int32_t *qp, const int32_t *qn, void *ws, int32_t *out, int *status,
+                         cudaStream_t st)
+{
+    UmmaArgs a;
+    const long long K = (long long)C * KH * KW;
+    a.N = N; a.C = C; a.Hp = Hp; a.Wp = Wp; a.Co = Co; a.OH = OH; a.OW = OW; a.sh = sh; a.sw = sw;
+    a.Kp = (int)((2 * K + kSlabBytes - 1) / kSlabBytes * kSlabBytes);
+    a.CB = Co < 128 ? Co : 128;
+    a.CBp = (a.CB + 7) / 8 * 8;
+    a.CBq = (a.CBp + 31) / 32 * 32;
+    a.NP = (a.CBq + a.CBp + 15) / 16 * 16;
+    a.tmem_cols = 32;
+    while (a.tmem_cols < 2 * a.CBq) a.tmem_cols *= 2; // the epilogue reads whole 32-column groups of both blocks
+    if (a.tmem_cols > 512 || a.NP > 256) return REXSC_E_UNSUPPORTED;
+    a.cap = cap;
+    a.M = (long long)N * OH * OW;
+    const int n_chunks = (Co + a.CB - 1) / a.CB;
+    uint8_t *w8 = static_cast<uint8_t *>(ws);
+    int8_t *q8 = reinterpret_cast<int8_t *>(w8);
+    int8_t *wpk = reinterpret_cast<int8_t *>(w8 + align_up((size_t)N * C * Hp * Wp, 256));
+    int32_t *koff = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(wpk) +
+                                                align_up((size_t)n_chunks * a.NP * a.Kp, 256));
+    const long long n_act = (long long)N * C * Hp * Wp;
+    fxp_umma_act_kernel<<<(unsigned)((n_act + 255) / 256 < 148 * 16 ? (n_act + 255) / 256 : 148 * 16), 256, 0, st>>>(
+        n_act, qa, q8);
+    REXSC_LAUNCH_CHECK("fxp_umma_act_kernel");
+    fxp_umma_pack_kernel<<<148 * 4, 256, 0, st>>>(a, (int)K, KH, KW, n_chunks, qp, qn, wpk, koff);
+    REXSC_LAUNCH_CHECK("fxp_umma_pack_kernel");
+    const size_t smem = (size_t)kUmmaM * kSlabBytes + 256 * kSlabBytes + 64 + 1024;
+    REXSC_CUDA_CHECK(cudaFuncSetAttribute(fxp_conv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)((a.M + kUmmaM - 1) / kUmmaM), (unsigned)n_chunks);
+    fxp_conv_umma_kernel<<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
+    REXSC_LAUNCH_CHECK("fxp_conv_umma_kernel");
+    return REXSC_OK;
+}
+
+} // namespace rexsc

@@ -32,6 +32,11 @@ def _kernel() -> int:
     return getattr(_kernel_choice, "value", _lib.KERNEL_AUTO)
 
 
+def set_fxp_kernel(name: str) -> None:
+    """Force the FXP conv kernel family: "auto", "cuda" (dp4a / sequential) or "tensor" (tcgen05 int8)."""
+    _kernel_choice.fxp = {"auto": 0, "cuda": 1, "tensor": 2}[name]
+
+
 # ---- workspace: one growing byte buffer per (device, stream), owned by torch's caching allocator --------
 _workspaces: dict = {}
 
@@ -383,6 +388,7 @@ def conv2d_saturate_acc(input: torch.Tensor, weight: torch.Tensor, add_config: i
         d.stride_h, d.stride_w = int(stride[0]), int(stride[1])
         d.act_dtype, d.w_dtype = _DTYPES[x.dtype], _DTYPES[w.dtype]
         d.add_config, d.precision_in, d.precision_out = int(add_config), int(precision_in), int(precision_out)
+        d.kernel = getattr(_kernel_choice, "fxp", 0)
         nbytes = lib.rexsc_fxp_conv2d_workspace_size(C.byref(d))
         if nbytes == 0:
             raise ValueError("conv2d_saturate_acc: unsupported shape or configuration")

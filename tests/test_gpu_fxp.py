@@ -34,13 +34,34 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("kernel", ["cuda", "tensor"])
 @pytest.mark.parametrize("case", CASES)
-def test_parity_vs_oracle(ops, oracle, case):
+def test_parity_vs_oracle(ops, oracle, case, kernel):
     N, Cin, H, W, Cout, K, pad, stride, add, p_in, p_out, ws = case
+    closed_form = add == 0 and 2 * p_in <= p_out
+    if kernel == "tensor" and not closed_form:
+        pytest.skip("the tensor-core kernel only implements the closed form")
     x, w = conv_inputs(N, Cin, H, W, Cout, K, prec=7, seed=int(ws * 100) + Cin, wscale=ws)
     ref = oracle.conv2d_saturate(x, w, add, p_in, p_out, (pad, pad), (stride, stride), pad8=True)
-    y = ops.conv2d_saturate_acc(x.cuda(), w.cuda(), add, p_in, p_out, (pad, pad), (stride, stride))
+    ops.set_fxp_kernel(kernel)
+    try:
+        y = ops.conv2d_saturate_acc(x.cuda(), w.cuda(), add, p_in, p_out, (pad, pad), (stride, stride))
+    finally:
+        ops.set_fxp_kernel("auto")
     assert torch.equal(y.cpu(), ref), f"{case}: {(y.cpu() != ref).sum().item()} of {ref.numel()} differ"
+
+
+def test_tensor_core_kernel_wide_layers(ops, oracle):
+    """More output channels than one CTA chunk (128) and a dot product spanning many 128-byte slabs."""
+    for (N, Cin, H, Cout, K) in [(2, 24, 6, 200, 3), (1, 96, 5, 136, 3)]:
+        x, w = conv_inputs(N, Cin, H, H, Cout, K, prec=7, seed=Cout, wscale=0.2)
+        ref = oracle.conv2d_saturate(x, w, 0, 6, 24, (1, 1), (1, 1))
+        ops.set_fxp_kernel("tensor")
+        try:
+            y = ops.conv2d_saturate_acc(x.cuda(), w.cuda(), 0, 6, 24, (1, 1), (1, 1))
+        finally:
+            ops.set_fxp_kernel("auto")
+        assert torch.equal(y.cpu(), ref)
 
 
 def test_half_inputs_and_rounding_ties(ops, oracle):

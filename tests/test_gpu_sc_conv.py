@@ -34,7 +34,9 @@ def assert_same(ours, ref, what):
     rp, rn = ref
     assert p.dtype == torch.int16 and n.dtype == torch.int16
     assert p.shape == rp.shape
-    assert p.stride() == rp.stride(), f"{what}: memory format differs"
+    # same memory format (strides of size-1 dimensions are arbitrary, so compare the format predicates)
+    for fmt in (torch.contiguous_format, torch.channels_last):
+        assert p.is_contiguous(memory_format=fmt) == rp.is_contiguous(memory_format=fmt), f"{what}: memory format"
     assert torch.equal(p.cpu(), rp), f"{what}: pos differs ({(p.cpu() != rp).sum().item()} elements)"
     assert torch.equal(n.cpu(), rn), f"{what}: neg differs ({(n.cpu() != rn).sum().item()} elements)"
 
@@ -227,3 +229,40 @@ def test_full_size_properties(ops):
     # negating the weights swaps the two outputs
     ps, ns = ops.conv2d_generic_general_split_acc(x, -w, *args)
     assert torch.equal(ps, n1) and torch.equal(ns, p1)
+
+
+def test_randomised_shapes_tiled_and_direct_vs_oracle(ops, oracle):
+    """40 seeded random configurations (shape, stride, padding, stream length, OR-n, layout, generator)."""
+    import random
+
+    rng = random.Random(20241)
+    for trial in range(40):
+        K = rng.choice([1, 1, 3, 3, 3, 5])
+        KW = K if rng.random() < 0.8 else rng.choice([1, 2, 3])
+        stride = rng.choice([1, 1, 2, 3])
+        pad = rng.choice([0, 1, 2]) if K > 1 else 0
+        H = rng.randint(max(K, 3), 14)
+        W = rng.randint(max(KW, 3), 14)
+        N = rng.randint(1, 5)
+        Cin = rng.choice([1, 3, 8, 9, 16, 31, 40])
+        Cout = rng.choice([1, 5, 32, 33, 48])
+        L = rng.choice([8, 16, 32, 32, 64, 128])
+        or_n = rng.choice([1, 2, 2, 3, 4])
+        cl = rng.random() < 0.5
+        xnor = rng.random() < 0.6
+        if H + 2 * pad < K or W + 2 * pad < KW:
+            continue
+        x, w = conv_inputs(N, Cin, H, W, Cout, K, prec=7, seed=trial, KW=KW)
+        if cl:
+            x = x.contiguous(memory_format=torch.channels_last)
+            w = w.contiguous(memory_format=torch.channels_last)
+        ref = oracle.conv2d_generic_general_split(x, w, L, -1, 16, (pad, pad), (stride, stride), PROG, or_n - 1, 1,
+                                                  xnor, False)
+        for kernel in ("tiled", "direct"):
+            try:
+                ours = run_ours(ops, x, w, L, pad, stride, or_n, xnor, kernel)
+            except ValueError as exc:
+                if kernel == "tiled" and "UNSUPPORTED" in str(exc):
+                    continue  # patch does not fit the stage: the direct kernel covers the shape
+                raise
+            assert_same(ours, ref, f"trial {trial}: {(N, Cin, H, W, Cout, K, KW, pad, stride, L, or_n, cl, xnor)} {kernel}")
