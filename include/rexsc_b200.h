@@ -206,7 +206,8 @@ typedef struct rexsc_fxp_conv_desc {
     int32_t add_config;    /* 0 fixed-point add, 1 simulated OR add, >= 2 simulated OR-2 pairs */
     int32_t precision_in;  /* quantisation scale 2^precision_in                                */
     int32_t precision_out; /* accumulator precision                                            */
-    int32_t kernel;        /* 0 auto, 1 CUDA-core kernels only, 2 tensor-core (tcgen05 int8) closed form */
+    int32_t kernel;        /* 0 auto, 1 CUDA-core kernels only, 2 tensor-core (tcgen05 int8) closed form,
+                              3 the same with unswizzled shared-memory operand tiles               */
 } rexsc_fxp_conv_desc;
 size_t rexsc_fxp_conv2d_workspace_size(const rexsc_fxp_conv_desc *desc);
 int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void *d_act, const void *d_weight,

@@ -239,7 +239,7 @@ size_t fxp_umma_workspace_bytes(int N, int C, int Hp, int Wp, int Co, long long 
 bool fxp_umma_supported(int C, int Hp, int Wp, long long K);
 int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
                          const int32_t *qa, const int32_t *qp, const int32_t *qn, void *ws, int32_t *out, int *status,
-                         cudaStream_t st);
+                         bool swizzled, cudaStream_t st);
 
 struct FxpPlan {
     FxpArgs a;
@@ -284,9 +284,9 @@ static int make_fxp_plan(const rexsc_fxp_conv_desc *d, FxpPlan *p)
     p->cap = p->closed ? (1 << pm) : 0;
     p->Kw = (int)((a.K + 3) / 4);
     p->Cop = (a.Co + kFxpCo - 1) / kFxpCo * kFxpCo;
-    if (d->kernel < 0 || d->kernel > 2) return REXSC_E_BAD_ARG;
+    if (d->kernel < 0 || d->kernel > 3) return REXSC_E_BAD_ARG;
     p->umma = p->closed && d->kernel != 1 && fxp_umma_supported(a.C, a.Hp, a.Wp, a.K);
-    if (d->kernel == 2 && !p->umma) return REXSC_E_UNSUPPORTED;
+    if (d->kernel >= 2 && !p->umma) return REXSC_E_UNSUPPORTED;
     size_t off = 0;
     p->off_status = off; off += 256;
     p->off_qa = off; off += align_up((size_t)n_act * 4, 256);
@@ -344,7 +344,7 @@ extern "C" int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void 
     REXSC_LAUNCH_CHECK("fxp_quant_w_kernel");
     if (p.umma) {
         return launch_fxp_conv_umma(a.N, a.C, a.Hp, a.Wp, a.Co, a.KH, a.KW, a.OH, a.OW, a.sh, a.sw, p.cap, qa, qp, qn,
-                                    ws + p.off_umma, d_out, status, st);
+                                    ws + p.off_umma, d_out, status, desc->kernel != 3, st);
     }
     if (p.closed) {
         long long tot = (long long)p.Kw * p.Cop;

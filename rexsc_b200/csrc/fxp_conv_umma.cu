@@ -53,6 +53,20 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t saddr)
 // byte offset of 16-byte chunk `c` (0..7) of row `r` inside a [rows][128 B] tile with 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128_offset(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
+// Unswizzled ("interleaved") K-major alternative: the tile is stored as 16-byte K-columns, [chunk][row][16 B], so
+// every row of a K-column sits 16 bytes after the previous one (8-row core matrices back to back, stride byte
+// offset 128) and the next K-column starts `rows * 16` bytes later (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_k_interleaved(uint32_t saddr, uint32_t rows)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3fff);
+    d |= (uint64_t)(((rows * 16) >> 4) & 0x3fff) << 16; // leading byte offset: next 16-byte K-column
+    d |= (uint64_t)(128 >> 4) << 32;                    // stride byte offset: next 8-row core matrix
+    d |= (uint64_t)1 << 46;
+    return d;                                           // layout type 0: no swizzle
+}
+__device__ __forceinline__ uint32_t interleaved_offset(int r, int c, int rows) { return (uint32_t)((c * rows + r) * 16); }
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
     for (uint32_t i = 0; i < kUmmaWaitLimit; i++) {
@@ -67,6 +81,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
     return false;
 }
 
+template <bool SWIZZLED>
 __global__ void __launch_bounds__(128, 1)
 fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *__restrict__ wpk,
                      const int32_t *__restrict__ koff, int32_t *__restrict__ out, int *__restrict__ status)
@@ -130,13 +145,14 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
                     }
                 }
             }
-            *reinterpret_cast<uint4 *>(a_s + sw128_offset(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(a_s + (SWIZZLED ? sw128_offset(tid, c) : interleaved_offset(tid, c, kUmmaM))) =
+                make_uint4(w[0], w[1], w[2], w[3]);
         }
         // ---- B slab: NP rows x 8 chunks, straight copy of the prepacked weights ------------------------------
         for (int i = tid; i < a.NP * 8; i += blockDim.x) {
             const int r = i >> 3, c = i & 7;
             const uint4 v = __ldg(reinterpret_cast<const uint4 *>(wchunk + (size_t)r * a.Kp + slab * kSlabBytes) + c);
-            *reinterpret_cast<uint4 *>(b_s + sw128_offset(r, c)) = v;
+            *reinterpret_cast<uint4 *>(b_s + (SWIZZLED ? sw128_offset(r, c) : interleaved_offset(r, c, a.NP))) = v;
         }
         // generic-proxy writes must be visible to the tensor core's async-proxy reads
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -144,14 +160,15 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t da = umma_desc_k_sw128(smem_addr(a_s));
-            const uint64_t db = umma_desc_k_sw128(smem_addr(b_s));
+            const uint64_t da = SWIZZLED ? umma_desc_k_sw128(smem_addr(a_s)) : umma_desc_k_interleaved(smem_addr(a_s), kUmmaM);
+            const uint64_t db = SWIZZLED ? umma_desc_k_sw128(smem_addr(b_s)) : umma_desc_k_interleaved(smem_addr(b_s), a.NP);
 #pragma unroll
             for (int kk = 0; kk < kSlabBytes / kUmmaK; kk++) {
                 const uint32_t accumulate = (slab > 0 || kk > 0) ? 1u : 0u;
-                // advancing K inside the swizzle row: +32 bytes = +2 in the descriptor's 16-byte address units
-                const uint64_t dak = da + (uint64_t)(kk * (kUmmaK >> 4));
-                const uint64_t dbk = db + (uint64_t)(kk * (kUmmaK >> 4));
+                // advancing K by 32 bytes: +2 address units (16 B) inside a swizzle row, or two K-columns further
+                // in the interleaved layout
+                const uint64_t dak = da + (uint64_t)(SWIZZLED ? kk * (kUmmaK >> 4) : kk * 2 * (kUmmaM * 16 >> 4));
+                const uint64_t dbk = db + (uint64_t)(SWIZZLED ? kk * (kUmmaK >> 4) : kk * 2 * (a.NP * 16 >> 4));
                 asm volatile(
                     "{\n\t.reg .pred p;\n\t"
                     "setp.ne.b32 p, %4, 0;\n\t"
@@ -287,7 +304,7 @@ bool fxp_umma_supported(int C, int Hp, int Wp, long long K)
 
 int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
                          const int32_t *qa, const int32_t *qp, const int32_t *qn, void *ws, int32_t *out, int *status,
-                         cudaStream_t st)
+                         bool swizzled, cudaStream_t st)
 {
     UmmaArgs a;
     const long long K = (long long)C * KH * KW;
@@ -315,9 +332,16 @@ int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, i
     fxp_umma_pack_kernel<<<148 * 4, 256, 0, st>>>(a, (int)K, KH, KW, n_chunks, qp, qn, wpk, koff);
     REXSC_LAUNCH_CHECK("fxp_umma_pack_kernel");
     const size_t smem = (size_t)kUmmaM * kSlabBytes + 256 * kSlabBytes + 64 + 1024;
-    REXSC_CUDA_CHECK(cudaFuncSetAttribute(fxp_conv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)((a.M + kUmmaM - 1) / kUmmaM), (unsigned)n_chunks);
-    fxp_conv_umma_kernel<<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
+    if (swizzled) {
+        REXSC_CUDA_CHECK(cudaFuncSetAttribute(fxp_conv_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)smem));
+        fxp_conv_umma_kernel<true><<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
+    } else {
+        REXSC_CUDA_CHECK(cudaFuncSetAttribute(fxp_conv_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)smem));
+        fxp_conv_umma_kernel<false><<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
+    }
     REXSC_LAUNCH_CHECK("fxp_conv_umma_kernel");
     return REXSC_OK;
 }

@@ -34,7 +34,7 @@ def _kernel() -> int:
 
 def set_fxp_kernel(name: str) -> None:
     """Force the FXP conv kernel family: "auto", "cuda" (dp4a / sequential) or "tensor" (tcgen05 int8)."""
-    _kernel_choice.fxp = {"auto": 0, "cuda": 1, "tensor": 2}[name]
+    _kernel_choice.fxp = {"auto": 0, "cuda": 1, "tensor": 2, "tensor_unswizzled": 3}[name]
 
 
 # ---- workspace: one growing byte buffer per (device, stream), owned by torch's caching allocator --------

@@ -34,12 +34,12 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("kernel", ["cuda", "tensor"])
+@pytest.mark.parametrize("kernel", ["cuda", "tensor", "tensor_unswizzled"])
 @pytest.mark.parametrize("case", CASES)
 def test_parity_vs_oracle(ops, oracle, case, kernel):
     N, Cin, H, W, Cout, K, pad, stride, add, p_in, p_out, ws = case
     closed_form = add == 0 and 2 * p_in <= p_out
-    if kernel == "tensor" and not closed_form:
+    if kernel.startswith("tensor") and not closed_form:
         pytest.skip("the tensor-core kernel only implements the closed form")
     x, w = conv_inputs(N, Cin, H, W, Cout, K, prec=7, seed=int(ws * 100) + Cin, wscale=ws)
     ref = oracle.conv2d_saturate(x, w, add, p_in, p_out, (pad, pad), (stride, stride), pad8=True)

@@ -60,14 +60,11 @@ def test_sc_conv_matches_reference_gpu_kernels(ops, ref_gpu, case, xnor):
     assert torch.equal(p, rp) and torch.equal(n, rn), f"{case} xnor={xnor}"
 
 
-def test_sc_linear_matches_reference_gpu_kernels(ops, ref_gpu):
-    g = torch.Generator().manual_seed(3)
-    x = torch.rand(128, 512, generator=g).cuda()
-    w = (torch.randn(128, 512, generator=g) * 0.1).clamp(-1, 1).cuda()
-    rp, rn = ref_gpu[0].linear_generic_general_acc(x, w, PROG, 32, -1, 1, 1, True, False)
-    torch.cuda.synchronize()
-    p, n = ops.linear_generic_general_acc(x, w, PROG, 32, -1, 1, 1, True, False)
-    assert torch.equal(p, rp) and torch.equal(n, rn)
+# The reference's GPU *linear* op is not executed here: its translation unit keeps its own copy of the scratch
+# pointers but shares the "already allocated" flag with the conv unit (sc_device.cuh:711-714, sc_device.cu:3,
+# sc_cuda_matmul.cu:634-644), so calling it after a conv in the same process dereferences unallocated buffers.
+# SC linear parity is pinned by the reference CPU extension's vectors instead (tests/test_gpu_sc_conv.py), which
+# the reference's GPU generator equals by construction (both ignore xnor and seed by channel).
 
 
 @pytest.mark.parametrize("or_n", [1, 2, 3, 4])
