@@ -37,9 +37,11 @@ enum {
 
 enum { REXSC_F32 = 0, REXSC_F16 = 1, REXSC_BF16 = 2 };
 
-/* Which SC conv kernel to use.  AUTO picks the tiled shared-memory kernel when the shape fits it
- * and the direct kernel otherwise; both give identical results. */
-enum { REXSC_KERNEL_AUTO = 0, REXSC_KERNEL_DIRECT = 1, REXSC_KERNEL_TILED = 2 };
+/* Which SC conv kernel to use; all give identical results.  DIRECT: one thread per output, any shape and any n.
+ * TILED: shared-memory implicit GEMM on the integer ALU pipe (LOP3 thermometers).  TENSOR: one int8 tcgen05 GEMM
+ * per time slot with min(count, n) applied to the TMEM accumulators.  AUTO picks TILED when the shape fits it
+ * and DIRECT otherwise. */
+enum { REXSC_KERNEL_AUTO = 0, REXSC_KERNEL_DIRECT = 1, REXSC_KERNEL_TILED = 2, REXSC_KERNEL_TENSOR = 3 };
 
 /*
  * Shape / configuration of one SC conv2d (or, with h = w = kh = kw = 1, SC linear) forward.
@@ -81,9 +83,9 @@ const char *rexsc_last_cuda_error(void);
  *             either may alias nothing else; both are fully overwritten
  */
 size_t rexsc_sc_conv2d_workspace_size(const rexsc_sc_conv_desc *desc);
-/* Which kernel a forward call with this descriptor runs: REXSC_KERNEL_DIRECT or REXSC_KERNEL_TILED, or a
- * negative REXSC_E_* code (REXSC_E_UNSUPPORTED when desc->kernel forces the tiled kernel on a shape whose
- * activation patch does not fit its shared-memory stage).  Host-only, launches nothing. */
+/* Which kernel a forward call with this descriptor runs: REXSC_KERNEL_DIRECT, _TILED or _TENSOR, or a negative
+ * REXSC_E_* code (REXSC_E_UNSUPPORTED when desc->kernel forces a kernel the shape does not fit, e.g. a patch
+ * larger than the tiled kernel's shared-memory stage).  Host-only, launches nothing. */
 int rexsc_sc_conv2d_kernel_choice(const rexsc_sc_conv_desc *desc);
 int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                         int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes,

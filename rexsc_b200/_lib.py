@@ -14,7 +14,7 @@ ERRORS = {
     -5: "REXSC_E_CUDA", -6: "REXSC_E_DEVICE_TIMEOUT", -7: "REXSC_E_STATIC_SCRATCH",
 }
 F32, F16, BF16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_DIRECT, KERNEL_TILED = 0, 1, 2
+KERNEL_AUTO, KERNEL_DIRECT, KERNEL_TILED, KERNEL_TENSOR = 0, 1, 2, 3
 
 
 class ScConvDesc(C.Structure):

@@ -16,14 +16,27 @@ void set_cuda_error(cudaError_t e, const char *where)
 struct ConvBuffers {
     int *status;
     uint32_t *lut_a, *lut_w, *A, *Wt, *S;
+    void *tc;
 };
+
+// which accumulate kernel a descriptor resolves to (or a negative error)
+static int resolve_kernel(const rexsc_sc_conv_desc *desc, const ConvPlan &p)
+{
+    const bool tiled_ok = conv_tiled_supported(p);
+    switch (desc->kernel) {
+    case REXSC_KERNEL_DIRECT: return REXSC_KERNEL_DIRECT;
+    case REXSC_KERNEL_TILED: return tiled_ok ? REXSC_KERNEL_TILED : REXSC_E_UNSUPPORTED;
+    case REXSC_KERNEL_TENSOR: return p.tc_ok ? REXSC_KERNEL_TENSOR : REXSC_E_UNSUPPORTED;
+    default: return tiled_ok ? REXSC_KERNEL_TILED : REXSC_KERNEL_DIRECT;
+    }
+}
 
 static int conv_buffers(const rexsc_sc_conv_desc *desc, void *d_workspace, size_t workspace_bytes, ConvPlan *p,
                         ConvBuffers *b)
 {
     int rc = make_conv_plan(desc, p);
     if (rc != REXSC_OK) return rc;
-    if (desc->kernel < REXSC_KERNEL_AUTO || desc->kernel > REXSC_KERNEL_TILED) return REXSC_E_BAD_ARG;
+    if (desc->kernel < REXSC_KERNEL_AUTO || desc->kernel > REXSC_KERNEL_TENSOR) return REXSC_E_BAD_ARG;
     if (!d_workspace || workspace_bytes < p->total || (reinterpret_cast<uintptr_t>(d_workspace) & 255))
         return REXSC_E_WORKSPACE;
     uint8_t *ws = static_cast<uint8_t *>(d_workspace);
@@ -33,6 +46,7 @@ static int conv_buffers(const rexsc_sc_conv_desc *desc, void *d_workspace, size_
     b->A = reinterpret_cast<uint32_t *>(ws + p->off_A);
     b->Wt = reinterpret_cast<uint32_t *>(ws + p->off_Wt);
     b->S = reinterpret_cast<uint32_t *>(ws + p->off_S);
+    b->tc = ws + p->off_tc;
     return REXSC_OK;
 }
 
@@ -56,7 +70,12 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
     if (rc != REXSC_OK) return rc;
     rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
     if (rc != REXSC_OK) return rc;
-    return launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
+    rc = launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
+    if (rc != REXSC_OK) return rc;
+    const int k = resolve_kernel(desc, p);
+    if (k < 0) return k;
+    if (k == REXSC_KERNEL_TENSOR) return launch_tc_bitplanes(p, b.A, b.Wt, b.S, b.tc, st);
+    return REXSC_OK;
 }
 
 // stage 2: OR-n accumulation over the stream words of the workspace
@@ -68,9 +87,10 @@ static int conv_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, i
     int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
     if (rc != REXSC_OK) return rc;
     if (!d_out_pos || !d_out_neg) return REXSC_E_BAD_ARG;
-    const bool tiled_ok = conv_tiled_supported(p);
-    if (desc->kernel == REXSC_KERNEL_TILED && !tiled_ok) return REXSC_E_UNSUPPORTED;
-    if (desc->kernel != REXSC_KERNEL_DIRECT && tiled_ok)
+    const int k = resolve_kernel(desc, p);
+    if (k < 0) return k;
+    if (k == REXSC_KERNEL_TENSOR) return launch_conv_tc(p, *desc, b.tc, d_out_pos, d_out_neg, b.status, st);
+    if (k == REXSC_KERNEL_TILED)
         return launch_conv_tiled(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, b.status, st);
     return launch_conv_direct(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, st);
 }
@@ -124,9 +144,8 @@ extern "C" int rexsc_sc_conv2d_kernel_choice(const rexsc_sc_conv_desc *desc)
     ConvPlan p;
     int rc = make_conv_plan(desc, &p);
     if (rc != REXSC_OK) return rc;
-    const bool tiled_ok = conv_tiled_supported(p);
-    if (desc->kernel == REXSC_KERNEL_TILED && !tiled_ok) return REXSC_E_UNSUPPORTED;
-    return (desc->kernel != REXSC_KERNEL_DIRECT && tiled_ok) ? REXSC_KERNEL_TILED : REXSC_KERNEL_DIRECT;
+    if (desc->kernel < REXSC_KERNEL_AUTO || desc->kernel > REXSC_KERNEL_TENSOR) return REXSC_E_BAD_ARG;
+    return resolve_kernel(desc, p);
 }
 
 extern "C" int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,

@@ -68,7 +68,8 @@ struct ConvPlan {
     int NT;               // ceil(Co / kTileN)
     long long Kdot;       // C * KH * KW, length of the dot product
     // workspace layout (byte offsets)
-    size_t off_status, off_lut_a, off_lut_w, off_A, off_Wt, off_S, total;
+    size_t off_status, off_lut_a, off_lut_w, off_A, off_Wt, off_S, off_tc, total;
+    bool tc_ok;           // the tensor-core kernel can run this shape (its bit planes live at off_tc)
     // per-plane sizes in words
     long long a_plane_words; // Cpad * NHWp  (one stream-word plane of activations)
     long long w_plane_words; // NT * CCH * KHW * kChunkC * kTileN
@@ -113,6 +114,13 @@ static inline long long patch_bound_words(long long BM, long long M, int OW, int
 // pad + quantise + stream generation + OR-n accumulation with the scratch at d_workspace (capi.cu)
 int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
                  int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st);
+
+bool conv_tc_supported(const ConvPlan &p);
+size_t conv_tc_workspace_bytes(const ConvPlan &p);
+int launch_tc_bitplanes(const ConvPlan &p, const uint32_t *d_A, const uint32_t *d_Wt, const uint32_t *d_S,
+                        void *d_tc_ws, cudaStream_t st);
+int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,
+                   int *d_status, cudaStream_t st);
 
 // ---- device helpers -----------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float load_as_float(const T *p, long long i);

@@ -234,6 +234,9 @@ static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
     p->off_A = off; off += align_up((size_t)p->words * p->a_plane_words * sizeof(uint32_t), 256);
     p->off_Wt = off; off += align_up((size_t)p->words * p->w_plane_words * sizeof(uint32_t), 256);
     p->off_S = off; off += align_up((size_t)p->NT * p->CCH * p->KHW * (kTileN / kWarpN) * sizeof(uint32_t), 256);
+    p->off_tc = off;
+    p->tc_ok = conv_tc_supported(*p);
+    if (p->tc_ok) off += conv_tc_workspace_bytes(*p);
     p->total = off;
     return REXSC_OK;
 }

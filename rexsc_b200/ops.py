@@ -24,8 +24,9 @@ _kernel_choice = threading.local()
 
 
 def set_conv_kernel(name: str) -> None:
-    """Force the SC conv kernel ("auto", "direct" or "tiled"); results are identical, only speed differs."""
-    _kernel_choice.value = {"auto": _lib.KERNEL_AUTO, "direct": _lib.KERNEL_DIRECT, "tiled": _lib.KERNEL_TILED}[name]
+    """Force the SC conv kernel ("auto", "direct", "tiled" or "tensor"); results are identical, only speed differs."""
+    _kernel_choice.value = {"auto": _lib.KERNEL_AUTO, "direct": _lib.KERNEL_DIRECT, "tiled": _lib.KERNEL_TILED,
+                            "tensor": _lib.KERNEL_TENSOR}[name]
 
 
 def _kernel() -> int:

@@ -41,19 +41,33 @@ def assert_same(ours, ref, what):
     assert torch.equal(n.cpu(), rn), f"{what}: neg differs ({(n.cpu() != rn).sum().item()} elements)"
 
 
-@pytest.mark.parametrize("kernel", ["direct", "tiled"])
+def _run_or_skip_unsupported(fn, kernel):
+    """Forcing a kernel on a shape it does not cover is refused with REXSC_E_UNSUPPORTED (ValueError)."""
+    try:
+        return fn()
+    except ValueError as exc:
+        if kernel in ("tiled", "tensor") and "UNSUPPORTED" in str(exc):
+            return None
+        raise
+
+
+@pytest.mark.parametrize("kernel", ["direct", "tiled", "tensor"])
 def test_golden_reference_cpu_vectors(ops, kernel):
     """xnor=False: pos - neg must equal what the reference's CPU extension returned."""
     g = load_golden("sc_conv_ref_cpu.npz")
     for name in golden_cases(g):
         N, Cin, H, W, Cout, K, pad, stride, L, or_n, cl = (int(v) for v in g[name + "/args"])
         if kernel == "tiled" and or_n > 4:
-            continue  # plain-count / large-n accumulation only exists in the direct kernel
+            continue  # plain-count / large-n accumulation is not in the ALU tiled kernel
         x, w = from128(g[name + "/x128"]), from128(g[name + "/w128"])
         if cl:
             x = x.contiguous(memory_format=torch.channels_last)
             w = w.contiguous(memory_format=torch.channels_last)
-        p, n = run_ours(ops, x, w, L, pad, stride, or_n, False, kernel)
+        res = _run_or_skip_unsupported(lambda: run_ours(ops, x, w, L, pad, stride, or_n, False, kernel), kernel)
+        if res is None:
+            assert kernel == "tensor" and K > 3   # only filters larger than 3x3 are outside the tensor kernel
+            continue
+        p, n = res
         y = (p - n).contiguous().cpu().numpy()
         assert int(y.astype(np.int64).sum()) == int(g[name + "/sum"][0]), name
         if name + "/y" in g.files:
@@ -79,10 +93,12 @@ CASES = [
 
 
 @pytest.mark.parametrize("xnor", [False, True])
-@pytest.mark.parametrize("kernel", ["direct", "tiled"])
+@pytest.mark.parametrize("kernel", ["direct", "tiled", "tensor"])
 @pytest.mark.parametrize("case", CASES)
 def test_parity_vs_oracle(ops, oracle, case, kernel, xnor):
     N, Cin, H, W, Cout, K, pad, stride, L, or_n, cl = case
+    if kernel == "tensor" and K > 3:
+        pytest.skip("the tensor-core kernel stages at most 9 filter taps")
     x, w = conv_inputs(N, Cin, H, W, Cout, K, prec=7, seed=hash(case) % 1000)
     if cl:
         x = x.contiguous(memory_format=torch.channels_last)
@@ -123,12 +139,13 @@ def test_combined_output_op(ops, oracle):
     assert y.dtype == torch.int16 and torch.equal(y.cpu(), ref[0] - ref[1])
 
 
+@pytest.mark.parametrize("kernel", ["auto", "tensor"])
 @pytest.mark.parametrize("or_n", [7, 51201])
-def test_large_n_and_plain_count(ops, oracle, or_n):
+def test_large_n_and_plain_count(ops, oracle, or_n, kernel):
     x, w = conv_inputs(1, 40, 6, 6, 9, 3, prec=5, seed=7)
     ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (1, 1), (1, 1), PROG, or_n - 1, 1, True, False)
-    ours = run_ours(ops, x, w, 32, 1, 1, or_n, True)
-    assert_same(ours, ref, f"or_n={or_n}")
+    ours = run_ours(ops, x, w, 32, 1, 1, or_n, True, kernel)
+    assert_same(ours, ref, f"or_n={or_n} {kernel}")
 
 
 def test_generator_options(ops, oracle):
@@ -137,7 +154,7 @@ def test_generator_options(ops, oracle):
     for gen, prog, lfsr, L in [(2, PROG, -1, 32), (1, (7, 2, 4), -1, 32), (1, PROG, 7, 32), (3, (7, 3, 2), -1, 16)]:
         for xnor in (False, True):
             ref = oracle.conv2d_generic_general_split(x, w, L, lfsr, 16, (1, 1), (1, 1), prog, 1, gen, xnor, False)
-            for kernel in ("direct", "tiled"):
+            for kernel in ("direct", "tiled", "tensor"):
                 ours = run_ours(ops, x, w, L, 1, 1, 2, xnor, kernel, gen=gen, prog=prog, lfsr=lfsr)
                 assert_same(ours, ref, f"gen={gen} prog={prog} lfsr={lfsr} {kernel} xnor={xnor}")
 
@@ -216,10 +233,13 @@ def test_full_size_properties(ops):
     p2, n2 = ops.conv2d_generic_general_split_acc(x, w, *args)
     ops.set_conv_kernel("direct")
     p3, n3 = ops.conv2d_generic_general_split_acc(x, w, *args)
+    ops.set_conv_kernel("tensor")
+    p4, n4 = ops.conv2d_generic_general_split_acc(x, w, *args)
     ops.set_conv_kernel("auto")
     assert ops.workspace_status() == 0
     assert torch.equal(p1, p2) and torch.equal(n1, n2)
     assert torch.equal(p1, p3) and torch.equal(n1, n3)
+    assert torch.equal(p1, p4) and torch.equal(n1, n4)
     assert int(p1.min()) >= 0 and int(p1.max()) <= 64 and int(n1.min()) >= 0 and int(n1.max()) <= 64
     pz, nz = ops.conv2d_generic_general_split_acc(x, torch.zeros_like(w), *args)
     assert int(pz.abs().max()) == 0 and int(nz.abs().max()) == 0
@@ -258,11 +278,8 @@ def test_randomised_shapes_tiled_and_direct_vs_oracle(ops, oracle):
             w = w.contiguous(memory_format=torch.channels_last)
         ref = oracle.conv2d_generic_general_split(x, w, L, -1, 16, (pad, pad), (stride, stride), PROG, or_n - 1, 1,
                                                   xnor, False)
-        for kernel in ("tiled", "direct"):
-            try:
-                ours = run_ours(ops, x, w, L, pad, stride, or_n, xnor, kernel)
-            except ValueError as exc:
-                if kernel == "tiled" and "UNSUPPORTED" in str(exc):
-                    continue  # patch does not fit the stage: the direct kernel covers the shape
-                raise
+        for kernel in ("tiled", "tensor", "direct"):
+            ours = _run_or_skip_unsupported(lambda: run_ours(ops, x, w, L, pad, stride, or_n, xnor, kernel), kernel)
+            if ours is None:
+                continue  # shape outside that kernel: the direct kernel covers it
             assert_same(ours, ref, f"trial {trial}: {(N, Cin, H, W, Cout, K, KW, pad, stride, L, or_n, cl, xnor)} {kernel}")
