@@ -26,7 +26,8 @@ namespace rexsc {
 namespace {
 
 constexpr int kTcThreads = 256;
-constexpr int kTcM = 128;          // stored-grid positions per CTA = TMEM lanes
+constexpr int kTcM = 256;          // stored-grid positions per CTA: two MMA row blocks that share one weight operand
+constexpr int kTcSub = 128;        // rows of one MMA (TMEM lanes)
 constexpr int kTcCout = 64;        // output channels per CTA
 constexpr int kTcN = 2 * kTcCout;  // MMA N: positive block [0,64), negative block [64,128)
 constexpr int kTcMaxTaps = 9;      // filter taps whose weight operand is staged at once
@@ -92,6 +93,17 @@ __device__ __forceinline__ uint4 spread16(uint32_t h)
         : "r"(taddr)                                                                                                  \
         : "memory")
 
+// 32 TMEM columns as 16 registers: the low 16 bits of two adjacent columns per register
+#define REXSC_TMEM_LD16_PACKED(arr, taddr)                                                                            \
+    asm volatile(                                                                                                     \
+        "tcgen05.ld.sync.aligned.32x32b.x16.pack::16b.b32 "                                                           \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                              \
+        : "=r"(arr[0]), "=r"(arr[1]), "=r"(arr[2]), "=r"(arr[3]), "=r"(arr[4]), "=r"(arr[5]), "=r"(arr[6]),           \
+          "=r"(arr[7]), "=r"(arr[8]), "=r"(arr[9]), "=r"(arr[10]), "=r"(arr[11]), "=r"(arr[12]), "=r"(arr[13]),       \
+          "=r"(arr[14]), "=r"(arr[15])                                                                                \
+        : "r"(taddr)                                                                                                  \
+        : "memory")
+
 __global__ void __launch_bounds__(kTcThreads, 2)
 sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__restrict__ Wb,
                   int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status)
@@ -127,16 +139,18 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const uint32_t tmem_base = *tmem_slot;
 
     // instruction descriptor: int32 accumulators, signed int8 operands, both K-major, N = 128, M = 128
-    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcN >> 3) << 17) | ((uint32_t)(kTcM >> 4) << 24);
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcN >> 3) << 17) | ((uint32_t)(kTcSub >> 4) << 24);
     const uint32_t a_lbo = (uint32_t)a.rows_a * 16, b_lbo = kTcN * 16;
     const int wrow_words = a.KHW * a.CW;               // words per weight row and slot
     const uint32_t *Wchunk = Wb + (size_t)nc * a.slots * kTcN * wrow_words;
 
-    // running sums: this thread owns TMEM lane 32*(warp%4)+lane and columns 64*(warp/4) .. +63, two per register
-    uint32_t acc[32];
+    // running sums: this thread owns row block warp/4, TMEM lane 32*(warp%4)+lane and all 128 columns of that block,
+    // two 16-bit sums per register (column pairs as the packed TMEM load delivers them)
+    uint32_t acc[64];
 #pragma unroll
-    for (int j = 0; j < 32; j++) acc[j] = 0u;
-    const uint32_t my_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * 64);
+    for (int j = 0; j < 64; j++) acc[j] = 0u;
+    const uint32_t my_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * kTcN);
+    const uint32_t n2 = (uint32_t)a.n_or | ((uint32_t)a.n_or << 16);
 
     // Bit words of one pipeline step (slot, 64-channel chunk) are fetched into registers one step ahead, so
     // that their L2 latency hides behind the previous step's MMAs.
@@ -184,24 +198,22 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             }
         }
     };
-    // count -> min(count, n) -> running sums, for the slot whose accumulators sit in TMEM buffer `buf`
-    auto slot_epilogue = [&](int buf) {
+    // count -> min(count, n) -> running sums for the slot whose accumulators are complete in TMEM
+    auto slot_epilogue = [&]() {
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            uint32_t v[32];
-            REXSC_TMEM_LD32(v, my_taddr + (uint32_t)(buf * kTcN + half * 32));
+        for (int g = 0; g < 4; g++) {
+            uint32_t v[16];
+            REXSC_TMEM_LD16_PACKED(v, my_taddr + (uint32_t)(g * 32));
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                const uint32_t lo = min(v[j], (uint32_t)a.n_or), hi = min(v[j + 1], (uint32_t)a.n_or);
-                acc[half * 16 + (j >> 1)] += lo + (hi << 16);
-            }
+            for (int j = 0; j < 16; j++) acc[g * 16 + j] += __vminu2(v[j], n2);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
 
     bool failed = false;
     const int n_steps = a.slots * a.CK;
+    const uint64_t da0 = desc_interleaved(saddr(a_s), a_lbo), db0 = desc_interleaved(saddr(b_s), b_lbo);
     load_bits(0);
     for (int step = 0; step < n_steps; step++) {
         const int s = step / a.CK, ck = step - s * a.CK;
@@ -211,39 +223,42 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         __syncthreads();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = saddr(a_s), b_addr = saddr(b_s);
-            const uint32_t d_addr = tmem_base + (uint32_t)((s & 1) * kTcN); // accumulators alternate between two buffers
-            for (int tap = 0; tap < a.KHW; tap++) {
+            // the start-address field counts 16-byte units from bit 0, i.e. operand rows: moving an operand by
+            // rows / K-columns is an integer add on the descriptor
 #pragma unroll
-                for (int kk = 0; kk < 2; kk++) {
-                    if (2 * ck + kk >= a.CW) break; // no channels in this half of the chunk
-                    const uint64_t da = desc_interleaved(a_addr + (uint32_t)(2 * kk) * a_lbo + (uint32_t)tap_s[tap] * 16, a_lbo);
-                    const uint64_t db = desc_interleaved(b_addr + (uint32_t)(tap * 4 + 2 * kk) * b_lbo, b_lbo);
-                    const uint32_t accumulate = (ck > 0 || tap > 0 || kk > 0) ? 1u : 0u;
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\t"
-                        "setp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                        ::"r"(d_addr), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
-                        : "memory");
+            for (int sub = 0; sub < kTcM / kTcSub; sub++) {
+                const uint32_t d_addr = tmem_base + (uint32_t)(sub * kTcN);
+                for (int tap = 0; tap < a.KHW; tap++) {
+#pragma unroll
+                    for (int kk = 0; kk < 2; kk++) {
+                        if (2 * ck + kk >= a.CW) break; // no channels in this half of the chunk
+                        const uint64_t da = da0 + (uint64_t)(uint32_t)(sub * kTcSub + tap_s[tap] + 2 * kk * a.rows_a);
+                        const uint64_t db = db0 + (uint64_t)(uint32_t)((tap * 4 + 2 * kk) * kTcN);
+                        const uint32_t accumulate = (ck > 0 || tap > 0 || kk > 0) ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\t"
+                            "setp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                            ::"r"(d_addr), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+                            : "memory");
+                    }
                 }
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar))
                          : "memory");
         }
-        // while the tensor core works: fetch the next step's bits and fold the previous slot's counts
+        // while the tensor core works: fetch the next step's bits
         if (step + 1 < n_steps) load_bits(step + 1);
-        if (ck == 0 && s > 0) slot_epilogue((s - 1) & 1);
         if (!tc_wait(saddr(bar), (uint32_t)(step & 1))) failed = true;
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (failed) break;
+        if (ck == a.CK - 1) slot_epilogue(); // the next slot's first MMA comes after the next barrier
     }
-    if (!failed) slot_epilogue((a.slots - 1) & 1);
 
     if (!failed) {
         // ---- store: row = one stored-grid position; it is an output pixel iff it is the tap-(0,0) origin of one ----
-        const long long q = q0 + (warp & 3) * 32 + lane;
+        const long long q = q0 + (warp >> 2) * kTcSub + (warp & 3) * 32 + lane;
         if (q < a.NHW) {
             const int colp = (int)(q % a.Wrow);
             const long long t = q / a.Wrow;
@@ -251,27 +266,32 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             const long long n = t / a.Hrows;
             const int oh = rowp / a.nrh;
             if (colp < a.OW && rowp % a.nrh == 0 && oh < a.OH) {
-                int16_t *dst = (warp >> 2) ? out_neg : out_pos;
                 const int co0 = nc * kTcCout;
                 const size_t ohw = (size_t)a.OH * a.OW;
                 const size_t m = ((size_t)n * a.OH + oh) * a.OW + colp;
-                if (a.out_nhwc) {
-                    int16_t *row = dst + m * a.Co + co0;
-                    if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
+                // acc[0..31] = positive block (columns 0..63), acc[32..63] = negative block
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4 *>(row + 2 * j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                for (int sign = 0; sign < 2; sign++) {
+                    int16_t *dst = sign ? out_neg : out_pos;
+                    const uint32_t *av = acc + sign * 32;
+                    if (a.out_nhwc) {
+                        int16_t *row = dst + m * a.Co + co0;
+                        if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<uint4 *>(row + 2 * j) = make_uint4(av[j], av[j + 1], av[j + 2], av[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 64; j++)
+                                if (co0 + j < a.Co) row[j] = (int16_t)((av[j >> 1] >> (16 * (j & 1))) & 0xffffu);
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 64; j++)
-                            if (co0 + j < a.Co) row[j] = (int16_t)((acc[j >> 1] >> (16 * (j & 1))) & 0xffffu);
+                            if (co0 + j < a.Co)
+                                dst[((size_t)n * a.Co + co0 + j) * ohw + (size_t)oh * a.OW + colp] =
+                                    (int16_t)((av[j >> 1] >> (16 * (j & 1))) & 0xffffu);
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 64; j++)
-                        if (co0 + j < a.Co)
-                            dst[((size_t)n * a.Co + co0 + j) * ohw + (size_t)oh * a.OW + colp] =
-                                (int16_t)((acc[j >> 1] >> (16 * (j & 1))) & 0xffffu);
                 }
             }
         }
