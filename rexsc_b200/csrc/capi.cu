@@ -25,9 +25,14 @@ static int resolve_kernel(const rexsc_sc_conv_desc *desc, const ConvPlan &p)
     const bool tiled_ok = conv_tiled_supported(p);
     switch (desc->kernel) {
     case REXSC_KERNEL_DIRECT: return REXSC_KERNEL_DIRECT;
-    case REXSC_KERNEL_TILED: return tiled_ok ? REXSC_KERNEL_TILED : REXSC_E_UNSUPPORTED;
-    case REXSC_KERNEL_TENSOR: return p.tc_ok ? REXSC_KERNEL_TENSOR : REXSC_E_UNSUPPORTED;
-    default: return tiled_ok ? REXSC_KERNEL_TILED : REXSC_KERNEL_DIRECT;
+    case REXSC_KERNEL_TILED: return tiled_ok ? (int)REXSC_KERNEL_TILED : (int)REXSC_E_UNSUPPORTED;
+    case REXSC_KERNEL_TENSOR: return p.tc_ok ? (int)REXSC_KERNEL_TENSOR : (int)REXSC_E_UNSUPPORTED;
+    default:
+        // AUTO: the tensor-core kernel wins where its row space is dense (stride 1, or 1x1 filters whose input is
+        // stored subsampled) and the dot product fills its 64-channel K chunks; strided 3x3 layers keep the ALU
+        // kernel, which skips the pixels a stride jumps over.
+        if (p.tc_ok && p.C >= 32 && ((p.sh == 1 && p.sw == 1) || p.KHW == 1)) return REXSC_KERNEL_TENSOR;
+        return tiled_ok ? (int)REXSC_KERNEL_TILED : (int)REXSC_KERNEL_DIRECT;
     }
 }
 
