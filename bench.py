@@ -151,10 +151,21 @@ def run_ours(args, rank, world, local_rank):
     launches = {"n": 0}
 
     def conv(l, x):
-        launches["n"] += 5  # 2 LUT builds, activation expand, weight expand, tiled accumulate
+        launches["n"] += l.get("kernels_per_call", 5)  # LUT builds, expands, (bit planes,) accumulate
         return ops.conv2d_generic_general_split_acc(x, l["w"], BIT_LENGTH, -1, 16, (0, 0), (l["stride"],) * 2, PROG,
                                                     OR_N - 1, 1, True, False)
 
+    import ctypes as C0
+    for l in layers:
+        d0 = _lib.ScConvDesc()
+        d0.batch, d0.c_in, d0.h_in, d0.w_in = l["x"].shape
+        d0.c_out, _, d0.kh, d0.kw = l["w"].shape
+        d0.stride_h = d0.stride_w = l["stride"]
+        d0.act_channels_last = d0.w_channels_last = d0.out_channels_last = 1
+        d0.bit_length, d0.lfsr_length, d0.bin_config, d0.gen_config, d0.xnor = BIT_LENGTH, -1, OR_N - 1, 1, 1
+        d0.prog_total_width, d0.prog_load_width, d0.prog_load_wait = PROG
+        # tensor-core path: 2 LUT builds, 2 expands, 2 bit-plane kernels, 1 MMA kernel; ALU paths: 2 + 2 + 1
+        l["kernels_per_call"] = 7 if lib.rexsc_sc_conv2d_kernel_choice(C0.byref(d0)) == 3 else 5
     guides = {}
     for i, l in enumerate(layers):
         p, n = conv(l, l["x"])
@@ -191,7 +202,7 @@ def run_ours(args, rank, world, local_rank):
     def step_e2e():
         # host buffers in, host buffers out: H2D / compute / D2H of consecutive calls overlap on three streams
         pipe.run(host_calls)
-        launches["n"] += 5 * len(host_calls)
+        launches["n"] += sum(l["kernels_per_call"] * l["rep"] for l in layers)
         for i, l in enumerate(layers):
             for _ in range(l["rep"]):
                 ops.or_approx_n_forward_acc(guides[i], OR_N)
@@ -225,10 +236,10 @@ def run_ours(args, rank, world, local_rank):
     ms_e2e, _ = timed(step_e2e, max(1, min(args.steps, 5)), 1)
     e2e_steps = max(1, min(args.steps, 5))
 
-    # ---- dominant kernel: tiled SC conv accumulate, timed alone per layer with CUDA events -----------------
+    # ---- accumulate kernels timed alone per layer with CUDA events (same stream, after the layer's expand stage) ----
     import ctypes as C
-    acc_ms = 0.0
-    acc_products = 0
+    per_kernel = {"tensor": {"ms": 0.0, "products": 0, "launches": 0}, "tiled": {"ms": 0.0, "products": 0, "launches": 0},
+                  "direct": {"ms": 0.0, "products": 0, "launches": 0}}
     exp_ms = 0.0
     for l in layers:
         x, w = l["x"], l["w"]
@@ -239,6 +250,7 @@ def run_ours(args, rank, world, local_rank):
         d.act_dtype, d.act_channels_last, d.w_dtype, d.w_channels_last, d.out_channels_last = 0, 1, 0, 1, 1
         d.bit_length, d.lfsr_length, d.bin_config, d.gen_config, d.xnor = BIT_LENGTH, -1, OR_N - 1, 1, 1
         d.prog_total_width, d.prog_load_width, d.prog_load_wait = PROG
+        which_kernel = {1: "direct", 2: "tiled", 3: "tensor"}[lib.rexsc_sc_conv2d_kernel_choice(C.byref(d))]
         nbytes = lib.rexsc_sc_conv2d_workspace_size(C.byref(d))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         oh = (d.h_in - d.kh) // d.stride_h + 1
@@ -264,10 +276,25 @@ def run_ours(args, rank, world, local_rank):
             if which == "expand":
                 exp_ms += best * l["rep"]
             else:
-                acc_ms += best * l["rep"]
-        o = oh
-        acc_products += l["rep"] * BATCH * o * o * d.c_out * d.c_in * d.kh * d.kw
+                k = per_kernel[which_kernel]
+                k["ms"] += best * l["rep"]
+                k["products"] += l["rep"] * BATCH * oh * oh * d.c_out * d.c_in * d.kh * d.kw
+                k["launches"] += l["rep"]
         del ws, pos, neg
+
+    # ---- live int8 tensor-pipe peak (back-to-back tcgen05 MMAs on fixed operands) ------------------------------
+    ops.mma_probe(296, 100, 128, dev)
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.mma_probe(296, 4000, 128, dev)
+        e1.record()
+        torch.cuda.synchronize()
+        t = e0.elapsed_time(e1)
+        best = t if best is None else min(best, t)
+    mma_peak_ops = 2.0 * 296 * 4000 * 16 * 128 * 128 * 32 / (best * 1e-3)  # int8 ops / s (2 per multiply-accumulate)
 
     # ---- live LOP3 peak (register-only probe) ------------------------------------------------------------
     blocks, iters = 148 * 8, 20000
@@ -300,8 +327,8 @@ def run_ours(args, rank, world, local_rank):
 
     return {
         "ms": ms, "launches": n_launch, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "h2d": h2d, "d2h": d2h,
-        "clocks": clocks, "acc_ms": acc_ms, "acc_products": acc_products, "exp_ms": exp_ms, "lop3_peak": lop3_peak,
-        "pw_gbs": pw_gbs,
+        "clocks": clocks, "per_kernel": per_kernel, "exp_ms": exp_ms, "lop3_peak": lop3_peak,
+        "mma_peak_ops": mma_peak_ops, "pw_gbs": pw_gbs,
     }
 
 
@@ -428,13 +455,38 @@ def main():
         imgs = BATCH * world * args.steps
         value = imgs / (r["ms"] * 1e-3)
         e2e_value = BATCH * world * r["e2e_steps"] / (r["ms_e2e"] * 1e-3)
-        lop3_per_product = 3  # OR-2 thermometer on the non-zero weight stream: x = a&w, T2 |= T1&x, T1 |= x
-        achieved = r["acc_products"] * lop3_per_product / (r["acc_ms"] * 1e-3)
+        pk = r["per_kernel"]
+        # tensor-core kernel: algorithmic int8 ops = 2 (multiply, add) x slots x valid output pixels x 2*Cout (positive
+        # and negative weight stream) x Cin*KH*KW  ==  4 x slots x products
+        tc_ops = 4.0 * BIT_LENGTH * pk["tensor"]["products"]
+        tc_achieved = tc_ops / (pk["tensor"]["ms"] * 1e-3) if pk["tensor"]["ms"] > 0 else 0.0
+        # ALU kernel: issued LOP3 lane-ops = 3 per word-product (OR-2 thermometer on the non-zero weight stream)
+        alu_achieved = pk["tiled"]["products"] * 3 / (pk["tiled"]["ms"] * 1e-3) if pk["tiled"]["ms"] > 0 else 0.0
+        roof_tensor = {
+            "bound": "tensor", "kernel": "sc_conv_tc_kernel (tcgen05 int8, one GEMM per time slot)",
+            "achieved": tc_achieved / 1e12, "peak": r["mma_peak_ops"] / 1e12, "unit": "TOP/s int8",
+            "frac": tc_achieved / r["mma_peak_ops"], "traffic": None,
+            "peak_source": "measured live: back-to-back tcgen05.mma kind::i8 M128 N128 K32 probe on this GPU",
+            "kernel_ms_per_step": pk["tensor"]["ms"], "launches_per_step": pk["tensor"]["launches"],
+            "tbitops_per_s_kernel": 64 * pk["tensor"]["products"] / (pk["tensor"]["ms"] * 1e-3) / 1e12
+            if pk["tensor"]["ms"] > 0 else 0.0,
+        }
+        roof_alu = {
+            "bound": "alu", "kernel": "sc_conv_tiled_kernel (LOP3 thermometer OR-n, strided 3x3 layers)",
+            "achieved": alu_achieved / 1e12, "peak": r["lop3_peak"] / 1e12, "unit": "T lane-LOP3/s",
+            "frac": alu_achieved / r["lop3_peak"], "traffic": None,
+            "peak_source": "measured live: register-only LOP3 probe on this GPU (integer ALU pipe)",
+            "kernel_ms_per_step": pk["tiled"]["ms"], "launches_per_step": pk["tiled"]["launches"],
+            "tbitops_per_s_kernel": 64 * pk["tiled"]["products"] / (pk["tiled"]["ms"] * 1e-3) / 1e12
+            if pk["tiled"]["ms"] > 0 else 0.0,
+        }
+        dominant, secondary = (roof_tensor, roof_alu) if pk["tensor"]["ms"] >= pk["tiled"]["ms"] else (roof_alu, roof_tensor)
+        dominant["expand_ms_per_step"] = r["exp_ms"]
         line = {
             "metric": "sc_resnet18_or2_L32_sc_forward_img_per_s", "value": value, "unit": "img/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms"] / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u32 bit-streams / int16", "data": "synthetic",
+            "dtype": "u32 bit-streams / int8 0-1 operands / int16", "data": "synthetic",
             "config": {
                 "workload": "SC ResNet-18 224x224 channels_last OR-2 L=32 batch 256/GPU: 19 SC conv2d forwards "
                             "(fp32 padded activations in, int16 pos/neg out) + 38 OR-n activation forwards (fp16 in)",
@@ -446,14 +498,8 @@ def main():
                     "d2h_bytes_per_step": r["d2h"]},
             "gpu_launches": r["launches"],
             "clocks": r["clocks"],
-            "roofline": {
-                "bound": "alu", "kernel": "sc_conv_tiled_kernel (OR-n accumulate, all 19 layers)",
-                "achieved": achieved / 1e12, "peak": r["lop3_peak"] / 1e12, "unit": "T lane-LOP3/s",
-                "frac": achieved / r["lop3_peak"], "traffic": None,
-                "peak_source": "measured live: register-only LOP3 probe on this GPU (integer ALU pipe)",
-                "kernel_ms_per_step": r["acc_ms"], "expand_ms_per_step": r["exp_ms"],
-                "tbitops_per_s_kernel": 64 * r["acc_products"] / (r["acc_ms"] * 1e-3) / 1e12,
-            },
+            "roofline": dominant,
+            "roofline_secondary": secondary,
             "roofline_pointwise": {
                 "bound": "hbm", "kernel": "pw_kernel<OrnFwd<half,2>>", "achieved": r["pw_gbs"], "unit": "GB/s",
                 "peak": _hbm_peak(), "frac": r["pw_gbs"] / _hbm_peak(), "peak_source": _hbm_peak_source(),

@@ -58,6 +58,7 @@ SYMBOLS = {
     "rexsc_fxp_conv2d_workspace_size": (_sz, [C.POINTER(FxpConvDesc)]),
     "rexsc_fxp_conv2d_fwd": (C.c_int, [C.POINTER(FxpConvDesc), _vp, _vp, _vp, _vp, _sz, _vp]),
     "rexsc_alu_probe": (C.c_int, [_i32, _i32, _vp, _vp]),
+    "rexsc_mma_probe": (C.c_int, [_i32, _i32, _i32, _vp, _vp]),
 }
 
 _lib = None

@@ -243,3 +243,8 @@ extern "C" int rexsc_alu_probe(int32_t blocks, int32_t iters, uint32_t *d_sink, 
     REXSC_LAUNCH_CHECK("alu_probe_kernel");
     return REXSC_OK;
 }
+
+extern "C" int rexsc_mma_probe(int32_t blocks, int32_t iters, int32_t n_cols, uint32_t *d_sink, void *stream)
+{
+    return launch_mma_probe(blocks, iters, n_cols, d_sink, (cudaStream_t)stream);
+}

@@ -115,6 +115,7 @@ static inline long long patch_bound_words(long long BM, long long M, int OW, int
 int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
                  int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st);
 
+int launch_mma_probe(int blocks, int iters, int n_cols, uint32_t *d_sink, cudaStream_t st);
 bool conv_tc_supported(const ConvPlan &p);
 size_t conv_tc_workspace_bytes(const ConvPlan &p);
 int launch_tc_bitplanes(const ConvPlan &p, const uint32_t *d_A, const uint32_t *d_Wt, const uint32_t *d_S,

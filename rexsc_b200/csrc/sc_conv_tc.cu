@@ -383,6 +383,70 @@ __global__ void __launch_bounds__(256) bitplane_weight_kernel(const uint32_t *__
     Wb[(((size_t)nchunk * slots + wd * 32 + lane) * kTcN + row) * ((size_t)KHW * CW) + tap * CW + cw] = mine;
 }
 
+// Tensor-pipe issue-rate probe: back-to-back int8 MMAs (M128 x N x K32) on fixed shared-memory operands.
+__global__ void __launch_bounds__(128, 2) mma_probe_kernel(int iters, int n_cols, uint32_t *sink)
+{
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((128u - (saddr(smem_raw) & 127u)) & 127u);
+    uint8_t *a_s = smem;                 // [2][128][16]
+    uint8_t *b_s = smem + 2 * 128 * 16;  // [2][n_cols][16]
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (int i = tid; i < (2 * 128 * 16 + 2 * n_cols * 16) / 16; i += blockDim.x)
+        reinterpret_cast<uint4 *>(smem)[i] = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(saddr(&bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(&tmem_slot)),
+                     "r"((uint32_t)n_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    bool ok = true;
+    if (tid == 0) {
+        const uint64_t da = desc_interleaved(saddr(a_s), 128 * 16), db = desc_interleaved(saddr(b_s), (uint32_t)n_cols * 16);
+        uint32_t phase = 0;
+        for (int it = 0; it < iters && ok; it++) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const uint32_t accumulate = (it > 0 || j > 0) ? 1u : 0u;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "setp.ne.b32 p, %4, 0;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                    ::"r"(tmem_base), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
+                    : "memory");
+            }
+            // commit and wait every 64 iterations so that the queue stays full but bounded
+            if ((it & 63) == 63 || it == iters - 1) {
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(&bar))
+                             : "memory");
+                ok = tc_wait(saddr(&bar), phase & 1u);
+                phase++;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t v[16];
+    REXSC_TMEM_LD16_PACKED(v, tmem_base + ((uint32_t)(warp * 32) << 16));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    sink[blockIdx.x * blockDim.x + tid] = v[0] + (ok ? 0u : 0x80000000u);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)n_cols) : "memory");
+}
+
 size_t tc_smem_bytes(const ConvPlan &p)
 {
     const int rows_a = (kTcM + p.max_tap + 7) / 8 * 8;
@@ -390,6 +454,15 @@ size_t tc_smem_bytes(const ConvPlan &p)
 }
 
 } // namespace
+
+int launch_mma_probe(int blocks, int iters, int n_cols, uint32_t *d_sink, cudaStream_t st)
+{
+    if (blocks < 1 || iters < 1 || (n_cols != 128 && n_cols != 256) || !d_sink) return REXSC_E_BAD_ARG;
+    const size_t smem = 2 * 128 * 16 + 2 * (size_t)n_cols * 16 + 128;
+    mma_probe_kernel<<<blocks, 128, smem, st>>>(iters, n_cols, d_sink);
+    REXSC_LAUNCH_CHECK("mma_probe_kernel");
+    return REXSC_OK;
+}
 
 bool conv_tc_supported(const ConvPlan &p)
 {

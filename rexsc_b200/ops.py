@@ -429,3 +429,15 @@ def alu_probe(blocks: int, iters: int, device="cuda") -> torch.Tensor:
         sink = torch.empty(blocks * 256, dtype=torch.int32, device=dev)
         _lib.check(lib.rexsc_alu_probe(int(blocks), int(iters), _ptr(sink), _stream(dev)), "rexsc_alu_probe")
     return sink
+
+
+def mma_probe(blocks: int, iters: int, n_cols: int = 128, device="cuda") -> torch.Tensor:
+    """Launch the int8 tensor-pipe probe; returns the sink tensor (blocks*128 words)."""
+    lib = _lib.load()
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(dev):
+        sink = torch.empty(blocks * 128, dtype=torch.int32, device=dev)
+        _lib.check(lib.rexsc_mma_probe(int(blocks), int(iters), int(n_cols), _ptr(sink), _stream(dev)), "rexsc_mma_probe")
+    return sink

@@ -56,7 +56,7 @@ def test_workspace_size_model(lib):
     # activation words dominate: planes * padded channels * padded pixel count * 4 bytes
     big = _desc(batch=256, c_in=64, h_in=58, w_in=58, c_out=64)
     nb = lib.rexsc_sc_conv2d_workspace_size(C.byref(big))
-    assert 256 * 58 * 58 * 64 * 4 <= nb <= 256 * 58 * 58 * 64 * 4 * 1.3   # row pitch may be padded against bank conflicts
+    assert 256 * 58 * 58 * 64 * 4 <= nb <= 256 * 58 * 58 * 64 * 4 * 2.6   # padded row pitch + bit planes of the tensor-core kernel
     two = _desc(batch=256, c_in=64, h_in=58, w_in=58, c_out=64, bit_length=64)
     assert lib.rexsc_sc_conv2d_workspace_size(C.byref(two)) > 1.9 * nb
 
