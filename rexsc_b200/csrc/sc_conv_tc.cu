@@ -15,9 +15,11 @@
 // The M dimension runs over consecutive positions of the stored (padded) pixel grid; positions that are not the
 // origin of an output pixel produce rows that are computed and dropped.
 //
-// One CTA = 256 threads: everybody expands operands, one thread issues the MMAs and commits to an mbarrier, then
-// the eight warps read TMEM (warp w: lanes 32*(w%4).., columns 64*(w/4)..), clamp to n and add into 16-bit packed
-// running sums.  Two CTAs share an SM, so one CTA's expansion / epilogue overlaps the other's MMAs.
+// One CTA per SM, 512 threads, 256 stored-grid positions (two MMA row blocks sharing one weight operand).  Operand
+// buffers are double-buffered: while the tensor core works through the MMAs of pipeline step i (one slot x one
+// 64-channel chunk), all threads expand the operands of step i+1 and fold the counts of the slot that just
+// finished (TMEM accumulators alternate between two 256-column buffers); the bit words of step i+2 are already
+// on their way from L2.  Warp w reads TMEM lanes 32*(w%4).., row block (w/4)%2, columns 64*(w/8)..
 // Every wait is bounded; on a time-out the CTA reports through the status word, frees its TMEM and returns.
 #include "common.cuh"
 
@@ -25,12 +27,14 @@ namespace rexsc {
 
 namespace {
 
-constexpr int kTcThreads = 256;
+constexpr int kTcWorkers = 512;             // threads that expand operands and fold counts
+constexpr int kTcThreads = kTcWorkers + 64; // + two warps that only issue MMAs, one per 128-row block
 constexpr int kTcM = 256;          // stored-grid positions per CTA: two MMA row blocks that share one weight operand
 constexpr int kTcSub = 128;        // rows of one MMA (TMEM lanes)
 constexpr int kTcCout = 64;        // output channels per CTA
 constexpr int kTcN = 2 * kTcCout;  // MMA N: positive block [0,64), negative block [64,128)
-constexpr int kTcMaxTaps = 9;      // filter taps whose weight operand is staged at once
+constexpr int kTcMaxTaps = 9;
+constexpr int kTcPrefetch = 4; // pipeline steps between the L2 prefetch of patch bits and their use      // filter taps whose weight operand is staged at once
 constexpr uint32_t kTcWaitLimit = 1u << 22;
 
 struct TcArgs {
@@ -40,6 +44,8 @@ struct TcArgs {
     int slots, n_or;
     long long NHW, NHWp;
     int out_nhwc;
+    int descale_each; // 1: running sums would overflow 16 bits in accumulator units, so every slot is descaled
+    int tap_off[kTcMaxTaps]; // patch-row offset of every tap (kernel parameters are warp-uniform by construction)
 };
 
 __device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -69,15 +75,27 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity)
     return false;
 }
 
-// 16 bits -> 16 bytes of 0/1 (bit i -> byte i)
-__device__ __forceinline__ uint4 spread16(uint32_t h)
+// Operand bytes are not 0/1.  Expanding bit i of a nibble to byte i costs one byte-replicate (PRMT) and one AND when
+// the byte keeps its bit where it was: patch bytes are 0 or 2^i (mask 0x08040201).  The weight bit planes store each
+// nibble bit-reversed and use mask 0x01020408, so their bytes are 0 or 2^(3-i); every coincidence contributes
+// 2^i * 2^(3-i) = 8 and the accumulators hold 8 * count.
+constexpr uint32_t kTcMaskA = 0x08040201u, kTcMaskW = 0x01020408u;
+constexpr int kTcScaleLog2 = 3;
+constexpr uint32_t kDescaleMask = (0xffffu >> kTcScaleLog2) * 0x00010001u; // after a packed 16-bit shift right
+
+// 32 bits -> two groups of 16 operand bytes (bits 0..15 and 16..31; byte i <- bit i)
+template <uint32_t MASK>
+__device__ __forceinline__ void spread32(uint32_t h, uint4 &lo16, uint4 &hi16)
 {
-    uint4 r;
-    r.x = ((h & 0xfu) * 0x00204081u) & 0x01010101u;
-    r.y = (((h >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
-    r.z = (((h >> 8) & 0xfu) * 0x00204081u) & 0x01010101u;
-    r.w = (((h >> 12) & 0xfu) * 0x00204081u) & 0x01010101u;
-    return r;
+    const uint32_t g = h >> 4; // high nibbles moved into the low half of each byte
+    lo16.x = __byte_perm(h, 0, 0x0000) & MASK;
+    lo16.y = __byte_perm(g, 0, 0x0000) & MASK;
+    lo16.z = __byte_perm(h, 0, 0x1111) & MASK;
+    lo16.w = __byte_perm(g, 0, 0x1111) & MASK;
+    hi16.x = __byte_perm(h, 0, 0x2222) & MASK;
+    hi16.y = __byte_perm(g, 0, 0x2222) & MASK;
+    hi16.z = __byte_perm(h, 0, 0x3333) & MASK;
+    hi16.w = __byte_perm(g, 0, 0x3333) & MASK;
 }
 
 #define REXSC_TMEM_LD32(arr, taddr)                                                                                   \
@@ -104,33 +122,37 @@ __device__ __forceinline__ uint4 spread16(uint32_t h)
         : "r"(taddr)                                                                                                  \
         : "memory")
 
-__global__ void __launch_bounds__(kTcThreads, 2)
+// KHW_T: taps known at compile time (9, 1) or 0 for any tap count up to kTcMaxTaps
+template <int KHW_T>
+__global__ void __launch_bounds__(kTcThreads, 1)
 sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__restrict__ Wb,
                   int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((128u - (saddr(smem_raw) & 127u)) & 127u);
-    uint8_t *a_s = smem;                                            // [4][rows_a][16]
-    uint8_t *b_s = a_s + 4 * a.rows_a * 16;                         // [KHW][4][128][16]
-    uint64_t *bar = reinterpret_cast<uint64_t *>(b_s + a.KHW * 4 * kTcN * 16);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
-    int *tap_s = reinterpret_cast<int *>(tmem_slot + 1);
+    const uint32_t a_bytes = 4u * (uint32_t)a.rows_a * 16u;          // [4][rows_a][16]
+    const uint32_t b_bytes = (uint32_t)a.KHW * 4u * kTcN * 16u;      // [KHW][4][128][16]
+    auto a_buf = [&](int buf) { return smem + (uint32_t)buf * a_bytes; };
+    auto b_buf = [&](int buf) { return smem + 2 * a_bytes + (uint32_t)buf * b_bytes; };
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * a_bytes + 2 * b_bytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // the shuffle tells the compiler what it cannot see: the warp index is the same in every lane
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const long long q0 = (long long)blockIdx.x * kTcM; // first stored-grid position of the tile
     const int nc = blockIdx.y;                         // 64-channel output chunk
 
-    if (tid < a.KHW) {
-        const int kh = tid / a.KW, kw = tid - kh * a.KW;
-        tap_s[tid] = tap_offset(kh, kw, a.sh, a.sw, a.nrh, a.Wrow, a.Wq);
-    }
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(saddr(bar)) : "memory");
+        // one arrival per issuing warp
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(saddr(&bars[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(saddr(&bars[1])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
+        // two accumulator buffers of 2 row blocks x 128 columns: the whole tensor memory of the SM
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(tmem_slot)),
-                     "r"((uint32_t)(2 * kTcN)) : "memory");
+                     "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -144,121 +166,185 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const int wrow_words = a.KHW * a.CW;               // words per weight row and slot
     const uint32_t *Wchunk = Wb + (size_t)nc * a.slots * kTcN * wrow_words;
 
-    // running sums: this thread owns row block warp/4, TMEM lane 32*(warp%4)+lane and all 128 columns of that block,
-    // two 16-bit sums per register (column pairs as the packed TMEM load delivers them)
-    uint32_t acc[64];
+    // running sums: this thread owns row block (warp/4)%2, TMEM lane 32*(warp%4)+lane and 64 columns (warp/8 = 0:
+    // positive block, 1: negative block), two 16-bit sums per register as the packed TMEM load delivers them
+    uint32_t acc[32];
 #pragma unroll
-    for (int j = 0; j < 64; j++) acc[j] = 0u;
-    const uint32_t my_taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)((warp >> 2) * kTcN);
-    const uint32_t n2 = (uint32_t)a.n_or | ((uint32_t)a.n_or << 16);
+    for (int j = 0; j < 32; j++) acc[j] = 0u;
+    const uint32_t my_tcol = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(((warp >> 2) & 1) * kTcN + (warp >> 3) * 64);
+    const uint32_t n2 = ((uint32_t)a.n_or << kTcScaleLog2) * 0x00010001u; // the clamp, in accumulator units, twice
 
-    // Bit words of one pipeline step (slot, 64-channel chunk) are fetched into registers one step ahead, so
-    // that their L2 latency hides behind the previous step's MMAs.
-    //   weights: thread -> (row = tid & 127, word half = tid >> 7), one word per filter tap
-    //   patch:   thread -> rows tid and tid + 256, both words of the chunk
-    const int w_row = tid & (kTcN - 1), w_half = tid >> 7;
-    uint32_t wbits[kTcMaxTaps], abits[4];
+    // Bit words of a step are fetched into registers two steps before their MMAs so that L2 latency is hidden.
+    //   weights: thread -> (row = tid & 127, word half = (tid >> 7) & 1, tap parity = tid >> 8), every other tap
+    //   patch:   thread -> row tid, both words of the chunk
+    const int w_row = tid & (kTcN - 1), w_half = (tid >> 7) & 1, w_par = tid >> 8;
+    uint32_t wbits[(kTcMaxTaps + 1) / 2], abits[2];
     auto load_bits = [&](int step) {
         const int s = step / a.CK, ck = step - s * a.CK;
         const int cw = 2 * ck + w_half;
         const uint32_t *src = Wchunk + ((size_t)s * kTcN + w_row) * wrow_words + cw;
 #pragma unroll
-        for (int tap = 0; tap < kTcMaxTaps; tap++)
-            wbits[tap] = (tap < a.KHW && cw < a.CW) ? __ldg(src + tap * a.CW) : 0u;
+        for (int i = 0; i < (kTcMaxTaps + 1) / 2; i++) {
+            const int tap = 2 * i + w_par;
+            wbits[i] = (tap < a.KHW && cw < a.CW) ? __ldg(src + tap * a.CW) : 0u;
+        }
+        const long long P = q0 + tid;
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int r = tid + kTcThreads * j;
-            const long long P = q0 + r;
+        for (int h = 0; h < 2; h++) {
+            const int cwa = 2 * ck + h;
+            abits[h] = (tid < a.rows_a && P < a.NHW && cwa < a.CW) ? __ldg(Ab + ((size_t)s * a.CW + cwa) * a.NHWp + P) : 0u;
+        }
+        // the patch bits stream from HBM: pull the line of a later step into L2 (one lane per 128-byte line)
+        if ((tid & 31) == 0 && tid < a.rows_a && step + kTcPrefetch < a.slots * a.CK) {
+            const int sp = (step + kTcPrefetch) / a.CK, ckp = (step + kTcPrefetch) - sp * a.CK;
+            const long long Pp = P < a.NHW ? P : a.NHW - 1;
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                if (2 * ckp + h < a.CW)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(Ab + ((size_t)sp * a.CW + 2 * ckp + h) * a.NHWp + Pp));
+        }
+    };
+    auto expand_bits = [&](int buf) {
+        uint8_t *b_s = b_buf(buf), *a_s = a_buf(buf);
+#pragma unroll
+        for (int i = 0; i < (kTcMaxTaps + 1) / 2; i++) {
+            const int tap = 2 * i + w_par;
+            if (tap < a.KHW) {
+                uint8_t *dst = b_s + ((size_t)(tap * 4 + 2 * w_half) * kTcN + w_row) * 16;
+                uint4 lo16, hi16;
+                spread32<kTcMaskW>(wbits[i], lo16, hi16);
+                *reinterpret_cast<uint4 *>(dst) = lo16;
+                *reinterpret_cast<uint4 *>(dst + kTcN * 16) = hi16;
+            }
+        }
+        if (tid < a.rows_a) {
 #pragma unroll
             for (int h = 0; h < 2; h++) {
-                const int cwa = 2 * ck + h;
-                abits[2 * j + h] = (r < a.rows_a && P < a.NHW && cwa < a.CW)
-                                       ? __ldg(Ab + ((size_t)s * a.CW + cwa) * a.NHWp + P) : 0u;
+                uint4 lo16, hi16;
+                spread32<kTcMaskA>(abits[h], lo16, hi16);
+                *reinterpret_cast<uint4 *>(a_s + ((size_t)(2 * h) * a.rows_a + tid) * 16) = lo16;
+                *reinterpret_cast<uint4 *>(a_s + ((size_t)(2 * h + 1) * a.rows_a + tid) * 16) = hi16;
             }
         }
     };
-    auto expand_bits = [&]() {
+    // count -> min(count, n) -> running sums, for the slot whose accumulators sit in TMEM buffer `tbuf`
+    auto slot_epilogue = [&](int tbuf) {
+        const uint32_t taddr = tmem_base + my_tcol + (uint32_t)(tbuf * 2 * kTcN);
+        uint32_t v0[16], v1[16];
+        REXSC_TMEM_LD16_PACKED(v0, taddr);
+        REXSC_TMEM_LD16_PACKED(v1, taddr + 32u);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int tap = 0; tap < kTcMaxTaps; tap++) {
-            if (tap < a.KHW) {
-                uint8_t *dst = b_s + ((size_t)(tap * 4 + 2 * w_half) * kTcN + w_row) * 16;
-                *reinterpret_cast<uint4 *>(dst) = spread16(wbits[tap]);
-                *reinterpret_cast<uint4 *>(dst + kTcN * 16) = spread16(wbits[tap] >> 16);
+        for (int j = 0; j < 16; j++) {
+            uint32_t t0 = __vminu2(v0[j], n2), t1 = __vminu2(v1[j], n2);
+            if (a.descale_each) {
+                t0 = (t0 >> kTcScaleLog2) & kDescaleMask;
+                t1 = (t1 >> kTcScaleLog2) & kDescaleMask;
             }
+            acc[j] += t0;
+            acc[16 + j] += t1;
         }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    };
+    // One thread issues the MMAs of one 128-row block.  A single thread gets one 128-column MMA through about every
+    // 128 clocks, half of what the tensor core can take, so the two row blocks are issued from two warps.  The
+    // issuing warps share their schedulers with the expanding warps, so the loop is kept to a few instructions per
+    // MMA: fully unrolled over taps, per-tap operand offsets in registers, descriptors patched in their low word
+    // (the start-address field counts 16-byte units, i.e. operand rows, from bit 0; no carry leaves the field
+    // because shared memory ends below 256 KB).
+    const int my_sub = warp - kTcWorkers / 32;
+    uint32_t a_tap[kTcMaxTaps];
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int r = tid + kTcThreads * j;
-            if (r < a.rows_a) {
+    for (int tap = 0; tap < kTcMaxTaps; tap++)
+        a_tap[tap] = (my_sub >= 0 && tap < a.KHW) ? (uint32_t)(my_sub * kTcSub + a.tap_off[tap]) : 0u;
+    const uint64_t da_proto = desc_interleaved(saddr(a_buf(0)), a_lbo), db_proto = desc_interleaved(saddr(b_buf(0)), b_lbo);
+    const uint32_t da_hi = (uint32_t)(da_proto >> 32), db_hi = (uint32_t)(db_proto >> 32);
+    const uint32_t a_kk = 2u * (uint32_t)a.rows_a; // rows between the two 32-channel halves of a chunk
+    auto issue_mmas = [&](int step) {
+        const int s = step / a.CK, ck = step - s * a.CK, buf = step & 1;
+        const uint32_t da_lo = (uint32_t)da_proto + (uint32_t)buf * (a_bytes >> 4);
+        const uint32_t db_lo = (uint32_t)db_proto + (uint32_t)buf * (b_bytes >> 4);
+        const uint32_t d_addr = tmem_base + (uint32_t)((s & 1) * 2 * kTcN + my_sub * kTcN);
+        const bool two = 2 * ck + 1 < a.CW; // channels in the second half of the chunk
+        const uint32_t first_acc = ck > 0 ? 1u : 0u;
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    *reinterpret_cast<uint4 *>(a_s + ((size_t)(2 * h) * a.rows_a + r) * 16) = spread16(abits[2 * j + h]);
-                    *reinterpret_cast<uint4 *>(a_s + ((size_t)(2 * h + 1) * a.rows_a + r) * 16) = spread16(abits[2 * j + h] >> 16);
+        for (int tap = 0; tap < (KHW_T ? KHW_T : kTcMaxTaps); tap++) {
+            if (KHW_T || tap < a.KHW) {
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    if (kk == 1 && !two) break;
+                    const uint32_t alo = da_lo + a_tap[tap] + (kk ? a_kk : 0u);
+                    const uint32_t blo = db_lo + (uint32_t)((tap * 4 + 2 * kk) * kTcN);
+                    const uint32_t accumulate = (tap > 0 || kk > 0) ? 1u : first_acc;
+                    asm volatile(
+                        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t"
+                        "mov.b64 da, {%1, %2};\n\t"
+                        "mov.b64 db, {%3, %4};\n\t"
+                        "setp.ne.b32 p, %6, 0;\n\t"
+                        "elect.sync _|e, 0xffffffff;\n\t"
+                        "@e tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, {%7, %7, %7, %7}, p;\n\t}"
+                        ::"r"(d_addr), "r"(alo), "r"(da_hi), "r"(blo), "r"(db_hi), "r"(idesc), "r"(accumulate), "r"(0u)
+                        : "memory");
                 }
             }
         }
-    };
-    // count -> min(count, n) -> running sums for the slot whose accumulators are complete in TMEM
-    auto slot_epilogue = [&]() {
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-            uint32_t v[16];
-            REXSC_TMEM_LD16_PACKED(v, my_taddr + (uint32_t)(g * 32));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int j = 0; j < 16; j++) acc[g * 16 + j] += __vminu2(v[j], n2);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                     "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(&bars[buf]))
+                     : "memory");
     };
 
     bool failed = false;
     const int n_steps = a.slots * a.CK;
-    const uint64_t da0 = desc_interleaved(saddr(a_s), a_lbo), db0 = desc_interleaved(saddr(b_s), b_lbo);
-    load_bits(0);
+    // prologue: operands of step 0 in buffer 0, bits of step 1 in registers
+    if (warp < kTcWorkers / 32) {
+        load_bits(0);
+        expand_bits(0);
+        if (n_steps > 1) load_bits(1);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
     for (int step = 0; step < n_steps; step++) {
-        const int s = step / a.CK, ck = step - s * a.CK;
-        expand_bits(); // the operand buffers are free: the previous step's MMAs were waited for
+        if (warp >= kTcWorkers / 32) {
+            // (a) feed the tensor core: the MMAs of this step queue up behind those of the previous one
+            // the whole warp runs the loop (its operands stay warp-uniform); one elected lane issues
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_mmas(step);
+            __syncwarp();
+        } else {
+            // (b) the previous step's MMAs must be done before its operand buffer is rewritten / its slot is folded
+            if (step > 0) {
+                if (!tc_wait(saddr(&bars[(step - 1) & 1]), (uint32_t)(((step - 1) >> 1) & 1))) failed = true;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            // (c) next step's operands into the other buffer, bits of the step after that on their way
+            if (step + 1 < n_steps) {
+                expand_bits((step + 1) & 1);
+                if (step + 2 < n_steps) load_bits(step + 2);
+            }
+            // (d) fold the slot that the previous step completed
+            if (step > 0 && (step % a.CK) == 0 && !failed) slot_epilogue(((step - 1) / a.CK) & 1);
+        }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // the start-address field counts 16-byte units from bit 0, i.e. operand rows: moving an operand by
-            // rows / K-columns is an integer add on the descriptor
-#pragma unroll
-            for (int sub = 0; sub < kTcM / kTcSub; sub++) {
-                const uint32_t d_addr = tmem_base + (uint32_t)(sub * kTcN);
-                for (int tap = 0; tap < a.KHW; tap++) {
-#pragma unroll
-                    for (int kk = 0; kk < 2; kk++) {
-                        if (2 * ck + kk >= a.CW) break; // no channels in this half of the chunk
-                        const uint64_t da = da0 + (uint64_t)(uint32_t)(sub * kTcSub + tap_s[tap] + 2 * kk * a.rows_a);
-                        const uint64_t db = db0 + (uint64_t)(uint32_t)((tap * 4 + 2 * kk) * kTcN);
-                        const uint32_t accumulate = (ck > 0 || tap > 0 || kk > 0) ? 1u : 0u;
-                        asm volatile(
-                            "{\n\t.reg .pred p;\n\t"
-                            "setp.ne.b32 p, %4, 0;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                            ::"r"(d_addr), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u)
-                            : "memory");
-                    }
-                }
-            }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar))
-                         : "memory");
-        }
-        // while the tensor core works: fetch the next step's bits
-        if (step + 1 < n_steps) load_bits(step + 1);
-        if (!tc_wait(saddr(bar), (uint32_t)(step & 1))) failed = true;
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (failed) break;
-        if (ck == a.CK - 1) slot_epilogue(); // the next slot's first MMA comes after the next barrier
+    }
+    if (!failed) {
+        // the last step's MMAs, then the last slot
+        if (!tc_wait(saddr(&bars[(n_steps - 1) & 1]), (uint32_t)(((n_steps - 1) >> 1) & 1))) failed = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        failed = __syncthreads_or(failed ? 1 : 0) != 0;
+        if (!failed && warp < kTcWorkers / 32) slot_epilogue((a.slots - 1) & 1);
     }
 
-    if (!failed) {
+    if (!failed && warp < kTcWorkers / 32) {
         // ---- store: row = one stored-grid position; it is an output pixel iff it is the tap-(0,0) origin of one ----
-        const long long q = q0 + (warp >> 2) * kTcSub + (warp & 3) * 32 + lane;
+        if (!a.descale_each) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) acc[j] = (acc[j] >> kTcScaleLog2) & kDescaleMask;
+        }
+        const long long q = q0 + ((warp >> 2) & 1) * kTcSub + (warp & 3) * 32 + lane;
         if (q < a.NHW) {
             const int colp = (int)(q % a.Wrow);
             const long long t = q / a.Wrow;
@@ -269,41 +355,35 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 const int co0 = nc * kTcCout;
                 const size_t ohw = (size_t)a.OH * a.OW;
                 const size_t m = ((size_t)n * a.OH + oh) * a.OW + colp;
-                // acc[0..31] = positive block (columns 0..63), acc[32..63] = negative block
+                int16_t *dst = (warp >> 3) ? out_neg : out_pos;
+                if (a.out_nhwc) {
+                    int16_t *row = dst + m * a.Co + co0;
+                    if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
 #pragma unroll
-                for (int sign = 0; sign < 2; sign++) {
-                    int16_t *dst = sign ? out_neg : out_pos;
-                    const uint32_t *av = acc + sign * 32;
-                    if (a.out_nhwc) {
-                        int16_t *row = dst + m * a.Co + co0;
-                        if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<uint4 *>(row + 2 * j) = make_uint4(av[j], av[j + 1], av[j + 2], av[j + 3]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 64; j++)
-                                if (co0 + j < a.Co) row[j] = (int16_t)((av[j >> 1] >> (16 * (j & 1))) & 0xffffu);
-                        }
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4 *>(row + 2 * j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 64; j++)
-                            if (co0 + j < a.Co)
-                                dst[((size_t)n * a.Co + co0 + j) * ohw + (size_t)oh * a.OW + colp] =
-                                    (int16_t)((av[j >> 1] >> (16 * (j & 1))) & 0xffffu);
+                            if (co0 + j < a.Co) row[j] = (int16_t)((acc[j >> 1] >> (16 * (j & 1))) & 0xffffu);
                     }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; j++)
+                        if (co0 + j < a.Co)
+                            dst[((size_t)n * a.Co + co0 + j) * ohw + (size_t)oh * a.OW + colp] =
+                                (int16_t)((acc[j >> 1] >> (16 * (j & 1))) & 0xffffu);
                 }
             }
         }
-    } else if (tid == 0) {
+    } else if (failed && tid == 0) {
         atomicExch(status, 4);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * kTcN))
-                     : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
 // ---- bit planes --------------------------------------------------------------------------------------------
@@ -346,7 +426,7 @@ __global__ void __launch_bounds__(256) bitplane_act_kernel(const uint32_t *__res
 }
 
 // weight words + signs (layout of the ALU kernels)  ->  Wb[nchunk][slot][row][tap*CW + cw],
-// row = sign*64 + local output channel, bit b = channel 32*cw + b
+// row = sign*64 + local output channel, bit b = channel 32*cw + (b ^ 3): nibbles are stored bit-reversed
 __global__ void __launch_bounds__(256) bitplane_weight_kernel(const uint32_t *__restrict__ Wt, const uint32_t *__restrict__ S,
                                                               uint32_t *__restrict__ Wb, int Co, int C, int KHW, int CCH,
                                                               int CW, int words, int NC, long long w_plane_words)
@@ -379,6 +459,9 @@ __global__ void __launch_bounds__(256) bitplane_weight_kernel(const uint32_t *__
         const uint32_t b = __ballot_sync(0xffffffffu, (v >> tt) & 1u);
         if (lane == tt) mine = b;
     }
+    // bit-reverse every nibble (see kTcMaskW): reverse all 32 bits, then put the nibbles back in order
+    mine = __byte_perm(__brev(mine), 0, 0x0123);
+    mine = ((mine & 0x0f0f0f0fu) << 4) | ((mine >> 4) & 0x0f0f0f0fu);
     const int slots = words * 32;
     Wb[(((size_t)nchunk * slots + wd * 32 + lane) * kTcN + row) * ((size_t)KHW * CW) + tap * CW + cw] = mine;
 }
@@ -450,7 +533,9 @@ __global__ void __launch_bounds__(128, 2) mma_probe_kernel(int iters, int n_cols
 size_t tc_smem_bytes(const ConvPlan &p)
 {
     const int rows_a = (kTcM + p.max_tap + 7) / 8 * 8;
-    return (size_t)4 * rows_a * 16 + (size_t)p.KHW * 4 * kTcN * 16 + 8 + 8 + kTcMaxTaps * 4 + 128;
+    const size_t need = 2 * ((size_t)4 * rows_a * 16 + (size_t)p.KHW * 4 * kTcN * 16) + 16 + 8 + 128;
+    // the kernel owns the SM's whole tensor memory: ask for enough shared memory that no second CTA is co-scheduled
+    return need > 120 * 1024 ? need : 120 * 1024;
 }
 
 } // namespace
@@ -468,10 +553,11 @@ bool conv_tc_supported(const ConvPlan &p)
 {
     if (p.n_or < 1) return false;
     if (p.KHW > kTcMaxTaps) return false;
-    if (tc_smem_bytes(p) > 112 * 1024) return false;                          // two CTAs per SM
-    if (kTcM + p.max_tap > 2 * kTcThreads) return false;                      // patch rows: two per thread
+    if (tc_smem_bytes(p) > 227 * 1024) return false;
+    if (kTcM + p.max_tap > kTcWorkers) return false;                          // patch rows: one per thread
     const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;                   // largest per-slot contribution
     if ((long long)p.words * 32 * cap > 65535) return false;                  // 16-bit running sums
+    if (((long long)p.Kdot << kTcScaleLog2) > 65535) return false;            // 16-bit packed accumulator reads
     if (p.Kdot > (1 << 24)) return false;
     if ((p.NHW + kTcM - 1) / kTcM > 0x7fffffffLL) return false;
     return true;
@@ -525,10 +611,18 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     a.rows_a = (kTcM + p.max_tap + 7) / 8 * 8;
     a.slots = slots; a.n_or = p.n_or;
     a.NHW = p.NHW; a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
+    {
+        const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;
+        a.descale_each = (((long long)slots * cap) << kTcScaleLog2) > 65535 ? 1 : 0;
+        a.n_or = (int)cap; // a count never exceeds the dot length, so clamping there changes nothing
+    }
+    for (int t = 0; t < kTcMaxTaps; t++)
+        a.tap_off[t] = t < p.KHW ? tap_offset(t / p.KW, t % p.KW, p.sh, p.sw, p.nrh, p.Wrow, p.Wq) : 0;
     const size_t smem = tc_smem_bytes(p);
-    REXSC_CUDA_CHECK(cudaFuncSetAttribute(sc_conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)((p.NHW + kTcM - 1) / kTcM), (unsigned)NC);
-    sc_conv_tc_kernel<<<grid, kTcThreads, smem, st>>>(a, Ab, Wb, d_pos, d_neg, d_status);
+    auto kernel = p.KHW == 9 ? sc_conv_tc_kernel<9> : p.KHW == 1 ? sc_conv_tc_kernel<1> : sc_conv_tc_kernel<0>;
+    REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, kTcThreads, smem, st>>>(a, Ab, Wb, d_pos, d_neg, d_status);
     REXSC_LAUNCH_CHECK("sc_conv_tc_kernel");
     return REXSC_OK;
 }
