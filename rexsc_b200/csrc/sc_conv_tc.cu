@@ -35,7 +35,8 @@ constexpr int kTcCout = 64;        // output channels per CTA
 constexpr int kTcN = 2 * kTcCout;  // MMA N: positive block [0,64), negative block [64,128)
 constexpr int kTcMaxTaps = 9;
 constexpr int kTcPrefetch = 4; // pipeline steps between the L2 prefetch of patch bits and their use      // filter taps whose weight operand is staged at once
-constexpr uint32_t kTcWaitLimit = 1u << 22;
+constexpr uint32_t kTcWaitLimit = 1u << 18; // try_wait attempts before a wait gives up (each may sleep kTcSuspendNs)
+constexpr uint32_t kTcSuspendNs = 4000;    // a waiting warp sleeps in the barrier unit instead of spinning on issue slots
 
 struct TcArgs {
     int OH, OW, sh, sw, KH, KW, KHW, Co, CW, CK;
@@ -67,9 +68,9 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity)
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(kTcSuspendNs) : "memory");
         if (ok) return true;
     }
     return false;
@@ -135,7 +136,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     auto a_buf = [&](int buf) { return smem + (uint32_t)buf * a_bytes; };
     auto b_buf = [&](int buf) { return smem + 2 * a_bytes + (uint32_t)buf * b_bytes; };
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * a_bytes + 2 * b_bytes);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
 
     const int tid = threadIdx.x, lane = tid & 31;
     // the shuffle tells the compiler what it cannot see: the warp index is the same in every lane
@@ -143,10 +144,19 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const long long q0 = (long long)blockIdx.x * kTcM; // first stored-grid position of the tile
     const int nc = blockIdx.y;                         // 64-channel output chunk
 
+    // mbarriers (index = operand buffer or accumulator buffer):
+    //   full[b]   operands of a step are in shared memory           (one arrival per expanding warp)
+    //   empty[b]  the MMAs that read operand buffer b have completed (one commit per issuing warp)
+    //   tfull[t]  a slot's counts are complete in accumulator buffer t (one commit per issuing warp)
+    //   tfree[t]  accumulator buffer t has been folded                (one arrival per expanding warp)
+    uint64_t *bar_full = bars, *bar_empty = bars + 2, *bar_tfull = bars + 4, *bar_tfree = bars + 6;
     if (tid == 0) {
-        // one arrival per issuing warp
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(saddr(&bars[0])) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 2;" ::"r"(saddr(&bars[1])) : "memory");
+        for (int b = 0; b < 2; b++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_full[b])), "r"(kTcWorkers / 32) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_empty[b])), "r"(kTcM / kTcSub) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_tfull[b])), "r"(kTcM / kTcSub) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_tfree[b])), "r"(kTcWorkers / 32) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -177,53 +187,69 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // Bit words of a step are fetched into registers two steps before their MMAs so that L2 latency is hidden.
     //   weights: thread -> (row = tid & 127, word half = (tid >> 7) & 1, tap parity = tid >> 8), every other tap
     //   patch:   thread -> row tid, both words of the chunk
+    // The loads walk the steps in order, so their addresses are kept as running pointers (no per-step division or
+    // 64-bit multiplication): ld_ck / ld_left describe the step that the next load_bits() call fetches.
     const int w_row = tid & (kTcN - 1), w_half = (tid >> 7) & 1, w_par = tid >> 8;
-    uint32_t wbits[(kTcMaxTaps + 1) / 2], abits[2];
-    auto load_bits = [&](int step) {
-        const int s = step / a.CK, ck = step - s * a.CK;
-        const int cw = 2 * ck + w_half;
-        const uint32_t *src = Wchunk + ((size_t)s * kTcN + w_row) * wrow_words + cw;
+    constexpr int kMyTaps = (kTcMaxTaps + 1) / 2;
+    uint32_t wbits[kMyTaps], abits[2];
+    const size_t w_tap_stride = (size_t)2 * a.CW * kTcN;                 // two taps further
+    const uint32_t *w_ptr = Wchunk + ((size_t)w_par * a.CW + w_half) * kTcN + w_row; // slot 0, chunk 0, first own tap
+    const long long P = q0 + tid;
+    const bool a_row_ok = tid < a.rows_a && P < a.NHW;
+    const uint32_t *a_ptr = Ab + (a_row_ok ? P : 0);                      // slot 0, word 0
+    const uint32_t *pf_ptr = Ab + (P < a.NHW ? P : a.NHW - 1) + (size_t)kTcPrefetch * a.CW * a.NHWp; // CK == 1 only
+    const bool pf_lane = lane == 0 && tid < a.rows_a && a.CK == 1;
+    int ld_ck = 0, ld_left = a.slots * a.CK;
+    auto load_bits = [&]() {
+        const bool half_ok = 2 * ld_ck + w_half < a.CW;
 #pragma unroll
-        for (int i = 0; i < (kTcMaxTaps + 1) / 2; i++) {
-            const int tap = 2 * i + w_par;
-            wbits[i] = (tap < a.KHW && cw < a.CW) ? __ldg(src + tap * a.CW) : 0u;
+        for (int i = 0; i < kMyTaps; i++) {
+            const bool tap_ok = (KHW_T ? 2 * i + w_par < KHW_T : 2 * i + w_par < a.KHW) && half_ok;
+            wbits[i] = tap_ok ? __ldg(w_ptr + i * w_tap_stride) : 0u;
         }
-        const long long P = q0 + tid;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const int cwa = 2 * ck + h;
-            abits[h] = (tid < a.rows_a && P < a.NHW && cwa < a.CW) ? __ldg(Ab + ((size_t)s * a.CW + cwa) * a.NHWp + P) : 0u;
+        abits[0] = a_row_ok ? __ldg(a_ptr) : 0u;
+        abits[1] = (a_row_ok && 2 * ld_ck + 1 < a.CW) ? __ldg(a_ptr + a.NHWp) : 0u;
+        // the patch bits stream from HBM: pull the lines of a later step into L2 (one lane per 128-byte line)
+        if (pf_lane && ld_left > kTcPrefetch) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_ptr));
+            if (a.CW > 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_ptr + a.NHWp));
         }
-        // the patch bits stream from HBM: pull the line of a later step into L2 (one lane per 128-byte line)
-        if ((tid & 31) == 0 && tid < a.rows_a && step + kTcPrefetch < a.slots * a.CK) {
-            const int sp = (step + kTcPrefetch) / a.CK, ckp = (step + kTcPrefetch) - sp * a.CK;
-            const long long Pp = P < a.NHW ? P : a.NHW - 1;
-#pragma unroll
-            for (int h = 0; h < 2; h++)
-                if (2 * ckp + h < a.CW)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(Ab + ((size_t)sp * a.CW + 2 * ckp + h) * a.NHWp + Pp));
+        // advance to the next step: next 64-channel chunk of the slot, or chunk 0 of the next slot
+        ld_left--;
+        if (++ld_ck == a.CK) {
+            ld_ck = 0;
+            w_ptr += ((size_t)a.KHW * a.CW - 2 * (a.CK - 1)) * kTcN;
+            a_ptr += (size_t)(a.CW - 2 * (a.CK - 1)) * a.NHWp;
+        } else {
+            w_ptr += 2 * kTcN;
+            a_ptr += (size_t)2 * a.NHWp;
         }
+        pf_ptr += (size_t)a.CW * a.NHWp;
     };
+    // per-thread shared-memory offsets of the expansion targets (buffer 0)
+    const uint32_t b_dst0 = (uint32_t)(((w_par * 4 + 2 * w_half) * kTcN + w_row) * 16);
+    const uint32_t a_dst0 = (uint32_t)tid * 16;
+    const uint32_t a_kcol = (uint32_t)a.rows_a * 16;
+    const bool a_store = tid < a.rows_a;
     auto expand_bits = [&](int buf) {
-        uint8_t *b_s = b_buf(buf), *a_s = a_buf(buf);
+        uint8_t *b_s = b_buf(buf) + b_dst0, *a_s = a_buf(buf) + a_dst0;
 #pragma unroll
-        for (int i = 0; i < (kTcMaxTaps + 1) / 2; i++) {
-            const int tap = 2 * i + w_par;
-            if (tap < a.KHW) {
-                uint8_t *dst = b_s + ((size_t)(tap * 4 + 2 * w_half) * kTcN + w_row) * 16;
+        for (int i = 0; i < kMyTaps; i++) {
+            if (KHW_T ? 2 * i + w_par < KHW_T : 2 * i + w_par < a.KHW) {
+                uint8_t *dst = b_s + i * (2 * 4 * kTcN * 16); // two taps further
                 uint4 lo16, hi16;
                 spread32<kTcMaskW>(wbits[i], lo16, hi16);
                 *reinterpret_cast<uint4 *>(dst) = lo16;
                 *reinterpret_cast<uint4 *>(dst + kTcN * 16) = hi16;
             }
         }
-        if (tid < a.rows_a) {
+        if (a_store) {
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 uint4 lo16, hi16;
                 spread32<kTcMaskA>(abits[h], lo16, hi16);
-                *reinterpret_cast<uint4 *>(a_s + ((size_t)(2 * h) * a.rows_a + tid) * 16) = lo16;
-                *reinterpret_cast<uint4 *>(a_s + ((size_t)(2 * h + 1) * a.rows_a + tid) * 16) = hi16;
+                *reinterpret_cast<uint4 *>(a_s + (2 * h) * a_kcol) = lo16;
+                *reinterpret_cast<uint4 *>(a_s + (2 * h + 1) * a_kcol) = hi16;
             }
         }
     };
@@ -235,14 +261,18 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         REXSC_TMEM_LD16_PACKED(v1, taddr + 32u);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-            uint32_t t0 = __vminu2(v0[j], n2), t1 = __vminu2(v1[j], n2);
-            if (a.descale_each) {
-                t0 = (t0 >> kTcScaleLog2) & kDescaleMask;
-                t1 = (t1 >> kTcScaleLog2) & kDescaleMask;
+        if (!a.descale_each) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                acc[j] += __vminu2(v0[j], n2);
+                acc[16 + j] += __vminu2(v1[j], n2);
             }
-            acc[j] += t0;
-            acc[16 + j] += t1;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                acc[j] += (__vminu2(v0[j], n2) >> kTcScaleLog2) & kDescaleMask;
+                acc[16 + j] += (__vminu2(v1[j], n2) >> kTcScaleLog2) & kDescaleMask;
+            }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
@@ -288,56 +318,73 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 }
             }
         }
+        // the commits arrive on their barriers when every MMA issued so far by this warp has completed
         asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
-                     "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(&bars[buf]))
+                     "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(&bar_empty[buf]))
                      : "memory");
+        if (ck == a.CK - 1)
+            asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                         "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(&bar_tfull[s & 1]))
+                         : "memory");
     };
 
     bool failed = false;
     const int n_steps = a.slots * a.CK;
-    // prologue: operands of step 0 in buffer 0, bits of step 1 in registers
-    if (warp < kTcWorkers / 32) {
-        load_bits(0);
-        expand_bits(0);
-        if (n_steps > 1) load_bits(1);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    for (int step = 0; step < n_steps; step++) {
-        if (warp >= kTcWorkers / 32) {
-            // (a) feed the tensor core: the MMAs of this step queue up behind those of the previous one
-            // the whole warp runs the loop (its operands stay warp-uniform); one elected lane issues
+    // The warps run unsynchronised; every dependence is an mbarrier phase.  Phase parities: barrier index b is used
+    // by steps (or slots) b, b + 2, ...; its k-th completion has parity k & 1.  A timed-out wait ends the warp's
+    // loop; the warps that depend on it time out in turn, so everybody reaches the end of the kernel.
+    auto wait_on = [&](uint64_t *bar, int k) {
+        const bool ok = tc_wait(saddr(bar), (uint32_t)(k & 1));
+        return __all_sync(0xffffffffu, ok) != 0;
+    };
+    auto warp_arrive = [&](uint64_t *bar) {
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
+    };
+    if (warp >= kTcWorkers / 32) {
+        // ---- MMA-issuing warps: operands ready -> accumulator free -> issue -> commit ----
+        for (int step = 0; step < n_steps && !failed; step++) {
+            const int s = step / a.CK, ck = step - s * a.CK;
+            if (!wait_on(&bar_full[step & 1], step >> 1)) { failed = true; break; }
+            if (ck == 0 && s >= 2 && !wait_on(&bar_tfree[s & 1], (s >> 1) - 1)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_mmas(step);
-            __syncwarp();
-        } else {
-            // (b) the previous step's MMAs must be done before its operand buffer is rewritten / its slot is folded
-            if (step > 0) {
-                if (!tc_wait(saddr(&bars[(step - 1) & 1]), (uint32_t)(((step - 1) >> 1) & 1))) failed = true;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            // (c) next step's operands into the other buffer, bits of the step after that on their way
-            if (step + 1 < n_steps) {
-                expand_bits((step + 1) & 1);
-                if (step + 2 < n_steps) load_bits(step + 2);
-            }
-            // (d) fold the slot that the previous step completed
-            if (step > 0 && (step % a.CK) == 0 && !failed) slot_epilogue(((step - 1) / a.CK) & 1);
         }
+    } else {
+        // ---- expanding / folding warps ----
+        load_bits();
+        expand_bits(0);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        failed = __syncthreads_or(failed ? 1 : 0) != 0;
-        if (failed) break;
+        warp_arrive(&bar_full[0]);
+        if (n_steps > 1) load_bits();
+        for (int step = 0; step < n_steps && !failed; step++) {
+            // operands of the next step go into the buffer that the previous step's MMAs have finished reading
+            if (step + 1 < n_steps) {
+                if (step > 0 && !wait_on(&bar_empty[(step - 1) & 1], (step - 1) >> 1)) { failed = true; break; }
+                expand_bits((step + 1) & 1);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                warp_arrive(&bar_full[(step + 1) & 1]);
+                if (step + 2 < n_steps) load_bits();
+            }
+            // fold the slot that the previous step completed and hand its accumulators back
+            if (step > 0 && (step % a.CK) == 0) {
+                const int s = (step - 1) / a.CK;
+                if (!wait_on(&bar_tfull[s & 1], s >> 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                slot_epilogue(s & 1);
+                warp_arrive(&bar_tfree[s & 1]);
+            }
+        }
+        if (!failed) {
+            const int s = a.slots - 1;
+            if (!wait_on(&bar_tfull[s & 1], s >> 1)) failed = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (!failed) slot_epilogue(s & 1);
+        }
     }
-    if (!failed) {
-        // the last step's MMAs, then the last slot
-        if (!tc_wait(saddr(&bars[(n_steps - 1) & 1]), (uint32_t)(((n_steps - 1) >> 1) & 1))) failed = true;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        failed = __syncthreads_or(failed ? 1 : 0) != 0;
-        if (!failed && warp < kTcWorkers / 32) slot_epilogue((a.slots - 1) & 1);
-    }
+    if (failed && lane == 0) atomicExch(status, 4);
 
+    // a failed warp leaves its share of the output unwritten; the status word reports it
     if (!failed && warp < kTcWorkers / 32) {
         // ---- store: row = one stored-grid position; it is an output pixel iff it is the tap-(0,0) origin of one ----
         if (!a.descale_each) {
@@ -376,8 +423,6 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 }
             }
         }
-    } else if (failed && tid == 0) {
-        atomicExch(status, 4);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -463,7 +508,7 @@ __global__ void __launch_bounds__(256) bitplane_weight_kernel(const uint32_t *__
     mine = __byte_perm(__brev(mine), 0, 0x0123);
     mine = ((mine & 0x0f0f0f0fu) << 4) | ((mine >> 4) & 0x0f0f0f0fu);
     const int slots = words * 32;
-    Wb[(((size_t)nchunk * slots + wd * 32 + lane) * kTcN + row) * ((size_t)KHW * CW) + tap * CW + cw] = mine;
+    Wb[(((size_t)nchunk * slots + wd * 32 + lane) * ((size_t)KHW * CW) + tap * CW + cw) * kTcN + row] = mine;
 }
 
 // Tensor-pipe issue-rate probe: back-to-back int8 MMAs (M128 x N x K32) on fixed shared-memory operands.
@@ -533,7 +578,7 @@ __global__ void __launch_bounds__(128, 2) mma_probe_kernel(int iters, int n_cols
 size_t tc_smem_bytes(const ConvPlan &p)
 {
     const int rows_a = (kTcM + p.max_tap + 7) / 8 * 8;
-    const size_t need = 2 * ((size_t)4 * rows_a * 16 + (size_t)p.KHW * 4 * kTcN * 16) + 16 + 8 + 128;
+    const size_t need = 2 * ((size_t)4 * rows_a * 16 + (size_t)p.KHW * 4 * kTcN * 16) + 8 * 8 + 8 + 128;
     // the kernel owns the SM's whole tensor memory: ask for enough shared memory that no second CTA is co-scheduled
     return need > 120 * 1024 ? need : 120 * 1024;
 }
