@@ -28,10 +28,9 @@ static int resolve_kernel(const rexsc_sc_conv_desc *desc, const ConvPlan &p)
     case REXSC_KERNEL_TILED: return tiled_ok ? (int)REXSC_KERNEL_TILED : (int)REXSC_E_UNSUPPORTED;
     case REXSC_KERNEL_TENSOR: return p.tc_ok ? (int)REXSC_KERNEL_TENSOR : (int)REXSC_E_UNSUPPORTED;
     default:
-        // AUTO: the tensor-core kernel wins where its row space is dense (stride 1, or 1x1 filters whose input is
-        // stored subsampled) and the dot product fills its 64-channel K chunks; strided 3x3 layers keep the ALU
-        // kernel, which skips the pixels a stride jumps over.
-        if (p.tc_ok && p.C >= 32 && ((p.sh == 1 && p.sw == 1) || p.KHW == 1)) return REXSC_KERNEL_TENSOR;
+        // AUTO: the tensor-core kernel wherever it fits (up to 9 taps, any stride) and the dot product fills its
+        // 32-channel K words; thin inputs and large filters keep the ALU kernels.
+        if (p.tc_ok && p.C >= 32) return REXSC_KERNEL_TENSOR;
         return tiled_ok ? (int)REXSC_KERNEL_TILED : (int)REXSC_KERNEL_DIRECT;
     }
 }

@@ -4,24 +4,31 @@
 //     count_t[pixel][sign, co] = sum_{tap, c} a_t[pixel + tap][c] * w_t[sign, co][tap, c],
 // and only min(count_t, n) is non-linear -- it is applied to the finished accumulator of every slot:
 //     out[pixel][sign, co] = sum_t min(count_t, n)            (sc_device.cu:127-151 of the reference).
-// So every slot is one int8 GEMM, M = 128 stored-grid positions (TMEM lanes), N = 128 (64 output channels x
-// {positive, negative} weight stream), K = taps x channels, issued as tcgen05.mma.kind::i8 M128 N128 K32.
+// So every slot is one int8 GEMM, M = output-pixel candidates (TMEM lanes, 128 per MMA), N = 128 (64 output
+// channels x {positive, negative} weight stream), K = taps x channels, issued as tcgen05.mma.kind::i8 M128 N128 K32.
+//
+// Rows.  The M dimension runs over the "origin grid": per image Ho x Wo candidates (i, j), candidate (i, j) being
+// the padded-input pixel (i*stride_h, j*stride_w), i.e. the top-left tap of output pixel (i, j) when i < OH and
+// j < OW (other rows are computed and dropped; they are the padding of the grid, a few percent).  A CTA owns 256
+// consecutive candidates.
 //
 // Operands are generated in shared memory from bit planes (one bit per element and slot, 32 channels per word):
-//   A_t  the slot's activation bits of the tile's patch, expanded to bytes as 16-byte K-columns
-//        [16-channel column][patch row][16 B] (unswizzled K-major).  Rows sit 16 bytes apart, so the operand of
-//        filter tap (kh, kw) is the SAME buffer with its start address moved by tap_offset rows: no im2col.
+//   A_t  the slot's activation bits of the tile's patch as 16-byte K-columns [16-channel column][patch row][16 B]
+//        (unswizzled K-major, rows 16 bytes apart).  The patch is kept as one plane per stride residue
+//        (kh % stride_h, kw % stride_w); inside a plane, row r holds the pixel of that residue that belongs to
+//        candidate o0 + r.  The operand of filter tap (kh, kw) is then the SAME buffer with its start address moved
+//        to plane(kh % sh, kw % sw) + (kh / sh) * Wo + kw / sw rows: no im2col, for any stride.
 //   B_t  the slot's weight bits, [tap][16-channel column][128 rows][16 B].
-// The M dimension runs over consecutive positions of the stored (padded) pixel grid; positions that are not the
-// origin of an output pixel produce rows that are computed and dropped.
+// Operand bytes are 0 or a power of two (see kTcMaskA), the accumulators hold 8 * count.
 //
-// One CTA per SM, 512 threads, 256 stored-grid positions (two MMA row blocks sharing one weight operand).  Operand
-// buffers are double-buffered: while the tensor core works through the MMAs of pipeline step i (one slot x one
-// 64-channel chunk), all threads expand the operands of step i+1 and fold the counts of the slot that just
-// finished (TMEM accumulators alternate between two 256-column buffers); the bit words of step i+2 are already
-// on their way from L2.  Warp w reads TMEM lanes 32*(w%4).., row block (w/4)%2, columns 64*(w/8)..
+// One CTA per SM: 16 warps expand operands and fold counts, 2 warps issue MMAs (one per 128-row block; a single
+// thread cannot keep the tensor core busy with 128-column MMAs).  A pipeline step is one slot x one chunk of 32 or
+// 64 channels.  Operand buffers and accumulators are double-buffered and every dependence is an mbarrier phase:
+// while the tensor core works through step i, the expanding warps write the operands of step i+1, fold the slot
+// that finished, and already hold the bit words of step i+2 in registers.
 // Every wait is bounded; on a time-out the CTA reports through the status word, frees its TMEM and returns.
 #include "common.cuh"
+#include <type_traits>
 
 namespace rexsc {
 
@@ -29,21 +36,28 @@ namespace {
 
 constexpr int kTcWorkers = 512;             // threads that expand operands and fold counts
 constexpr int kTcThreads = kTcWorkers + 64; // + two warps that only issue MMAs, one per 128-row block
-constexpr int kTcM = 256;          // stored-grid positions per CTA: two MMA row blocks that share one weight operand
+constexpr int kTcM = 256;          // candidates per CTA: two MMA row blocks that share one weight operand
 constexpr int kTcSub = 128;        // rows of one MMA (TMEM lanes)
 constexpr int kTcCout = 64;        // output channels per CTA
 constexpr int kTcN = 2 * kTcCout;  // MMA N: positive block [0,64), negative block [64,128)
-constexpr int kTcMaxTaps = 9;
-constexpr int kTcPrefetch = 4; // pipeline steps between the L2 prefetch of patch bits and their use      // filter taps whose weight operand is staged at once
+constexpr int kTcMaxTaps = 9;      // filter taps whose weight operand is staged at once
+constexpr int kTcMaxARows = 3;     // patch rows per expanding thread (all residue planes together)
+constexpr int kTcMaxBWords = 5;    // weight words per expanding thread and step
+constexpr int kTcPrefetch = 4;     // pipeline steps between the L2 prefetch of patch bits and their use
 constexpr uint32_t kTcWaitLimit = 1u << 18; // try_wait attempts before a wait gives up (each may sleep kTcSuspendNs)
 constexpr uint32_t kTcSuspendNs = 4000;    // a waiting warp sleeps in the barrier unit instead of spinning on issue slots
 
 struct TcArgs {
-    int OH, OW, sh, sw, KH, KW, KHW, Co, CW, CK;
-    int nrh, Wq, Hrows, Wrow, max_tap;
-    int rows_a;      // patch rows staged per slot: kTcM + max_tap, rounded up to 8
+    int OH, OW, KHW, Co, CW;
+    int KWc;         // 32-channel words per pipeline step: 2, or 1 when shared memory is short
+    int CK;          // pipeline steps per slot = ceil(CW / KWc)
+    int nrh, nrw, Wq, Hrows, Wrow; // stored pixel grid (see tap_offset in common.cuh)
+    int Ho, Wo;      // origin grid of one image
+    int Mh;          // patch rows per residue plane: kTcM + largest in-plane tap shift, rounded up to 8
+    int rows_a;      // patch rows of all planes
     int slots, n_or;
-    long long NHW, NHWp;
+    long long total_o; // candidates = N * Ho * Wo
+    long long NHWp;
     int out_nhwc;
     int descale_each; // 1: running sums would overflow 16 bits in accumulator units, so every slot is descaled
     int tap_off[kTcMaxTaps]; // patch-row offset of every tap (kernel parameters are warp-uniform by construction)
@@ -124,15 +138,17 @@ __device__ __forceinline__ void spread32(uint32_t h, uint4 &lo16, uint4 &hi16)
         : "memory")
 
 // KHW_T: taps known at compile time (9, 1) or 0 for any tap count up to kTcMaxTaps
-template <int KHW_T>
+// KWC:   32-channel words per pipeline step (TcArgs::KWc);  RA: patch rows per expanding thread (1 .. kTcMaxARows)
+template <int KHW_T, int KWC, int RA>
 __global__ void __launch_bounds__(kTcThreads, 1)
 sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__restrict__ Wb,
                   int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((128u - (saddr(smem_raw) & 127u)) & 127u);
-    const uint32_t a_bytes = 4u * (uint32_t)a.rows_a * 16u;          // [4][rows_a][16]
-    const uint32_t b_bytes = (uint32_t)a.KHW * 4u * kTcN * 16u;      // [KHW][4][128][16]
+    const int KHW = KHW_T ? KHW_T : a.KHW;
+    const uint32_t a_bytes = 2u * (uint32_t)KWC * (uint32_t)a.rows_a * 16u; // [2*KWc columns][rows_a][16]
+    const uint32_t b_bytes = (uint32_t)KHW * 2u * (uint32_t)KWC * kTcN * 16u; // [KHW][2*KWc columns][128][16]
     auto a_buf = [&](int buf) { return smem + (uint32_t)buf * a_bytes; };
     auto b_buf = [&](int buf) { return smem + 2 * a_bytes + (uint32_t)buf * b_bytes; };
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 2 * a_bytes + 2 * b_bytes);
@@ -141,7 +157,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const int tid = threadIdx.x, lane = tid & 31;
     // the shuffle tells the compiler what it cannot see: the warp index is the same in every lane
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const long long q0 = (long long)blockIdx.x * kTcM; // first stored-grid position of the tile
+    const long long o0 = (long long)blockIdx.x * kTcM; // first candidate of the tile
     const int nc = blockIdx.y;                         // 64-channel output chunk
 
     // mbarriers (index = operand buffer or accumulator buffer):
@@ -173,7 +189,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // instruction descriptor: int32 accumulators, signed int8 operands, both K-major, N = 128, M = 128
     const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcN >> 3) << 17) | ((uint32_t)(kTcSub >> 4) << 24);
     const uint32_t a_lbo = (uint32_t)a.rows_a * 16, b_lbo = kTcN * 16;
-    const int wrow_words = a.KHW * a.CW;               // words per weight row and slot
+    const int wrow_words = KHW * a.CW;                 // weight words per row and slot
     const uint32_t *Wchunk = Wb + (size_t)nc * a.slots * kTcN * wrow_words;
 
     // running sums: this thread owns row block (warp/4)%2, TMEM lane 32*(warp%4)+lane and 64 columns (warp/8 = 0:
@@ -184,72 +200,101 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const uint32_t my_tcol = ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(((warp >> 2) & 1) * kTcN + (warp >> 3) * 64);
     const uint32_t n2 = ((uint32_t)a.n_or << kTcScaleLog2) * 0x00010001u; // the clamp, in accumulator units, twice
 
-    // Bit words of a step are fetched into registers two steps before their MMAs so that L2 latency is hidden.
-    //   weights: thread -> (row = tid & 127, word half = (tid >> 7) & 1, tap parity = tid >> 8), every other tap
-    //   patch:   thread -> row tid, both words of the chunk
-    // The loads walk the steps in order, so their addresses are kept as running pointers (no per-step division or
-    // 64-bit multiplication): ld_ck / ld_left describe the step that the next load_bits() call fetches.
-    const int w_row = tid & (kTcN - 1), w_half = (tid >> 7) & 1, w_par = tid >> 8;
-    constexpr int kMyTaps = (kTcMaxTaps + 1) / 2;
-    uint32_t wbits[kMyTaps], abits[2];
-    const size_t w_tap_stride = (size_t)2 * a.CW * kTcN;                 // two taps further
-    const uint32_t *w_ptr = Wchunk + ((size_t)w_par * a.CW + w_half) * kTcN + w_row; // slot 0, chunk 0, first own tap
-    const long long P = q0 + tid;
-    const bool a_row_ok = tid < a.rows_a && P < a.NHW;
-    const uint32_t *a_ptr = Ab + (a_row_ok ? P : 0);                      // slot 0, word 0
-    const uint32_t *pf_ptr = Ab + (P < a.NHW ? P : a.NHW - 1) + (size_t)kTcPrefetch * a.CW * a.NHWp; // CK == 1 only
-    const bool pf_lane = lane == 0 && tid < a.rows_a && a.CK == 1;
+    // ---- what an expanding thread loads and writes -------------------------------------------------------------
+    // Bit words of a step are fetched into registers two steps before their MMAs so that L2 latency is hidden; the
+    // loads walk the steps in order, so the step-dependent part of every address is a running pointer.
+    //   weights: item e = tid + 512*i, row = e & 127, (tap, word) = e >> 7  -> wbits[i]
+    //   patch:   row g = tid + 512*r of the residue planes                  -> abits[r][word]
+    uint32_t wbits[kTcMaxBWords], abits[RA][KWC];
+    const int w_row = tid & (kTcN - 1), w_rest0 = tid >> 7;               // (tap, word) index of item 0
+    const int w_half = KWC == 2 ? (w_rest0 & 1) : 0;
+    const int w_tap0 = KWC == 2 ? (w_rest0 >> 1) : w_rest0;
+    const int w_items = KHW * KWC;                                      // (tap, word) pairs per step
+    const size_t w_item_stride = (size_t)(4 / KWC) * a.CW * kTcN;       // item i -> i + 1: 4 pairs further
+    const uint32_t *w_ptr = Wchunk + ((size_t)w_tap0 * a.CW + w_half) * kTcN + w_row; // slot 0, chunk 0, item 0
+    uint32_t a_off[RA]; // stored-grid position of the thread's patch rows, ~0u: outside the tensor
+#pragma unroll
+    for (int r = 0; r < RA; r++) {
+        const int g = tid + kTcWorkers * r;
+        a_off[r] = ~0u;
+        if (g < a.rows_a) {
+            const int plane = g / a.Mh, q = g - plane * a.Mh;
+            const long long o = o0 + q;
+            if (o < a.total_o) {
+                const int j = (int)(o % a.Wo);
+                const long long t = o / a.Wo;
+                const int i = (int)(t % a.Ho);
+                const long long n = t / a.Ho;
+                const int rh = plane / a.nrw, rw = plane - rh * a.nrw;
+                a_off[r] = (uint32_t)((n * a.Hrows + (long long)i * a.nrh + rh) * a.Wrow + rw * a.Wq + j);
+            }
+        }
+    }
+    const uint32_t *a_plane = Ab;                                          // bit plane of slot 0, word 0
+    const bool pf_on = (a.CW % KWC) == 0;                                // planes are then visited in storage order
+    const uint32_t *pf_plane = Ab + (size_t)kTcPrefetch * KWC * a.NHWp;
     int ld_ck = 0, ld_left = a.slots * a.CK;
     auto load_bits = [&]() {
-        const bool half_ok = 2 * ld_ck + w_half < a.CW;
+        const int words_left = a.CW - ld_ck * KWC; // words of this chunk that exist
 #pragma unroll
-        for (int i = 0; i < kMyTaps; i++) {
-            const bool tap_ok = (KHW_T ? 2 * i + w_par < KHW_T : 2 * i + w_par < a.KHW) && half_ok;
-            wbits[i] = tap_ok ? __ldg(w_ptr + i * w_tap_stride) : 0u;
+        for (int i = 0; i < kTcMaxBWords; i++) {
+            const bool ok = w_rest0 + 4 * i < w_items && w_half < words_left;
+            wbits[i] = ok ? __ldg(w_ptr + i * w_item_stride) : 0u;
         }
-        abits[0] = a_row_ok ? __ldg(a_ptr) : 0u;
-        abits[1] = (a_row_ok && 2 * ld_ck + 1 < a.CW) ? __ldg(a_ptr + a.NHWp) : 0u;
+#pragma unroll
+        for (int r = 0; r < RA; r++) {
+            abits[r][0] = a_off[r] != ~0u ? __ldg(a_plane + a_off[r]) : 0u;
+            if (KWC == 2) abits[r][KWC - 1] = (a_off[r] != ~0u && words_left > 1) ? __ldg(a_plane + a.NHWp + a_off[r]) : 0u;
+        }
         // the patch bits stream from HBM: pull the lines of a later step into L2 (one lane per 128-byte line)
-        if (pf_lane && ld_left > kTcPrefetch) {
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_ptr));
-            if (a.CW > 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_ptr + a.NHWp));
+        if (pf_on && lane == 0 && ld_left > kTcPrefetch) {
+#pragma unroll
+            for (int r = 0; r < RA; r++)
+                if (a_off[r] != ~0u) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_plane + a_off[r]));
+                    if (KWC == 2) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf_plane + a.NHWp + a_off[r]));
+                }
         }
-        // advance to the next step: next 64-channel chunk of the slot, or chunk 0 of the next slot
+        // advance to the next step: next chunk of the slot, or chunk 0 of the next slot
         ld_left--;
         if (++ld_ck == a.CK) {
             ld_ck = 0;
-            w_ptr += ((size_t)a.KHW * a.CW - 2 * (a.CK - 1)) * kTcN;
-            a_ptr += (size_t)(a.CW - 2 * (a.CK - 1)) * a.NHWp;
+            w_ptr += ((size_t)wrow_words - (size_t)KWC * (a.CK - 1)) * kTcN;
+            a_plane += (size_t)(a.CW - KWC * (a.CK - 1)) * a.NHWp;
         } else {
-            w_ptr += 2 * kTcN;
-            a_ptr += (size_t)2 * a.NHWp;
+            w_ptr += (size_t)KWC * kTcN;
+            a_plane += (size_t)KWC * a.NHWp;
         }
-        pf_ptr += (size_t)a.CW * a.NHWp;
+        pf_plane += (size_t)KWC * a.NHWp;
     };
     // per-thread shared-memory offsets of the expansion targets (buffer 0)
-    const uint32_t b_dst0 = (uint32_t)(((w_par * 4 + 2 * w_half) * kTcN + w_row) * 16);
-    const uint32_t a_dst0 = (uint32_t)tid * 16;
+    const uint32_t b_dst0 = (uint32_t)(((w_tap0 * 2 * KWC + 2 * w_half) * kTcN + w_row) * 16);
     const uint32_t a_kcol = (uint32_t)a.rows_a * 16;
-    const bool a_store = tid < a.rows_a;
     auto expand_bits = [&](int buf) {
-        uint8_t *b_s = b_buf(buf) + b_dst0, *a_s = a_buf(buf) + a_dst0;
+        uint8_t *b_s = b_buf(buf) + b_dst0, *a_s = a_buf(buf) + (uint32_t)tid * 16;
 #pragma unroll
-        for (int i = 0; i < kMyTaps; i++) {
-            if (KHW_T ? 2 * i + w_par < KHW_T : 2 * i + w_par < a.KHW) {
-                uint8_t *dst = b_s + i * (2 * 4 * kTcN * 16); // two taps further
+        for (int i = 0; i < kTcMaxBWords; i++) {
+            if (w_rest0 + 4 * i < w_items) {
+                uint8_t *dst = b_s + i * (8 * kTcN * 16); // 4 (tap, word) pairs = 8 K-columns further
                 uint4 lo16, hi16;
                 spread32<kTcMaskW>(wbits[i], lo16, hi16);
                 *reinterpret_cast<uint4 *>(dst) = lo16;
                 *reinterpret_cast<uint4 *>(dst + kTcN * 16) = hi16;
             }
         }
-        if (a_store) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
+        for (int r = 0; r < RA; r++) {
+            if (tid + kTcWorkers * r < a.rows_a) {
+                uint8_t *dst = a_s + r * (kTcWorkers * 16);
                 uint4 lo16, hi16;
-                spread32<kTcMaskA>(abits[h], lo16, hi16);
-                *reinterpret_cast<uint4 *>(a_s + (2 * h) * a_kcol) = lo16;
-                *reinterpret_cast<uint4 *>(a_s + (2 * h + 1) * a_kcol) = hi16;
+                spread32<kTcMaskA>(abits[r][0], lo16, hi16);
+                *reinterpret_cast<uint4 *>(dst) = lo16;
+                *reinterpret_cast<uint4 *>(dst + a_kcol) = hi16;
+                if (KWC == 2) {
+                    spread32<kTcMaskA>(abits[r][KWC - 1], lo16, hi16);
+                    *reinterpret_cast<uint4 *>(dst + 2 * a_kcol) = lo16;
+                    *reinterpret_cast<uint4 *>(dst + 3 * a_kcol) = hi16;
+                }
             }
         }
     };
@@ -260,7 +305,6 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         REXSC_TMEM_LD16_PACKED(v0, taddr);
         REXSC_TMEM_LD16_PACKED(v1, taddr + 32u);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
         if (!a.descale_each) {
 #pragma unroll
             for (int j = 0; j < 16; j++) {
@@ -286,16 +330,17 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     uint32_t a_tap[kTcMaxTaps];
 #pragma unroll
     for (int tap = 0; tap < kTcMaxTaps; tap++)
-        a_tap[tap] = (my_sub >= 0 && tap < a.KHW) ? (uint32_t)(my_sub * kTcSub + a.tap_off[tap]) : 0u;
+        a_tap[tap] = (my_sub >= 0 && tap < KHW) ? (uint32_t)(my_sub * kTcSub + a.tap_off[tap]) : 0u;
     const uint64_t da_proto = desc_interleaved(saddr(a_buf(0)), a_lbo), db_proto = desc_interleaved(saddr(b_buf(0)), b_lbo);
     const uint32_t da_hi = (uint32_t)(da_proto >> 32), db_hi = (uint32_t)(db_proto >> 32);
-    const uint32_t a_kk = 2u * (uint32_t)a.rows_a; // rows between the two 32-channel halves of a chunk
+    const uint32_t a_kk = 2u * (uint32_t)a.rows_a;             // rows between the 32-channel words of a chunk
+    const uint32_t b_tap = 2u * (uint32_t)KWC * kTcN;        // rows between taps of the weight operand
     auto issue_mmas = [&](int step) {
         const int s = step / a.CK, ck = step - s * a.CK, buf = step & 1;
         const uint32_t da_lo = (uint32_t)da_proto + (uint32_t)buf * (a_bytes >> 4);
         const uint32_t db_lo = (uint32_t)db_proto + (uint32_t)buf * (b_bytes >> 4);
         const uint32_t d_addr = tmem_base + (uint32_t)((s & 1) * 2 * kTcN + my_sub * kTcN);
-        const bool two = 2 * ck + 1 < a.CW; // channels in the second half of the chunk
+        const bool two = KWC == 2 && ck * 2 + 1 < a.CW; // a second 32-channel word in this chunk
         const uint32_t first_acc = ck > 0 ? 1u : 0u;
 #pragma unroll
         for (int tap = 0; tap < (KHW_T ? KHW_T : kTcMaxTaps); tap++) {
@@ -304,7 +349,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 for (int kk = 0; kk < 2; kk++) {
                     if (kk == 1 && !two) break;
                     const uint32_t alo = da_lo + a_tap[tap] + (kk ? a_kk : 0u);
-                    const uint32_t blo = db_lo + (uint32_t)((tap * 4 + 2 * kk) * kTcN);
+                    const uint32_t blo = db_lo + (uint32_t)tap * b_tap + (uint32_t)(2 * kk * kTcN);
                     const uint32_t accumulate = (tap > 0 || kk > 0) ? 1u : first_acc;
                     asm volatile(
                         "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\t"
@@ -386,22 +431,21 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
 
     // a failed warp leaves its share of the output unwritten; the status word reports it
     if (!failed && warp < kTcWorkers / 32) {
-        // ---- store: row = one stored-grid position; it is an output pixel iff it is the tap-(0,0) origin of one ----
+        // ---- store: row = one candidate of the origin grid; it is an output pixel iff i < OH and j < OW ----
         if (!a.descale_each) {
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[j] = (acc[j] >> kTcScaleLog2) & kDescaleMask;
         }
-        const long long q = q0 + ((warp >> 2) & 1) * kTcSub + (warp & 3) * 32 + lane;
-        if (q < a.NHW) {
-            const int colp = (int)(q % a.Wrow);
-            const long long t = q / a.Wrow;
-            const int rowp = (int)(t % a.Hrows);
-            const long long n = t / a.Hrows;
-            const int oh = rowp / a.nrh;
-            if (colp < a.OW && rowp % a.nrh == 0 && oh < a.OH) {
+        const long long o = o0 + ((warp >> 2) & 1) * kTcSub + (warp & 3) * 32 + lane;
+        if (o < a.total_o) {
+            const int ow = (int)(o % a.Wo);
+            const long long t = o / a.Wo;
+            const int oh = (int)(t % a.Ho);
+            const long long n = t / a.Ho;
+            if (ow < a.OW && oh < a.OH) {
                 const int co0 = nc * kTcCout;
                 const size_t ohw = (size_t)a.OH * a.OW;
-                const size_t m = ((size_t)n * a.OH + oh) * a.OW + colp;
+                const size_t m = ((size_t)n * a.OH + oh) * a.OW + ow;
                 int16_t *dst = (warp >> 3) ? out_neg : out_pos;
                 if (a.out_nhwc) {
                     int16_t *row = dst + m * a.Co + co0;
@@ -418,7 +462,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
 #pragma unroll
                     for (int j = 0; j < 64; j++)
                         if (co0 + j < a.Co)
-                            dst[((size_t)n * a.Co + co0 + j) * ohw + (size_t)oh * a.OW + colp] =
+                            dst[((size_t)n * a.Co + co0 + j) * ohw + (size_t)oh * a.OW + ow] =
                                 (int16_t)((acc[j >> 1] >> (16 * (j & 1))) & 0xffffu);
                 }
             }
@@ -575,12 +619,50 @@ __global__ void __launch_bounds__(128, 2) mma_probe_kernel(int iters, int n_cols
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)n_cols) : "memory");
 }
 
-size_t tc_smem_bytes(const ConvPlan &p)
+// geometry of the tensor-core kernel for one plan; ok = false when the layer does not fit
+struct TcGeom {
+    bool ok;
+    int planes, Ho, Wo, Mh, rows_a, KWc, CK, CW;
+    size_t smem;
+    int tap_off[kTcMaxTaps];
+};
+
+TcGeom tc_geometry(const ConvPlan &p)
 {
-    const int rows_a = (kTcM + p.max_tap + 7) / 8 * 8;
-    const size_t need = 2 * ((size_t)4 * rows_a * 16 + (size_t)p.KHW * 4 * kTcN * 16) + 8 * 8 + 8 + 128;
-    // the kernel owns the SM's whole tensor memory: ask for enough shared memory that no second CTA is co-scheduled
-    return need > 120 * 1024 ? need : 120 * 1024;
+    TcGeom g{};
+    g.ok = false;
+    if (p.KHW > kTcMaxTaps || p.KHW < 1) return g;
+    g.planes = p.nrh * p.nrw;
+    g.Ho = p.Hrows / p.nrh;
+    g.Wo = p.Wq;
+    int max_shift = 0;
+    for (int kh = 0; kh < p.KH; kh++)
+        for (int kw = 0; kw < p.KW; kw++) {
+            const int shift = (kh / p.sh) * g.Wo + kw / p.sw;
+            if (shift > max_shift) max_shift = shift;
+        }
+    g.Mh = (kTcM + max_shift + 7) / 8 * 8;
+    g.rows_a = g.planes * g.Mh;
+    if (g.rows_a > kTcMaxARows * kTcWorkers) return g;
+    for (int t = 0; t < kTcMaxTaps; t++) g.tap_off[t] = 0;
+    for (int kh = 0; kh < p.KH; kh++)
+        for (int kw = 0; kw < p.KW; kw++) {
+            const int plane = (kh % p.sh) * p.nrw + kw % p.sw; // residues below nrh / nrw by construction of the grid
+            g.tap_off[kh * p.KW + kw] = plane * g.Mh + (kh / p.sh) * g.Wo + kw / p.sw;
+        }
+    g.CW = (p.C + 31) / 32;
+    for (int kwc = g.CW >= 2 ? 2 : 1; kwc >= 1; kwc--) {
+        const size_t need = 2 * ((size_t)2 * kwc * g.rows_a * 16 + (size_t)p.KHW * 2 * kwc * kTcN * 16) + 8 * 8 + 8 + 128;
+        if (need <= 227 * 1024 && p.KHW * kwc <= 4 * kTcMaxBWords) {
+            g.KWc = kwc;
+            g.CK = (g.CW + kwc - 1) / kwc;
+            // the kernel owns the SM's whole tensor memory: ask for enough shared memory that no second CTA is co-scheduled
+            g.smem = need > 120 * 1024 ? need : 120 * 1024;
+            g.ok = true;
+            break;
+        }
+    }
+    return g;
 }
 
 } // namespace
@@ -597,14 +679,16 @@ int launch_mma_probe(int blocks, int iters, int n_cols, uint32_t *d_sink, cudaSt
 bool conv_tc_supported(const ConvPlan &p)
 {
     if (p.n_or < 1) return false;
-    if (p.KHW > kTcMaxTaps) return false;
-    if (tc_smem_bytes(p) > 227 * 1024) return false;
-    if (kTcM + p.max_tap > kTcWorkers) return false;                          // patch rows: one per thread
+    if (p.Hrows % p.nrh != 0) return false;
+    const TcGeom g = tc_geometry(p);
+    if (!g.ok) return false;
     const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;                   // largest per-slot contribution
     if ((long long)p.words * 32 * cap > 65535) return false;                  // 16-bit running sums
     if (((long long)p.Kdot << kTcScaleLog2) > 65535) return false;            // 16-bit packed accumulator reads
     if (p.Kdot > (1 << 24)) return false;
-    if ((p.NHW + kTcM - 1) / kTcM > 0x7fffffffLL) return false;
+    const long long total_o = (long long)p.N * g.Ho * g.Wo;
+    if ((total_o + kTcM - 1) / kTcM > 0x7fffffffLL) return false;
+    if (p.NHWp > 0xfffffffeLL) return false;                                  // 32-bit position offsets
     return true;
 }
 
@@ -644,30 +728,37 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
                    int *d_status, cudaStream_t st)
 {
     if (!conv_tc_supported(p)) return REXSC_E_UNSUPPORTED;
-    const int CW = (p.C + 31) / 32, NC = (p.Co + kTcCout - 1) / kTcCout;
+    const TcGeom g = tc_geometry(p);
+    const int CW = g.CW, NC = (p.Co + kTcCout - 1) / kTcCout;
     const int slots = p.words * 32;
     const uint32_t *Ab = static_cast<const uint32_t *>(d_tc_ws);
     const uint32_t *Wb = reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(d_tc_ws) +
                                                             align_up((size_t)slots * CW * p.NHWp * 4, 256));
     TcArgs a;
-    a.OH = p.OH; a.OW = p.OW; a.sh = p.sh; a.sw = p.sw; a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.Co = p.Co;
-    a.CW = CW; a.CK = (CW + 1) / 2;
-    a.nrh = p.nrh; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow; a.max_tap = p.max_tap;
-    a.rows_a = (kTcM + p.max_tap + 7) / 8 * 8;
-    a.slots = slots; a.n_or = p.n_or;
-    a.NHW = p.NHW; a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
+    a.OH = p.OH; a.OW = p.OW; a.KHW = p.KHW; a.Co = p.Co;
+    a.CW = CW; a.KWc = g.KWc; a.CK = g.CK;
+    a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.Ho = g.Ho; a.Wo = g.Wo; a.Mh = g.Mh; a.rows_a = g.rows_a;
+    a.slots = slots;
+    a.total_o = (long long)p.N * g.Ho * g.Wo;
+    a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
     {
         const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;
         a.descale_each = (((long long)slots * cap) << kTcScaleLog2) > 65535 ? 1 : 0;
         a.n_or = (int)cap; // a count never exceeds the dot length, so clamping there changes nothing
     }
-    for (int t = 0; t < kTcMaxTaps; t++)
-        a.tap_off[t] = t < p.KHW ? tap_offset(t / p.KW, t % p.KW, p.sh, p.sw, p.nrh, p.Wrow, p.Wq) : 0;
-    const size_t smem = tc_smem_bytes(p);
-    dim3 grid((unsigned)((p.NHW + kTcM - 1) / kTcM), (unsigned)NC);
-    auto kernel = p.KHW == 9 ? sc_conv_tc_kernel<9> : p.KHW == 1 ? sc_conv_tc_kernel<1> : sc_conv_tc_kernel<0>;
-    REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kernel<<<grid, kTcThreads, smem, st>>>(a, Ab, Wb, d_pos, d_neg, d_status);
+    for (int t = 0; t < kTcMaxTaps; t++) a.tap_off[t] = g.tap_off[t];
+    dim3 grid((unsigned)((a.total_o + kTcM - 1) / kTcM), (unsigned)NC);
+    const int ra = (g.rows_a + kTcWorkers - 1) / kTcWorkers;
+    auto pick = [&](auto khw_tag) {
+        constexpr int KHW_T = decltype(khw_tag)::value;
+        if (g.KWc == 2) return ra == 1 ? sc_conv_tc_kernel<KHW_T, 2, 1> : sc_conv_tc_kernel<KHW_T, 2, kTcMaxARows>;
+        return ra == 1 ? sc_conv_tc_kernel<KHW_T, 1, 1> : sc_conv_tc_kernel<KHW_T, 1, kTcMaxARows>;
+    };
+    auto kernel = p.KHW == 9 ? pick(std::integral_constant<int, 9>{})
+                : p.KHW == 1 ? pick(std::integral_constant<int, 1>{}) : pick(std::integral_constant<int, 0>{});
+    REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
+    kernel<<<grid, kTcThreads, g.smem, st>>>(a, Ab, Wb, d_pos, d_neg, d_status);
     REXSC_LAUNCH_CHECK("sc_conv_tc_kernel");
     return REXSC_OK;
 }
