@@ -72,13 +72,17 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
     rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
                           desc->prog_load_width, desc->prog_load_wait, 1, b.lut_w, st);
     if (rc != REXSC_OK) return rc;
-    rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
+    const int k = resolve_kernel(desc, p);
+    if (k < 0) return k;
+    // the tensor-core kernel reads channel-packed bit planes; the ALU kernels read time-packed stream words
+    if (k == REXSC_KERNEL_TENSOR)
+        rc = launch_expand_act_bits(p, *desc, d_act, b.lut_a, static_cast<uint32_t *>(b.tc), st);
+    else
+        rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
     if (rc != REXSC_OK) return rc;
     rc = launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
     if (rc != REXSC_OK) return rc;
-    const int k = resolve_kernel(desc, p);
-    if (k < 0) return k;
-    if (k == REXSC_KERNEL_TENSOR) return launch_tc_bitplanes(p, b.A, b.Wt, b.S, b.tc, st);
+    if (k == REXSC_KERNEL_TENSOR) return launch_tc_weight_bitplanes(p, b.Wt, b.S, b.tc, st);
     return REXSC_OK;
 }
 

@@ -88,6 +88,9 @@ int launch_build_lut(int l, int bit_length, int gen_config, int xnor, int tw, in
                      uint32_t *d_lut, cudaStream_t st);
 int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const uint32_t *d_lut,
                       uint32_t *d_A, cudaStream_t st);
+// the same expansion, written as channel-packed bit planes Ab[slot][cw][P] for the tensor-core kernel
+int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const uint32_t *d_lut,
+                           uint32_t *d_Ab, cudaStream_t st);
 int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_w, const uint32_t *d_lut,
                          uint32_t *d_Wt, uint32_t *d_S, cudaStream_t st);
 int launch_conv_direct(const ConvPlan &p, const rexsc_sc_conv_desc &d, const uint32_t *d_A, const uint32_t *d_Wt,
@@ -118,8 +121,8 @@ int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *
 int launch_mma_probe(int blocks, int iters, int n_cols, uint32_t *d_sink, cudaStream_t st);
 bool conv_tc_supported(const ConvPlan &p);
 size_t conv_tc_workspace_bytes(const ConvPlan &p);
-int launch_tc_bitplanes(const ConvPlan &p, const uint32_t *d_A, const uint32_t *d_Wt, const uint32_t *d_S,
-                        void *d_tc_ws, cudaStream_t st);
+int launch_tc_weight_bitplanes(const ConvPlan &p, const uint32_t *d_Wt, const uint32_t *d_S, void *d_tc_ws,
+                               cudaStream_t st);
 int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,
                    int *d_status, cudaStream_t st);
 

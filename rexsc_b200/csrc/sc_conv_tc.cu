@@ -476,44 +476,6 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
 }
 
 // ---- bit planes --------------------------------------------------------------------------------------------
-// activation words A[wd][c][P] (bit t = slot 32*wd + t)  ->  Ab[slot][cw][P] (bit b = channel 32*cw + b)
-__global__ void __launch_bounds__(256) bitplane_act_kernel(const uint32_t *__restrict__ A, uint32_t *__restrict__ Ab,
-                                                           int Cpad, int CW, long long NHWp, long long a_plane_words)
-{
-    __shared__ uint32_t tile[32][33]; // [channel][pixel]
-    __shared__ uint32_t outp[32][33]; // [slot][pixel]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long P0 = (long long)blockIdx.x * 32;
-    const int cw = blockIdx.y, wd = blockIdx.z;
-    const uint32_t *Aw = A + (size_t)wd * a_plane_words;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int cl = warp + 8 * i, c = cw * 32 + cl;
-        uint32_t v = 0;
-        if (c < Cpad && P0 + lane < NHWp) v = Aw[(size_t)c * NHWp + P0 + lane];
-        tile[cl][lane] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int p = warp + 8 * i;
-        const uint32_t v = tile[lane][p]; // lane = channel
-        uint32_t mine = 0;
-#pragma unroll
-        for (int t = 0; t < 32; t++) {
-            const uint32_t b = __ballot_sync(0xffffffffu, (v >> t) & 1u);
-            if (lane == t) mine = b;
-        }
-        outp[lane][p] = mine; // lane = slot
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int t = warp + 8 * i;
-        if (P0 + lane < NHWp) Ab[((size_t)(wd * 32 + t) * CW + cw) * NHWp + P0 + lane] = outp[t][lane];
-    }
-}
-
 // weight words + signs (layout of the ALU kernels)  ->  Wb[nchunk][slot][row][tap*CW + cw],
 // row = sign*64 + local output channel, bit b = channel 32*cw + (b ^ 3): nibbles are stored bit-reversed
 __global__ void __launch_bounds__(256) bitplane_weight_kernel(const uint32_t *__restrict__ Wt, const uint32_t *__restrict__ S,
@@ -700,27 +662,19 @@ size_t conv_tc_workspace_bytes(const ConvPlan &p)
     return align_up(ab, 256) + align_up(wb, 256);
 }
 
-// stream words of the ALU layout -> bit planes (part of the expand stage when the tensor kernel is selected)
-int launch_tc_bitplanes(const ConvPlan &p, const uint32_t *d_A, const uint32_t *d_Wt, const uint32_t *d_S,
-                        void *d_tc_ws, cudaStream_t st)
+// weight stream words of the ALU layout -> bit planes (part of the expand stage when the tensor kernel is selected;
+// the activation bit planes in front of them are written by launch_expand_act_bits)
+int launch_tc_weight_bitplanes(const ConvPlan &p, const uint32_t *d_Wt, const uint32_t *d_S, void *d_tc_ws, cudaStream_t st)
 {
     if (!conv_tc_supported(p)) return REXSC_E_UNSUPPORTED;
     const int CW = (p.C + 31) / 32, NC = (p.Co + kTcCout - 1) / kTcCout;
     const int slots = p.words * 32;
-    uint32_t *Ab = static_cast<uint32_t *>(d_tc_ws);
     uint32_t *Wb = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(d_tc_ws) +
                                                 align_up((size_t)slots * CW * p.NHWp * 4, 256));
-    {
-        dim3 grid((unsigned)((p.NHWp + 31) / 32), (unsigned)CW, (unsigned)p.words);
-        bitplane_act_kernel<<<grid, 256, 0, st>>>(d_A, Ab, p.Cpad, CW, p.NHWp, p.a_plane_words);
-        REXSC_LAUNCH_CHECK("bitplane_act_kernel");
-    }
-    {
-        const long long warps = (long long)NC * p.words * kTcN * p.KHW * CW;
-        bitplane_weight_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(d_Wt, d_S, Wb, p.Co, p.C, p.KHW, p.CCH, CW,
-                                                                                     p.words, NC, p.w_plane_words);
-        REXSC_LAUNCH_CHECK("bitplane_weight_kernel");
-    }
+    const long long warps = (long long)NC * p.words * kTcN * p.KHW * CW;
+    bitplane_weight_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(d_Wt, d_S, Wb, p.Co, p.C, p.KHW, p.CCH, CW,
+                                                                                 p.words, NC, p.w_plane_words);
+    REXSC_LAUNCH_CHECK("bitplane_weight_kernel");
     return REXSC_OK;
 }
 

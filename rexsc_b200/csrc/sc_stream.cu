@@ -360,6 +360,123 @@ int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void
     return REXSC_E_BAD_ARG;
 }
 
+// ---- activation expansion straight to bit planes (operand format of the tensor-core kernel) ---------------------
+// Ab[slot][cw][P], bit b = channel 32*cw + b.  One warp owns 32 stored pixels x 32 channels: it quantises them into a
+// private tile, then per pixel looks the 32 stream words up (lane = channel; bit t = slot t), transposes the 32x32 bit
+// matrix across the warp so that lane t holds the word of slot t (bit b = channel b), and stages it so that the final
+// stores run with the pixel index fastest (one 128-byte run per slot).  The stream words never touch global memory.
+__device__ __forceinline__ uint32_t transpose32(uint32_t x, int lane)
+{
+    // recursive block swap: after the step with distance j, 2j x 2j blocks are transposed at block granularity j
+#pragma unroll
+    for (int j = 16; j >= 1; j >>= 1) {
+        const uint32_t low = j == 16 ? 0x0000ffffu : j == 8 ? 0x00ff00ffu : j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
+        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
+        x = (lane & j) ? ((x & ~low) | ((y & ~low) >> j)) : ((x & low) | ((y & low) << j));
+    }
+    return x;
+}
+
+template <typename T, bool NHWC>
+__global__ void __launch_bounds__(256) expand_act_bits_kernel(ExpandActArgs a, const T *__restrict__ x,
+                                                              const uint32_t *__restrict__ lut, uint32_t *__restrict__ Ab,
+                                                              int CW, long long items)
+{
+    __shared__ uint8_t q_s[8][32][36];   // [warp][pixel][channel], padded
+    __shared__ uint32_t o_s[8][32][33];  // [warp][slot][pixel], padded
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long item = (long long)blockIdx.x * 8 + warp; // neighbouring warps: the channel words of the same pixels
+    if (item >= items) return;
+    const int cw = (int)(item % CW);
+    const long long P0 = (item / CW) * 32;
+    const int c0 = cw * 32;
+    // lane = pixel: where it sits in the input
+    int n = 0, h = 0, w = 0;
+    const long long P = P0 + lane;
+    const bool live = P < a.NHW && decode_pixel(a, P, n, h, w);
+    const int hi = h - a.ph, wi = w - a.pw;
+    const bool inside = live && hi >= 0 && hi < a.H && wi >= 0 && wi < a.W;
+    const uint32_t hw_mod = ((uint32_t)h * (uint32_t)a.Wp + (uint32_t)w) % (uint32_t)a.period;
+    const long long xbase = NHWC ? (((long long)n * a.H + hi) * a.W + wi) * a.C : (((long long)n * a.C) * a.H + hi) * a.W + wi;
+    // quantise the 32 x 32 tile, reading along the input's fastest dimension
+    if (NHWC) {
+        const int c = c0 + lane;
+        for (int p = 0; p < 32; p++) {
+            const bool ins = __shfl_sync(0xffffffffu, inside ? 1 : 0, p) != 0;
+            const long long xb = __shfl_sync(0xffffffffu, xbase, p);
+            int q = 0;
+            if (ins && c < a.C) q = quant_ceil_unipolar(load_as_float<T>(x, xb + c), a.scale);
+            q_s[warp][p][lane] = (uint8_t)q;
+        }
+    } else {
+        const long long plane = (long long)a.H * a.W;
+        for (int cc = 0; cc < 32; cc++) {
+            const int c = c0 + cc;
+            int q = 0;
+            if (inside && c < a.C) q = quant_ceil_unipolar(load_as_float<T>(x, xbase + c * plane), a.scale);
+            q_s[warp][lane][cc] = (uint8_t)q;
+        }
+    }
+    __syncwarp();
+    // lane = channel from here on
+    const int c = c0 + lane;
+    const uint32_t lane_phase = a.linear_seeds ? (uint32_t)c % (uint32_t)a.period
+                                               : (uint32_t)(((unsigned long long)c * a.plane_mod) % (uint32_t)a.period);
+    for (int wd = 0; wd < a.words; wd++) {
+#pragma unroll 4
+        for (int p = 0; p < 32; p++) {
+            const int q = q_s[warp][p][lane];
+            uint32_t phase = lane_phase;
+            if (!a.linear_seeds) {
+                phase += __shfl_sync(0xffffffffu, hw_mod, p);
+                if (phase >= (uint32_t)a.period) phase -= (uint32_t)a.period;
+            }
+            const uint32_t v = q > 0 ? __ldg(lut + ((size_t)phase * a.nvals + q) * a.words + wd) : 0u;
+            o_s[warp][lane][p] = transpose32(v, lane);
+        }
+        __syncwarp();
+        if (P0 + lane < a.NHWp) {
+#pragma unroll 4
+            for (int t = 0; t < 32; t++)
+                Ab[((size_t)(wd * 32 + t) * CW + cw) * a.NHWp + P0 + lane] = o_s[warp][t][lane];
+        }
+        __syncwarp();
+    }
+}
+
+int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const uint32_t *d_lut,
+                           uint32_t *d_Ab, cudaStream_t st)
+{
+    ExpandActArgs a;
+    a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
+    a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
+    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
+    a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
+    a.scale = (float)p.nvals;
+    const int CW = (p.C + 31) / 32;
+    const long long items = ((p.NHWp + 31) / 32) * CW;
+    const long long blocks = (items + 7) / 8;
+    if (blocks > 0x7fffffffLL) return REXSC_E_TOO_LONG;
+    const bool nhwc = d.act_channels_last != 0;
+#define REXSC_ACT_BITS(T)                                                                                              \
+    do {                                                                                                               \
+        if (nhwc)                                                                                                      \
+            expand_act_bits_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>(a, (const T *)d_act, d_lut, d_Ab, CW, items); \
+        else                                                                                                           \
+            expand_act_bits_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>(a, (const T *)d_act, d_lut, d_Ab, CW, items); \
+    } while (0)
+    switch (d.act_dtype) {
+    case REXSC_F32: REXSC_ACT_BITS(float); break;
+    case REXSC_F16: REXSC_ACT_BITS(__half); break;
+    case REXSC_BF16: REXSC_ACT_BITS(__nv_bfloat16); break;
+    default: return REXSC_E_BAD_ARG;
+    }
+#undef REXSC_ACT_BITS
+    REXSC_LAUNCH_CHECK("expand_act_bits_kernel");
+    return REXSC_OK;
+}
+
 // ---- weight expansion -----------------------------------------------------------------------
 // Seed index of a weight element: c*KH*KW + kh*KW + kw, offset 13 for both signs
 // (torch_c/sc-extension/sc_cuda_conv.cu:45,55-56; sc_device.cuh:33-34); linear: c only.
