@@ -241,6 +241,7 @@ def run_ours(args, rank, world, local_rank):
     per_kernel = {"tensor": {"ms": 0.0, "products": 0, "launches": 0}, "tiled": {"ms": 0.0, "products": 0, "launches": 0},
                   "direct": {"ms": 0.0, "products": 0, "launches": 0}}
     exp_ms = 0.0
+    exp_bytes = 0
     for l in layers:
         x, w = l["x"], l["w"]
         d = _lib.ScConvDesc()
@@ -275,6 +276,10 @@ def run_ours(args, rank, world, local_rank):
                     best = t if best is None else min(best, t)
             if which == "expand":
                 exp_ms += best * l["rep"]
+                # algorithmic bytes of the stage: the activations read once + their bit planes (or stream words) written
+                # once, one bit per element and time slot, channels padded to whole 32-bit words
+                px = d.batch * d.h_in * d.w_in
+                exp_bytes += l["rep"] * (x.numel() * x.element_size() + BIT_LENGTH // 8 * ((d.c_in + 31) // 32 * 32) * px)
             else:
                 k = per_kernel[which_kernel]
                 k["ms"] += best * l["rep"]
@@ -327,7 +332,7 @@ def run_ours(args, rank, world, local_rank):
 
     return {
         "ms": ms, "launches": n_launch, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "h2d": h2d, "d2h": d2h,
-        "clocks": clocks, "per_kernel": per_kernel, "exp_ms": exp_ms, "lop3_peak": lop3_peak,
+        "clocks": clocks, "per_kernel": per_kernel, "exp_ms": exp_ms, "exp_bytes": exp_bytes, "lop3_peak": lop3_peak,
         "mma_peak_ops": mma_peak_ops, "pw_gbs": pw_gbs,
     }
 
@@ -480,7 +485,15 @@ def main():
             "tbitops_per_s_kernel": 64 * pk["tiled"]["products"] / (pk["tiled"]["ms"] * 1e-3) / 1e12
             if pk["tiled"]["ms"] > 0 else 0.0,
         }
+        exp_gbs = r["exp_bytes"] / (r["exp_ms"] * 1e-3) / 1e9 if r["exp_ms"] > 0 else 0.0
+        roof_expand = {
+            "bound": "hbm", "kernel": "expand stage (expand_act_bits_kernel + LUT build + weight expansion, per layer)",
+            "achieved": exp_gbs, "peak": _hbm_peak(), "unit": "GB/s", "frac": exp_gbs / _hbm_peak(), "traffic": None,
+            "peak_source": _hbm_peak_source(), "kernel_ms_per_step": r["exp_ms"],
+        }
         dominant, secondary = (roof_tensor, roof_alu) if pk["tensor"]["ms"] >= pk["tiled"]["ms"] else (roof_alu, roof_tensor)
+        if secondary["launches_per_step"] == 0:
+            secondary = roof_expand  # every layer of this workload runs on one accumulate kernel
         dominant["expand_ms_per_step"] = r["exp_ms"]
         line = {
             "metric": "sc_resnet18_or2_L32_sc_forward_img_per_s", "value": value, "unit": "img/s",
@@ -505,6 +518,8 @@ def main():
                 "peak": _hbm_peak(), "frac": r["pw_gbs"] / _hbm_peak(), "peak_source": _hbm_peak_source(),
             },
         }
+        if secondary is not roof_expand:
+            line["roofline_expand"] = roof_expand
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_block()
         print(json.dumps(line), flush=True)
