@@ -162,15 +162,14 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
 
     // mbarriers (index = operand buffer or accumulator buffer):
     //   full[b]   operands of a step are in shared memory           (one arrival per expanding warp)
-    //   empty[b]  the MMAs that read operand buffer b have completed (one commit per issuing warp)
-    //   tfull[t]  a slot's counts are complete in accumulator buffer t (one commit per issuing warp)
+    //   empty[b]  the MMAs that read operand buffer b have completed  (one commit per issuing warp); after the last
+    //             chunk of a slot this also says that the slot's counts are complete in their accumulator buffer
     //   tfree[t]  accumulator buffer t has been folded                (one arrival per expanding warp)
-    uint64_t *bar_full = bars, *bar_empty = bars + 2, *bar_tfull = bars + 4, *bar_tfree = bars + 6;
+    uint64_t *bar_full = bars, *bar_empty = bars + 2, *bar_tfree = bars + 4;
     if (tid == 0) {
         for (int b = 0; b < 2; b++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_full[b])), "r"(kTcWorkers / 32) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_empty[b])), "r"(kTcM / kTcSub) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_tfull[b])), "r"(kTcM / kTcSub) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_tfree[b])), "r"(kTcWorkers / 32) : "memory");
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -335,8 +334,8 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const uint32_t da_hi = (uint32_t)(da_proto >> 32), db_hi = (uint32_t)(db_proto >> 32);
     const uint32_t a_kk = 2u * (uint32_t)a.rows_a;             // rows between the 32-channel words of a chunk
     const uint32_t b_tap = 2u * (uint32_t)KWC * kTcN;        // rows between taps of the weight operand
-    auto issue_mmas = [&](int step) {
-        const int s = step / a.CK, ck = step - s * a.CK, buf = step & 1;
+    auto issue_mmas = [&](int step, int s, int ck) {
+        const int buf = step & 1;
         const uint32_t da_lo = (uint32_t)da_proto + (uint32_t)buf * (a_bytes >> 4);
         const uint32_t db_lo = (uint32_t)db_proto + (uint32_t)buf * (b_bytes >> 4);
         const uint32_t d_addr = tmem_base + (uint32_t)((s & 1) * 2 * kTcN + my_sub * kTcN);
@@ -367,10 +366,6 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
                      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(&bar_empty[buf]))
                      : "memory");
-        if (ck == a.CK - 1)
-            asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
-                         "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(&bar_tfull[s & 1]))
-                         : "memory");
     };
 
     bool failed = false;
@@ -388,12 +383,13 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     };
     if (warp >= kTcWorkers / 32) {
         // ---- MMA-issuing warps: operands ready -> accumulator free -> issue -> commit ----
-        for (int step = 0; step < n_steps && !failed; step++) {
-            const int s = step / a.CK, ck = step - s * a.CK;
+        int s = 0, ck = 0;
+        for (int step = 0; step < n_steps; step++) {
             if (!wait_on(&bar_full[step & 1], step >> 1)) { failed = true; break; }
             if (ck == 0 && s >= 2 && !wait_on(&bar_tfree[s & 1], (s >> 1) - 1)) { failed = true; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_mmas(step);
+            issue_mmas(step, s, ck);
+            if (++ck == a.CK) { ck = 0; s++; }
         }
     } else {
         // ---- expanding / folding warps ----
@@ -402,29 +398,26 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         warp_arrive(&bar_full[0]);
         if (n_steps > 1) load_bits();
-        for (int step = 0; step < n_steps && !failed; step++) {
-            // operands of the next step go into the buffer that the previous step's MMAs have finished reading
+        int s_prev = 0, ck_prev = -1; // slot and chunk of step - 1
+        for (int step = 0; step <= n_steps; step++) {
+            // the previous step's MMAs: its operand buffer is free again and, after the last chunk of a slot, the
+            // slot's counts are complete
+            if (step > 0) {
+                if (!wait_on(&bar_empty[(step - 1) & 1], (step - 1) >> 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
             if (step + 1 < n_steps) {
-                if (step > 0 && !wait_on(&bar_empty[(step - 1) & 1], (step - 1) >> 1)) { failed = true; break; }
                 expand_bits((step + 1) & 1);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 warp_arrive(&bar_full[(step + 1) & 1]);
                 if (step + 2 < n_steps) load_bits();
             }
             // fold the slot that the previous step completed and hand its accumulators back
-            if (step > 0 && (step % a.CK) == 0) {
-                const int s = (step - 1) / a.CK;
-                if (!wait_on(&bar_tfull[s & 1], s >> 1)) { failed = true; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                slot_epilogue(s & 1);
-                warp_arrive(&bar_tfree[s & 1]);
+            if (ck_prev == a.CK - 1) {
+                slot_epilogue(s_prev & 1);
+                warp_arrive(&bar_tfree[s_prev & 1]);
             }
-        }
-        if (!failed) {
-            const int s = a.slots - 1;
-            if (!wait_on(&bar_tfull[s & 1], s >> 1)) failed = true;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (!failed) slot_epilogue(s & 1);
+            if (++ck_prev == a.CK) { ck_prev = 0; s_prev++; }
         }
     }
     if (failed && lane == 0) atomicExch(status, 4);
