@@ -151,7 +151,7 @@ def run_ours(args, rank, world, local_rank):
     launches = {"n": 0}
 
     def conv(l, x):
-        launches["n"] += l.get("kernels_per_call", 5)  # LUT builds, expands, (bit planes,) accumulate
+        launches["n"] += l.get("kernels_per_call", 4)  # LUT builds, expands, (bit planes,) accumulate
         return ops.conv2d_generic_general_split_acc(x, l["w"], BIT_LENGTH, -1, 16, (0, 0), (l["stride"],) * 2, PROG,
                                                     OR_N - 1, 1, True, False)
 
@@ -164,8 +164,8 @@ def run_ours(args, rank, world, local_rank):
         d0.act_channels_last = d0.w_channels_last = d0.out_channels_last = 1
         d0.bit_length, d0.lfsr_length, d0.bin_config, d0.gen_config, d0.xnor = BIT_LENGTH, -1, OR_N - 1, 1, 1
         d0.prog_total_width, d0.prog_load_width, d0.prog_load_wait = PROG
-        # tensor-core path: 2 LUT builds, 2 expands, 1 weight bit-plane kernel, 1 MMA kernel; ALU paths: 2 + 2 + 1
-        l["kernels_per_call"] = 6 if lib.rexsc_sc_conv2d_kernel_choice(C0.byref(d0)) == 3 else 5
+        # tensor-core path: stream tables (1 launch), activation bit planes, weight bit planes, MMA kernel; ALU paths: tables + 2 expands + 1
+        l["kernels_per_call"] = 4 if lib.rexsc_sc_conv2d_kernel_choice(C0.byref(d0)) == 3 else 4
     guides = {}
     for i, l in enumerate(layers):
         p, n = conv(l, l["x"])

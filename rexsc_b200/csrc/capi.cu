@@ -64,26 +64,24 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
     if (rc != REXSC_OK) return rc;
     if (!d_act || !d_weight) return REXSC_E_BAD_ARG;
     REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
-    // The linear generators always use the XOR LFSR (torch_c/sc-extension/sc_cuda_matmul.cu:27-57).
-    const int xnor = desc->linear_seeds ? 0 : (desc->xnor ? 1 : 0);
-    rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
-                          desc->prog_load_width, desc->prog_load_wait, 0, b.lut_a, st);
-    if (rc != REXSC_OK) return rc;
-    rc = launch_build_lut(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
-                          desc->prog_load_width, desc->prog_load_wait, 1, b.lut_w, st);
-    if (rc != REXSC_OK) return rc;
     const int k = resolve_kernel(desc, p);
     if (k < 0) return k;
-    // the tensor-core kernel reads channel-packed bit planes; the ALU kernels read time-packed stream words
-    if (k == REXSC_KERNEL_TENSOR)
+    // The linear generators always use the XOR LFSR (torch_c/sc-extension/sc_cuda_matmul.cu:27-57).
+    const int xnor = desc->linear_seeds ? 0 : (desc->xnor ? 1 : 0);
+    rc = launch_build_lut_pair(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
+                               desc->prog_load_width, desc->prog_load_wait, b.lut_a, b.lut_w, st);
+    if (rc != REXSC_OK) return rc;
+    if (k == REXSC_KERNEL_TENSOR) {
+        // the tensor-core kernel reads channel-packed bit planes: Ab, then Wb, in the tensor region of the workspace
         rc = launch_expand_act_bits(p, *desc, d_act, b.lut_a, static_cast<uint32_t *>(b.tc), st);
-    else
-        rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
+        if (rc != REXSC_OK) return rc;
+        return launch_expand_weight_bits(p, *desc, d_weight, b.lut_w,
+                                         reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p)), st);
+    }
+    // the ALU kernels read time-packed stream words
+    rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
     if (rc != REXSC_OK) return rc;
-    rc = launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
-    if (rc != REXSC_OK) return rc;
-    if (k == REXSC_KERNEL_TENSOR) return launch_tc_weight_bitplanes(p, b.Wt, b.S, b.tc, st);
-    return REXSC_OK;
+    return launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
 }
 
 // stage 2: OR-n accumulation over the stream words of the workspace

@@ -121,8 +121,12 @@ int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *
 int launch_mma_probe(int blocks, int iters, int n_cols, uint32_t *d_sink, cudaStream_t st);
 bool conv_tc_supported(const ConvPlan &p);
 size_t conv_tc_workspace_bytes(const ConvPlan &p);
-int launch_tc_weight_bitplanes(const ConvPlan &p, const uint32_t *d_Wt, const uint32_t *d_S, void *d_tc_ws,
-                               cudaStream_t st);
+// weights -> Wb bit planes of the tensor-core kernel (sc_stream.cu)
+int launch_build_lut_pair(int l, int bit_length, int gen_config, int xnor, int tw, int lw, int lwait, uint32_t *d_lut_a,
+                          uint32_t *d_lut_w, cudaStream_t st);
+int launch_expand_weight_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_w, const uint32_t *d_lut,
+                              uint32_t *d_Wb, cudaStream_t st);
+size_t conv_tc_weight_offset(const ConvPlan &p);
 int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,
                    int *d_status, cudaStream_t st);
 

@@ -468,48 +468,6 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
-// ---- bit planes --------------------------------------------------------------------------------------------
-// weight words + signs (layout of the ALU kernels)  ->  Wb[nchunk][slot][row][tap*CW + cw],
-// row = sign*64 + local output channel, bit b = channel 32*cw + (b ^ 3): nibbles are stored bit-reversed
-__global__ void __launch_bounds__(256) bitplane_weight_kernel(const uint32_t *__restrict__ Wt, const uint32_t *__restrict__ S,
-                                                              uint32_t *__restrict__ Wb, int Co, int C, int KHW, int CCH,
-                                                              int CW, int words, int NC, long long w_plane_words)
-{
-    // one warp per (nchunk, wd, row, tap, cw); lane = channel
-    const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    const long long total = (long long)NC * words * kTcN * KHW * CW;
-    if (gw >= total) return;
-    long long t = gw;
-    const int cw = (int)(t % CW); t /= CW;
-    const int tap = (int)(t % KHW); t /= KHW;
-    const int row = (int)(t % kTcN); t /= kTcN;
-    const int wd = (int)(t % words);
-    const int nchunk = (int)(t / words);
-    const int sign = row >> 6, col = row & 63;
-    const int co = nchunk * kTcCout + col;
-    const int c = cw * 32 + lane;
-    uint32_t v = 0;
-    if (co < Co && c < C) {
-        const int nt = co / kTileN, nl = co % kTileN, cch = c / kChunkC, cc = c % kChunkC;
-        const size_t blk = ((size_t)nt * CCH + cch) * KHW + tap;
-        const uint32_t sg = S[blk * (kTileN / kWarpN) + nl / kWarpN];
-        const int neg = (sg >> (cc * kWarpN + nl % kWarpN)) & 1u;
-        if (neg == sign) v = Wt[(size_t)wd * w_plane_words + (blk * kChunkC + cc) * kTileN + nl];
-    }
-    uint32_t mine = 0;
-#pragma unroll
-    for (int tt = 0; tt < 32; tt++) {
-        const uint32_t b = __ballot_sync(0xffffffffu, (v >> tt) & 1u);
-        if (lane == tt) mine = b;
-    }
-    // bit-reverse every nibble (see kTcMaskW): reverse all 32 bits, then put the nibbles back in order
-    mine = __byte_perm(__brev(mine), 0, 0x0123);
-    mine = ((mine & 0x0f0f0f0fu) << 4) | ((mine >> 4) & 0x0f0f0f0fu);
-    const int slots = words * 32;
-    Wb[(((size_t)nchunk * slots + wd * 32 + lane) * ((size_t)KHW * CW) + tap * CW + cw) * kTcN + row] = mine;
-}
-
 // Tensor-pipe issue-rate probe: back-to-back int8 MMAs (M128 x N x K32) on fixed shared-memory operands.
 __global__ void __launch_bounds__(128, 2) mma_probe_kernel(int iters, int n_cols, uint32_t *sink)
 {
@@ -655,20 +613,11 @@ size_t conv_tc_workspace_bytes(const ConvPlan &p)
     return align_up(ab, 256) + align_up(wb, 256);
 }
 
-// weight stream words of the ALU layout -> bit planes (part of the expand stage when the tensor kernel is selected;
-// the activation bit planes in front of them are written by launch_expand_act_bits)
-int launch_tc_weight_bitplanes(const ConvPlan &p, const uint32_t *d_Wt, const uint32_t *d_S, void *d_tc_ws, cudaStream_t st)
+// byte offset of the weight bit planes Wb inside the tensor-core region of the workspace (Ab comes first)
+size_t conv_tc_weight_offset(const ConvPlan &p)
 {
-    if (!conv_tc_supported(p)) return REXSC_E_UNSUPPORTED;
-    const int CW = (p.C + 31) / 32, NC = (p.Co + kTcCout - 1) / kTcCout;
-    const int slots = p.words * 32;
-    uint32_t *Wb = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(d_tc_ws) +
-                                                align_up((size_t)slots * CW * p.NHWp * 4, 256));
-    const long long warps = (long long)NC * p.words * kTcN * p.KHW * CW;
-    bitplane_weight_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(d_Wt, d_S, Wb, p.Co, p.C, p.KHW, p.CCH, CW,
-                                                                                 p.words, NC, p.w_plane_words);
-    REXSC_LAUNCH_CHECK("bitplane_weight_kernel");
-    return REXSC_OK;
+    const int CW = (p.C + 31) / 32;
+    return align_up((size_t)p.words * 32 * CW * p.NHWp * 4, 256);
 }
 
 int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,

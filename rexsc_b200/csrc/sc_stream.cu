@@ -39,35 +39,47 @@ __host__ __device__ __forceinline__ int lfsr_next(int v, int l, int xnor)
 // advance then compare; progressive-loading mask on the value; int8 storage of state and value; for
 // gen_config g the weight bit t lands in slots t*g..t*g+g-1 and the activation bit t in slots
 // (t/g)*g*g + j*g + t%g.
-__global__ void build_lut_kernel(int l, int bit_length, int g, int xnor, int tw, int lw, int lwait, int is_weight,
-                                 int words, uint32_t *__restrict__ lut)
+struct LutParams {
+    int l, bit_length, g, xnor, tw, lw, lwait, words;
+};
+
+// stream words of one (seed phase, value) pair into out[0 .. words)
+template <typename Store>
+__device__ __forceinline__ void lut_entry(const LutParams &lp, int is_weight, int phase, int value, Store store)
 {
-    const int nvals = 1 << l;
-    const int period = nvals - 1;
-    int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= period * nvals) return;
-    int phase = idx / nvals;
-    int value = idx - phase * nvals;
-    int state = (int)(int8_t)(phase + 1 - (xnor ? 1 : 0));
-    int val8 = (int)(int8_t)value;
+    int state = (int)(int8_t)(phase + 1 - (lp.xnor ? 1 : 0));
+    const int val8 = (int)(int8_t)value;
     uint32_t acc[32]; // words <= 32 (slots <= 1024)
 #pragma unroll 1
-    for (int j = 0; j < words; j++) acc[j] = 0u;
+    for (int j = 0; j < lp.words; j++) acc[j] = 0u;
 #pragma unroll 1
-    for (int t = 0; t < bit_length; t++) {
-        int cur = (t / lwait + 1) * lw - 1;
-        if (cur > tw) cur = tw;
-        int sh = tw - cur;
-        int actual = (val8 >> sh) << sh;
-        state = (int)(int8_t)lfsr_next(state, l, xnor);
+    for (int t = 0; t < lp.bit_length; t++) {
+        int cur = (t / lp.lwait + 1) * lp.lw - 1;
+        if (cur > lp.tw) cur = lp.tw;
+        const int sh = lp.tw - cur;
+        const int actual = (val8 >> sh) << sh;
+        state = (int)(int8_t)lfsr_next(state, lp.l, lp.xnor);
         if (actual > state) {
-            for (int j = 0; j < g; j++) {
-                int slot = is_weight ? t * g + j : (t / g) * g * g + j * g + t % g;
+            for (int j = 0; j < lp.g; j++) {
+                const int slot = is_weight ? t * lp.g + j : (t / lp.g) * lp.g * lp.g + j * lp.g + t % lp.g;
                 acc[slot >> 5] |= 1u << (slot & 31);
             }
         }
     }
-    for (int j = 0; j < words; j++) lut[(size_t)idx * words + j] = acc[j];
+    for (int j = 0; j < lp.words; j++) store(j, acc[j]);
+}
+
+// blockIdx.y = 0: the table `lut` for generator kind `is_weight`; blockIdx.y = 1 (pair launch): the weight table lut_w
+__global__ void build_lut_kernel(LutParams lp, int is_weight, uint32_t *__restrict__ lut, uint32_t *__restrict__ lut_w)
+{
+    if (blockIdx.y == 1) { is_weight = 1; lut = lut_w; }
+    const int nvals = 1 << lp.l;
+    const int period = nvals - 1;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= period * nvals) return;
+    const int phase = idx / nvals;
+    const int value = idx - phase * nvals;
+    lut_entry(lp, is_weight, phase, value, [&](int j, uint32_t v) { lut[(size_t)idx * lp.words + j] = v; });
 }
 
 int launch_build_lut(int l, int bit_length, int gen_config, int xnor, int tw, int lw, int lwait, int is_weight,
@@ -78,8 +90,23 @@ int launch_build_lut(int l, int bit_length, int gen_config, int xnor, int tw, in
     if (slots > 1024) return REXSC_E_TOO_LONG;
     int words = (slots + 31) / 32;
     int total = ((1 << l) - 1) * (1 << l);
-    build_lut_kernel<<<(total + 127) / 128, 128, 0, st>>>(l, bit_length, gen_config, xnor, tw, lw, lwait, is_weight,
-                                                         words, d_lut);
+    LutParams lp{l, bit_length, gen_config, xnor, tw, lw, lwait, words};
+    build_lut_kernel<<<(total + 127) / 128, 128, 0, st>>>(lp, is_weight, d_lut, nullptr);
+    REXSC_LAUNCH_CHECK("build_lut_kernel");
+    return REXSC_OK;
+}
+
+// activation and weight tables of one conv call in a single launch
+int launch_build_lut_pair(int l, int bit_length, int gen_config, int xnor, int tw, int lw, int lwait, uint32_t *d_lut_a,
+                          uint32_t *d_lut_w, cudaStream_t st)
+{
+    if (l < 1 || l > 8 || bit_length < 1 || gen_config < 1 || lwait < 1) return REXSC_E_BAD_ARG;
+    const int slots = bit_length * gen_config;
+    if (slots > 1024) return REXSC_E_TOO_LONG;
+    const int words = (slots + 31) / 32;
+    const int total = ((1 << l) - 1) * (1 << l);
+    LutParams lp{l, bit_length, gen_config, xnor, tw, lw, lwait, words};
+    build_lut_kernel<<<dim3((total + 127) / 128, 2), 128, 0, st>>>(lp, 0, d_lut_a, d_lut_w);
     REXSC_LAUNCH_CHECK("build_lut_kernel");
     return REXSC_OK;
 }
@@ -362,28 +389,33 @@ int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void
 
 // ---- activation expansion straight to bit planes (operand format of the tensor-core kernel) ---------------------
 // Ab[slot][cw][P], bit b = channel 32*cw + b.  One warp owns 32 stored pixels x 32 channels: it quantises them into a
-// private tile, then per pixel looks the 32 stream words up (lane = channel; bit t = slot t), transposes the 32x32 bit
-// matrix across the warp so that lane t holds the word of slot t (bit b = channel b), and stages it so that the final
-// stores run with the pixel index fastest (one 128-byte run per slot).  The stream words never touch global memory.
-__device__ __forceinline__ uint32_t transpose32(uint32_t x, int lane)
+// private byte tile reading along the input's fastest dimension, then every lane takes ONE pixel: it looks up the
+// stream words of that pixel's 32 channels (bit t = slot t), transposes the 32 x 32 bit matrix in its registers, and
+// holds the 32 slot words (bit b = channel b) -- so each slot's store is one 128-byte run over the warp's pixels.
+// The time-packed stream words never touch memory.
+__device__ __forceinline__ void transpose32_regs(uint32_t (&v)[32])
 {
-    // recursive block swap: after the step with distance j, 2j x 2j blocks are transposed at block granularity j
+    // block swap at distances 16, 8, 4, 2, 1: element (row k, column c + j) <-> (row k + j, column c)
 #pragma unroll
     for (int j = 16; j >= 1; j >>= 1) {
-        const uint32_t low = j == 16 ? 0x0000ffffu : j == 8 ? 0x00ff00ffu : j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
-        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
-        x = (lane & j) ? ((x & ~low) | ((y & ~low) >> j)) : ((x & low) | ((y & low) << j));
+        const uint32_t m = j == 16 ? 0x0000ffffu : j == 8 ? 0x00ff00ffu : j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
+#pragma unroll
+        for (int k = 0; k < 32; k++) {
+            if ((k & j) == 0) {
+                const uint32_t t = ((v[k] >> j) ^ v[k + j]) & m;
+                v[k + j] ^= t;
+                v[k] ^= t << j;
+            }
+        }
     }
-    return x;
 }
 
 template <typename T, bool NHWC>
-__global__ void __launch_bounds__(256) expand_act_bits_kernel(ExpandActArgs a, const T *__restrict__ x,
+__global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a, const T *__restrict__ x,
                                                               const uint32_t *__restrict__ lut, uint32_t *__restrict__ Ab,
                                                               int CW, long long items)
 {
-    __shared__ uint8_t q_s[8][32][36];   // [warp][pixel][channel], padded
-    __shared__ uint32_t o_s[8][32][33];  // [warp][slot][pixel], padded
+    __shared__ uint8_t q_s[8][32][36];   // [warp][pixel][channel], padded: a lane's row starts in its own bank
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long item = (long long)blockIdx.x * 8 + warp; // neighbouring warps: the channel words of the same pixels
     if (item >= items) return;
@@ -401,6 +433,7 @@ __global__ void __launch_bounds__(256) expand_act_bits_kernel(ExpandActArgs a, c
     // quantise the 32 x 32 tile, reading along the input's fastest dimension
     if (NHWC) {
         const int c = c0 + lane;
+#pragma unroll 4
         for (int p = 0; p < 32; p++) {
             const bool ins = __shfl_sync(0xffffffffu, inside ? 1 : 0, p) != 0;
             const long long xb = __shfl_sync(0xffffffffu, xbase, p);
@@ -410,6 +443,7 @@ __global__ void __launch_bounds__(256) expand_act_bits_kernel(ExpandActArgs a, c
         }
     } else {
         const long long plane = (long long)a.H * a.W;
+#pragma unroll 4
         for (int cc = 0; cc < 32; cc++) {
             const int c = c0 + cc;
             int q = 0;
@@ -418,29 +452,34 @@ __global__ void __launch_bounds__(256) expand_act_bits_kernel(ExpandActArgs a, c
         }
     }
     __syncwarp();
-    // lane = channel from here on
-    const int c = c0 + lane;
-    const uint32_t lane_phase = a.linear_seeds ? (uint32_t)c % (uint32_t)a.period
-                                               : (uint32_t)(((unsigned long long)c * a.plane_mod) % (uint32_t)a.period);
+    // lane = pixel; the channel part of the seed phase is the same for all lanes and advances by a constant
+    const uint32_t period = (uint32_t)a.period;
+    const uint32_t step_mod = a.linear_seeds ? 1u % period : a.plane_mod % period;
+    const uint32_t phase0 = a.linear_seeds ? (uint32_t)c0 % period : (uint32_t)(((unsigned long long)c0 * a.plane_mod) % period);
+    const uint32_t pix_mod = a.linear_seeds ? 0u : hw_mod;
+    const bool store_ok = P0 + lane < a.NHWp;
     for (int wd = 0; wd < a.words; wd++) {
-#pragma unroll 4
-        for (int p = 0; p < 32; p++) {
-            const int q = q_s[warp][p][lane];
-            uint32_t phase = lane_phase;
-            if (!a.linear_seeds) {
-                phase += __shfl_sync(0xffffffffu, hw_mod, p);
-                if (phase >= (uint32_t)a.period) phase -= (uint32_t)a.period;
+        uint32_t v[32];
+        uint32_t cph = phase0;
+#pragma unroll
+        for (int cc = 0; cc < 32; cc++) {
+            const int q = q_s[warp][lane][cc];
+            uint32_t phase = cph + pix_mod;
+            if (phase >= period) phase -= period;
+            v[cc] = q > 0 ? __ldg(lut + ((size_t)phase * a.nvals + q) * a.words + wd) : 0u;
+            cph += step_mod;
+            if (cph >= period) cph -= period;
+        }
+        transpose32_regs(v);
+        if (store_ok) {
+            uint32_t *dst = Ab + ((size_t)(wd * 32) * CW + cw) * a.NHWp + P0 + lane;
+            const size_t slot_stride = (size_t)CW * a.NHWp;
+#pragma unroll
+            for (int t = 0; t < 32; t++) {
+                *dst = v[t];
+                dst += slot_stride;
             }
-            const uint32_t v = q > 0 ? __ldg(lut + ((size_t)phase * a.nvals + q) * a.words + wd) : 0u;
-            o_s[warp][lane][p] = transpose32(v, lane);
         }
-        __syncwarp();
-        if (P0 + lane < a.NHWp) {
-#pragma unroll 4
-            for (int t = 0; t < 32; t++)
-                Ab[((size_t)(wd * 32 + t) * CW + cw) * a.NHWp + P0 + lane] = o_s[warp][t][lane];
-        }
-        __syncwarp();
     }
 }
 
@@ -553,6 +592,104 @@ int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const v
     default: return REXSC_E_BAD_ARG;
     }
     REXSC_LAUNCH_CHECK("expand_weight_kernel");
+    return REXSC_OK;
+}
+
+// ---- weight expansion straight to bit planes (operand format of the tensor-core kernel) ------------------------
+// Wb[nchunk][slot][tap*CW + cw][row], row = sign*64 + local output channel, nibbles bit-reversed (the kernel's operand
+// scaling).  One warp per (output channel, tap, channel word): lane = input channel; the 32 x 32 bit matrix
+// (channel x slot) of each sign is transposed across the warp so that lane t holds slot t's channel-packed word.
+__device__ __forceinline__ uint32_t transpose32_warp(uint32_t x, int lane)
+{
+    // recursive block swap across lanes: after the step with distance j, 2j x 2j blocks are transposed
+#pragma unroll
+    for (int j = 16; j >= 1; j >>= 1) {
+        const uint32_t low = j == 16 ? 0x0000ffffu : j == 8 ? 0x00ff00ffu : j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
+        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
+        x = (lane & j) ? ((x & ~low) | ((y & ~low) >> j)) : ((x & low) | ((y & low) << j));
+    }
+    return x;
+}
+
+__device__ __forceinline__ uint32_t reverse_nibbles(uint32_t v)
+{
+    v = __byte_perm(__brev(v), 0, 0x0123); // all 32 bits reversed, bytes back in order: every byte bit-reversed
+    return ((v & 0x0f0f0f0fu) << 4) | ((v >> 4) & 0x0f0f0f0fu); // nibbles of a byte back in order
+}
+
+struct ExpandWBitsArgs {
+    int C, Co, KH, KW, KHW, CW, NC;
+    int period, nvals, words, linear_seeds, ohwi;
+    float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) expand_weight_bits_kernel(ExpandWBitsArgs a, const T *__restrict__ wt,
+                                                                 const uint32_t *__restrict__ lut, uint32_t *__restrict__ Wb,
+                                                                 long long items)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slots = a.words * 32;
+    const size_t row_words = (size_t)a.KHW * a.CW;
+    const long long item = (long long)blockIdx.x * 8 + warp;
+    if (item >= items) return; // warp-uniform
+    {
+        const int cw = (int)(item % a.CW);
+        long long t = item / a.CW;
+        const int tap = (int)(t % a.KHW);
+        const int co = (int)(t / a.KHW); // 0 .. NC*64: rows past Co stay zero
+        const int kh = tap / a.KW, kw = tap - kh * a.KW;
+        const int ci = cw * 32 + lane;
+        int mag = 0;
+        bool neg = false;
+        if (ci < a.C && co < a.Co) {
+            const long long wi = a.ohwi ? (((long long)co * a.KH + kh) * a.KW + kw) * a.C + ci
+                                        : (((long long)co * a.C + ci) * a.KH + kh) * a.KW + kw;
+            const float v = load_as_float<T>(wt, wi) * a.scale;
+            // w_pos = ceil(clamp(v, 0, L-1)); w_neg = ceil(-clamp(v, 1-L, 0))  (sc_cuda.cpp:92-93)
+            const int qp = (int)ceilf(fminf(fmaxf(v, 0.f), a.scale - 1.f));
+            const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - a.scale), 0.f));
+            if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
+        }
+        // seed index c*KH*KW + kh*KW + kw, offset 13 for both signs (sc_cuda_conv.cu:45,55-56); linear: c only
+        const long long seed_ind = a.linear_seeds ? (long long)ci : ((long long)ci * a.KH + kh) * a.KW + kw;
+        const int phase = (int)((13 + seed_ind) % a.period);
+        const int nchunk = co >> 6, col = co & 63;
+        for (int wd = 0; wd < a.words; wd++) {
+            const uint32_t v = mag > 0 ? __ldg(lut + ((size_t)phase * a.nvals + mag) * a.words + wd) : 0u;
+            const uint32_t tp = reverse_nibbles(transpose32_warp(neg ? 0u : v, lane));
+            const uint32_t tn = reverse_nibbles(transpose32_warp(neg ? v : 0u, lane));
+            uint32_t *dst = Wb + (((size_t)nchunk * slots + wd * 32 + lane) * row_words + (size_t)tap * a.CW + cw) * 128 + col;
+            dst[0] = tp;
+            dst[64] = tn;
+        }
+    }
+}
+
+int launch_expand_weight_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_w, const uint32_t *d_lut,
+                              uint32_t *d_Wb, cudaStream_t st)
+{
+    ExpandWBitsArgs a;
+    a.C = p.C; a.Co = p.Co; a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW;
+    a.CW = (p.C + 31) / 32; a.NC = (p.Co + 63) / 64;
+    a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
+    a.ohwi = d.w_channels_last; a.scale = (float)p.nvals;
+    const long long items = (long long)a.NC * 64 * a.KHW * a.CW;
+    const long long blocks = (items + 7) / 8;
+    if (blocks > 0x7fffffffLL) return REXSC_E_TOO_LONG;
+    switch (d.w_dtype) {
+    case REXSC_F32:
+        expand_weight_bits_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(a, (const float *)d_w, d_lut, d_Wb, items);
+        break;
+    case REXSC_F16:
+        expand_weight_bits_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(a, (const __half *)d_w, d_lut, d_Wb, items);
+        break;
+    case REXSC_BF16:
+        expand_weight_bits_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(a, (const __nv_bfloat16 *)d_w, d_lut, d_Wb, items);
+        break;
+    default: return REXSC_E_BAD_ARG;
+    }
+    REXSC_LAUNCH_CHECK("expand_weight_bits_kernel");
     return REXSC_OK;
 }
 
