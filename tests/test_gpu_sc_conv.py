@@ -283,3 +283,64 @@ def test_randomised_shapes_tiled_and_direct_vs_oracle(ops, oracle):
             if ours is None:
                 continue  # shape outside that kernel: the direct kernel covers it
             assert_same(ours, ref, f"trial {trial}: {(N, Cin, H, W, Cout, K, KW, pad, stride, L, or_n, cl, xnor)} {kernel}")
+
+
+TENSOR_CASES = [
+    # N, Cin, H, W, Cout, K, pad, stride, L, or_n, channels_last -- shapes that exercise the tensor-core kernel's
+    # variants: residue planes of strided layers (32-channel steps, several patch rows per thread), odd channel-word
+    # counts (a last chunk with one word), several 64-channel output chunks, tiles that span images, long streams
+    # (per-slot descaling) and plain counting
+    (5, 64, 56, 56, 128, 3, 1, 2, 32, 2, True),    # ResNet stride-2 3x3: 4 residue planes
+    (3, 96, 17, 15, 70, 3, 1, 2, 32, 2, True),     # 3 channel words, ragged Cout, non-square, stride 2
+    (2, 160, 12, 12, 130, 3, 1, 1, 32, 2, True),   # 5 channel words: chunks of 2, 2, 1; three output chunks
+    (2, 64, 12, 12, 64, 2, 0, 2, 32, 2, True),     # 2x2 stride 2
+    (4, 64, 14, 14, 64, 1, 0, 2, 32, 2, True),     # 1x1 stride 2: stored grid keeps residue 0 only
+    (2, 40, 11, 13, 30, 3, 1, 1, 128, 3, False),   # NCHW, L=128: running sums descaled every slot
+    (2, 64, 9, 9, 64, 3, 1, 1, 64, 4, True),       # two word planes, OR-4
+    (70, 32, 4, 4, 8, 3, 1, 1, 32, 1, False),      # tiles span many small images
+    (2, 64, 10, 10, 32, 3, 1, 3, 32, 2, True),     # stride 3: 9 residue planes
+]
+
+
+@pytest.mark.parametrize("case", TENSOR_CASES)
+def test_tensor_kernel_variants_vs_direct(ops, case):
+    """The tensor-core kernel against the direct kernel (itself pinned to the oracle above) on shapes too large for
+    the oracle; both receive the same inputs through the public op."""
+    N, Cin, H, W, Cout, K, pad, stride, L, or_n, cl = case
+    x, w = conv_inputs(N, Cin, H, W, Cout, K, prec=7, seed=hash(case) % 1000)
+    if cl:
+        x = x.contiguous(memory_format=torch.channels_last)
+        w = w.contiguous(memory_format=torch.channels_last)
+    ref = run_ours(ops, x, w, L, pad, stride, or_n, True, "direct")
+    got = _run_or_skip_unsupported(lambda: run_ours(ops, x, w, L, pad, stride, or_n, True, "tensor"), "tensor")
+    if got is None:
+        assert stride == 3, f"{case}: only the 9-plane stride-3 case may be outside the tensor kernel"
+        return
+    assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), str(case)
+    plain = run_ours(ops, x, w, L, pad, stride, 51201, True, "tensor")   # plain counting (n above any count)
+    plain_ref = run_ours(ops, x, w, L, pad, stride, 51201, True, "direct")
+    assert torch.equal(plain[0], plain_ref[0]) and torch.equal(plain[1], plain_ref[1]), f"{case} plain count"
+
+
+def test_auto_kernel_choice(ops):
+    """AUTO resolves to the tensor-core kernel for every layer shape of the bench workload that has >= 32 input
+    channels and at most 9 taps, and to an ALU kernel for thin inputs and large filters."""
+    import ctypes as C
+    from rexsc_b200 import _lib
+    lib = _lib.load()
+
+    def choice(N, Cin, H, Cout, K, stride):
+        d = _lib.ScConvDesc()
+        d.batch, d.c_in, d.h_in, d.w_in, d.c_out, d.kh, d.kw = N, Cin, H, H, Cout, K, K
+        d.stride_h = d.stride_w = stride
+        d.act_channels_last = d.w_channels_last = d.out_channels_last = 1
+        d.bit_length, d.lfsr_length, d.bin_config, d.gen_config, d.xnor = 32, -1, 1, 1, 1
+        d.prog_total_width, d.prog_load_width, d.prog_load_wait = PROG
+        return lib.rexsc_sc_conv2d_kernel_choice(C.byref(d))
+
+    assert choice(256, 64, 58, 64, 3, 1) == 3
+    assert choice(256, 64, 58, 128, 3, 2) == 3
+    assert choice(256, 64, 56, 128, 1, 2) == 3
+    assert choice(256, 512, 9, 512, 3, 1) == 3
+    assert choice(256, 3, 230, 64, 7, 2) in (1, 2)
+    assert choice(32, 3, 36, 32, 5, 1) in (1, 2)
