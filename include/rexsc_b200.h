@@ -39,9 +39,9 @@ enum { REXSC_F32 = 0, REXSC_F16 = 1, REXSC_BF16 = 2 };
 
 /* Which SC conv kernel to use; all give identical results.  DIRECT: one thread per output, any shape and any n.
  * TILED: shared-memory implicit GEMM on the integer ALU pipe (LOP3 thermometers).  TENSOR: one int8 tcgen05 GEMM
- * per time slot with min(count, n) applied to the TMEM accumulators (filters of at most 9 taps).  AUTO picks
- * TENSOR for stride-1 / 1x1 layers with at least 32 input channels, else TILED when the shape fits it, else
- * DIRECT. */
+ * per time slot with min(count, n) applied to the TMEM accumulators (filters of at most 9 taps, any stride whose
+ * residue planes fit its shared-memory patch).  AUTO picks TENSOR whenever the shape fits it and there are at least
+ * 32 input channels, else TILED when the shape fits that, else DIRECT. */
 enum { REXSC_KERNEL_AUTO = 0, REXSC_KERNEL_DIRECT = 1, REXSC_KERNEL_TILED = 2, REXSC_KERNEL_TENSOR = 3 };
 
 /*

@@ -416,6 +416,7 @@ __global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a
                                                               int CW, long long items)
 {
     __shared__ uint8_t q_s[8][32][36];   // [warp][pixel][channel], padded: a lane's row starts in its own bank
+    __shared__ long long xb_s[8][32];    // [warp][pixel] input offset of the pixel's channel 0
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long item = (long long)blockIdx.x * 8 + warp; // neighbouring warps: the channel words of the same pixels
     if (item >= items) return;
@@ -431,24 +432,37 @@ __global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a
     const uint32_t hw_mod = ((uint32_t)h * (uint32_t)a.Wp + (uint32_t)w) % (uint32_t)a.period;
     const long long xbase = NHWC ? (((long long)n * a.H + hi) * a.W + wi) * a.C : (((long long)n * a.C) * a.H + hi) * a.W + wi;
     // quantise the 32 x 32 tile, reading along the input's fastest dimension
+    // (the loads of a batch are all issued before the first value is used: the kernel lives on memory-level
+    // parallelism, its occupancy is limited by the 32 live words of the transpose)
+    constexpr int kBatch = 16;
     if (NHWC) {
+        // lane = channel; the pixels' base offsets are handed over through shared memory (-1: padding, no load)
+        xb_s[warp][lane] = inside ? xbase : -1;
+        __syncwarp();
         const int c = c0 + lane;
-#pragma unroll 4
-        for (int p = 0; p < 32; p++) {
-            const bool ins = __shfl_sync(0xffffffffu, inside ? 1 : 0, p) != 0;
-            const long long xb = __shfl_sync(0xffffffffu, xbase, p);
-            int q = 0;
-            if (ins && c < a.C) q = quant_ceil_unipolar(load_as_float<T>(x, xb + c), a.scale);
-            q_s[warp][p][lane] = (uint8_t)q;
+#pragma unroll
+        for (int p0 = 0; p0 < 32; p0 += kBatch) {
+            float val[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; i++) {
+                const long long xb = xb_s[warp][p0 + i];
+                val[i] = (xb >= 0 && c < a.C) ? load_as_float<T>(x, xb + c) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; i++) q_s[warp][p0 + i][lane] = (uint8_t)quant_ceil_unipolar(val[i], a.scale);
         }
     } else {
         const long long plane = (long long)a.H * a.W;
-#pragma unroll 4
-        for (int cc = 0; cc < 32; cc++) {
-            const int c = c0 + cc;
-            int q = 0;
-            if (inside && c < a.C) q = quant_ceil_unipolar(load_as_float<T>(x, xbase + c * plane), a.scale);
-            q_s[warp][lane][cc] = (uint8_t)q;
+#pragma unroll
+        for (int cc0 = 0; cc0 < 32; cc0 += kBatch) {
+            float val[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; i++) {
+                const int c = c0 + cc0 + i;
+                val[i] = (inside && c < a.C) ? load_as_float<T>(x, xbase + c * plane) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; i++) q_s[warp][lane][cc0 + i] = (uint8_t)quant_ceil_unipolar(val[i], a.scale);
         }
     }
     __syncwarp();
