@@ -48,6 +48,10 @@ RESNET18_SC_LAYERS = [
 ]
 
 
+WORKLOAD = ("SC ResNet-18 224x224 channels_last OR-2 L=32 batch 256/GPU: 19 SC conv2d forwards "
+            "(fp32 padded activations in, int16 pos/neg out) + 38 OR-n activation forwards (fp16 in)")
+
+
 def layer_out(h, k, s, p):
     return (h + 2 * p - k) // s + 1
 
@@ -417,8 +421,10 @@ def run_reference(args, rank, world):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32 bit-streams / int16",
         "data": "synthetic",
-        "config": {"workload": f"SC ResNet-18 224x224 OR-2 L=32 SC-conv forward, CPU reference at batch {sample_batch} "
-                               f"per step (bounded sample of the batch-{BATCH} workload)"},
+        # the same workload as the other arm; a step here is a bounded sample of it (see cpu_baseline.sample): the
+        # reference's CPU extension has no point-wise ops and no XNOR generator
+        "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH,
+                   "sample": f"the 19 SC conv forwards at batch {sample_batch} per step on the host cores"},
         "cpu_baseline": {"value": value, "unit": "img/s", "cores": threads, "kind": kind,
                          "sample": f"19 SC conv layers at batch {sample_batch} per step, xnor=False"},
         "e2e": {"value": value, "unit": "img/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -501,8 +507,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32 bit-streams / int8 0-1 operands / int16", "data": "synthetic",
             "config": {
-                "workload": "SC ResNet-18 224x224 channels_last OR-2 L=32 batch 256/GPU: 19 SC conv2d forwards "
-                            "(fp32 padded activations in, int16 pos/neg out) + 38 OR-n activation forwards (fp16 in)",
+                "workload": WORKLOAD,
                 "batch_per_gpu": BATCH, "parallelism": f"batch-sharded x{world}, no data-path collective",
                 "l2_policy": "inputs larger than L2 (layer activations 13-220 MB, 1.3 GB per step)",
             },
