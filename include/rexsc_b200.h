@@ -117,7 +117,9 @@ int rexsc_sc_conv2d_fwd_static(const rexsc_sc_conv_desc *desc, const void *d_act
  *   accumulate  OR-n accumulation of the stream words into the int16 outputs (replaces im2col + GEMM +
  *               scatter, sc_cuda_kernel.cu:367-562 and sc_device.cu:186-386).
  * fwd == expand followed by accumulate on the same stream.  Splitting lets a caller time the stages or keep
- * expanded streams across calls while the tensors they came from are unchanged.
+ * expanded streams across calls while the tensors they came from are unchanged: expand accepts a null d_act or a
+ * null d_weight (not both) and then leaves that operand's part of the workspace as an earlier expand with the same
+ * descriptor wrote it -- e.g. inference expands the weights of a layer once and only the activations per call.
  */
 int rexsc_sc_conv2d_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                            void *d_workspace, size_t workspace_bytes, void *stream);

@@ -54,15 +54,17 @@ static int conv_buffers(const rexsc_sc_conv_desc *desc, void *d_workspace, size_
     return REXSC_OK;
 }
 
-// stage 1: stream generation (LUTs, activation words, weight words + signs) into the workspace
+// stage 1: stream generation (LUTs, activation words, weight words + signs) into the workspace.
+// allow_partial: a null operand is skipped and what an earlier expand with the same descriptor and workspace wrote
+// for it stays in place (a caller whose weights do not change between calls expands them once).
 static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, void *d_workspace,
-                       size_t workspace_bytes, cudaStream_t st)
+                       size_t workspace_bytes, cudaStream_t st, bool allow_partial)
 {
     ConvPlan p;
     ConvBuffers b;
     int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
     if (rc != REXSC_OK) return rc;
-    if (!d_act || !d_weight) return REXSC_E_BAD_ARG;
+    if (allow_partial ? (!d_act && !d_weight) : (!d_act || !d_weight)) return REXSC_E_BAD_ARG;
     REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
     const int k = resolve_kernel(desc, p);
     if (k < 0) return k;
@@ -73,15 +75,22 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
     if (rc != REXSC_OK) return rc;
     if (k == REXSC_KERNEL_TENSOR) {
         // the tensor-core kernel reads channel-packed bit planes: Ab, then Wb, in the tensor region of the workspace
-        rc = launch_expand_act_bits(p, *desc, d_act, b.lut_a, static_cast<uint32_t *>(b.tc), st);
-        if (rc != REXSC_OK) return rc;
-        return launch_expand_weight_bits(p, *desc, d_weight, b.lut_w,
-                                         reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p)), st);
+        if (d_act) {
+            rc = launch_expand_act_bits(p, *desc, d_act, b.lut_a, static_cast<uint32_t *>(b.tc), st);
+            if (rc != REXSC_OK) return rc;
+        }
+        if (d_weight)
+            rc = launch_expand_weight_bits(p, *desc, d_weight, b.lut_w,
+                                           reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p)), st);
+        return rc;
     }
     // the ALU kernels read time-packed stream words
-    rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
-    if (rc != REXSC_OK) return rc;
-    return launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
+    if (d_act) {
+        rc = launch_expand_act(p, *desc, d_act, b.lut_a, b.A, st);
+        if (rc != REXSC_OK) return rc;
+    }
+    if (d_weight) rc = launch_expand_weight(p, *desc, d_weight, b.lut_w, b.Wt, b.S, st);
+    return rc;
 }
 
 // stage 2: OR-n accumulation over the stream words of the workspace
@@ -109,7 +118,7 @@ int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *
         int rc = make_conv_plan(desc, &p);
         return rc != REXSC_OK ? rc : REXSC_E_BAD_ARG;
     }
-    int rc = conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, st);
+    int rc = conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, st, false);
     if (rc != REXSC_OK) return rc;
     return conv_accumulate(desc, d_out_pos, d_out_neg, d_workspace, workspace_bytes, st);
 }
@@ -165,7 +174,7 @@ extern "C" int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d
 extern "C" int rexsc_sc_conv2d_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                                       void *d_workspace, size_t workspace_bytes, void *stream)
 {
-    return conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, (cudaStream_t)stream);
+    return conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, (cudaStream_t)stream, true);
 }
 
 extern "C" int rexsc_sc_conv2d_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, int16_t *d_out_neg,

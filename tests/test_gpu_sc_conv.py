@@ -344,3 +344,44 @@ def test_auto_kernel_choice(ops):
     assert choice(256, 512, 9, 512, 3, 1) == 3
     assert choice(256, 3, 230, 64, 7, 2) in (1, 2)
     assert choice(32, 3, 36, 32, 5, 1) in (1, 2)
+
+
+@pytest.mark.parametrize("kernel", [1, 2, 3])
+def test_split_expand_keeps_the_other_operand(ops, kernel):
+    """rexsc_sc_conv2d_expand with one null operand leaves the other operand's streams in the workspace: weights
+    expanded once serve several activation tensors (C ABI called the way bench.py does)."""
+    import ctypes as C
+    from rexsc_b200 import _lib
+    lib = _lib.load()
+    N, Cin, H, Cout, K = 3, 64, 10, 40, 3
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.rand(N, Cin, H, H, generator=g).cuda().contiguous(memory_format=torch.channels_last) for _ in range(2)]
+    w = (torch.randn(Cout, Cin, K, K, generator=g) * 0.1).clamp(-1, 1).cuda().contiguous(memory_format=torch.channels_last)
+    d = _lib.ScConvDesc()
+    d.batch, d.c_in, d.h_in, d.w_in, d.c_out, d.kh, d.kw = N, Cin, H, H, Cout, K, K
+    d.stride_h = d.stride_w = 1
+    d.act_channels_last = d.w_channels_last = d.out_channels_last = 1
+    d.bit_length, d.lfsr_length, d.bin_config, d.gen_config, d.xnor = 32, -1, 1, 1, 1
+    d.prog_total_width, d.prog_load_width, d.prog_load_wait = PROG
+    d.kernel = kernel
+    nbytes = lib.rexsc_sc_conv2d_workspace_size(C.byref(d))
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    vp = lambda t: C.c_void_p(t.data_ptr())
+    oh = H - K + 1
+
+    def outputs():
+        pos = torch.empty((N, Cout, oh, oh), dtype=torch.int16, device="cuda", memory_format=torch.channels_last)
+        return pos, torch.empty_like(pos)
+
+    assert lib.rexsc_sc_conv2d_expand(C.byref(d), None, None, vp(ws), nbytes, st) == -1        # REXSC_E_BAD_ARG
+    assert lib.rexsc_sc_conv2d_expand(C.byref(d), None, vp(w), vp(ws), nbytes, st) == 0        # weights once
+    for x in xs:
+        assert lib.rexsc_sc_conv2d_expand(C.byref(d), vp(x), None, vp(ws), nbytes, st) == 0    # activations per call
+        pos, neg = outputs()
+        assert lib.rexsc_sc_conv2d_accumulate(C.byref(d), vp(pos), vp(neg), vp(ws), nbytes, st) == 0
+        ws2 = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        rpos, rneg = outputs()
+        assert lib.rexsc_sc_conv2d_fwd(C.byref(d), vp(x), vp(w), vp(rpos), vp(rneg), vp(ws2), nbytes, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(pos, rpos) and torch.equal(neg, rneg)
