@@ -21,7 +21,8 @@
 //   B_t  the slot's weight bits, [tap][16-channel column][128 rows][16 B].
 // Operand bytes are 0 or a power of two (see kTcMaskA), the accumulators hold 8 * count.
 //
-// One CTA per SM: 16 warps expand operands and fold counts, 2 warps issue MMAs (one per 128-row block; a single
+// One persistent CTA per SM walks its tiles as a single pipeline (a tile's first loads and its store overlap the
+// neighbouring tiles' MMAs): 16 warps expand operands and fold counts, 2 warps issue MMAs (one per 128-row block; a single
 // thread cannot keep the tensor core busy with 128-column MMAs).  A pipeline step is one slot x one chunk of 32 or
 // 64 channels.  Operand buffers and accumulators are double-buffered and every dependence is an mbarrier phase:
 // while the tensor core works through step i, the expanding warps write the operands of step i+1, fold the slot
@@ -57,6 +58,8 @@ struct TcArgs {
     int rows_a;      // patch rows of all planes
     int slots, n_or;
     long long total_o; // candidates = N * Ho * Wo
+    int tiles_x;       // candidate tiles = ceil(total_o / kTcM); a CTA walks tiles blockIdx.x, + gridDim.x, ... of the
+    int total_tiles;   // tiles_x * (64-channel output chunks), output chunk = tile index / tiles_x
     long long NHWp;
     int out_nhwc;
     int descale_each; // 1: running sums would overflow 16 bits in accumulator units, so every slot is descaled
@@ -157,8 +160,14 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const int tid = threadIdx.x, lane = tid & 31;
     // the shuffle tells the compiler what it cannot see: the warp index is the same in every lane
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const long long o0 = (long long)blockIdx.x * kTcM; // first candidate of the tile
-    const int nc = blockIdx.y;                         // 64-channel output chunk
+    // Persistent CTA: it owns tiles blockIdx.x, blockIdx.x + gridDim.x, ... and runs them as ONE pipeline, so a tile's
+    // first loads / expansion and its last epilogue / store overlap the neighbouring tiles' MMAs.
+    const int my_tiles = (a.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto tile_origin = [&](int k, long long &o0, int &nc) {
+        const int L = (int)blockIdx.x + k * (int)gridDim.x;
+        nc = L / a.tiles_x;                                  // 64-channel output chunk
+        o0 = (long long)(L - nc * a.tiles_x) * kTcM;         // first candidate of the tile
+    };
 
     // mbarriers (index = operand buffer or accumulator buffer):
     //   full[b]   operands of a step are in shared memory           (one arrival per expanding warp)
@@ -189,7 +198,6 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcN >> 3) << 17) | ((uint32_t)(kTcSub >> 4) << 24);
     const uint32_t a_lbo = (uint32_t)a.rows_a * 16, b_lbo = kTcN * 16;
     const int wrow_words = KHW * a.CW;                 // weight words per row and slot
-    const uint32_t *Wchunk = Wb + (size_t)nc * a.slots * kTcN * wrow_words;
 
     // running sums: this thread owns row block (warp/4)%2, TMEM lane 32*(warp%4)+lane and 64 columns (warp/8 = 0:
     // positive block, 1: negative block), two 16-bit sums per register as the packed TMEM load delivers them
@@ -210,29 +218,38 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const int w_tap0 = KWC == 2 ? (w_rest0 >> 1) : w_rest0;
     const int w_items = KHW * KWC;                                      // (tap, word) pairs per step
     const size_t w_item_stride = (size_t)(4 / KWC) * a.CW * kTcN;       // item i -> i + 1: 4 pairs further
-    const uint32_t *w_ptr = Wchunk + ((size_t)w_tap0 * a.CW + w_half) * kTcN + w_row; // slot 0, chunk 0, item 0
+    const uint32_t *w_ptr = Wb, *a_plane = Ab, *pf_plane = Ab;
     uint32_t a_off[RA]; // stored-grid position of the thread's patch rows, ~0u: outside the tensor
+    const bool pf_on = (a.CW % KWC) == 0;                                // planes are then visited in storage order
+    int ld_ck = 0, ld_left = 0, ld_tile = -1;
+    // point the loads at tile k of this CTA: slot 0, chunk 0
+    auto load_tile = [&](int k) {
+        long long o0;
+        int nc;
+        tile_origin(k, o0, nc);
+        ld_tile = k;
+        ld_ck = 0;
+        ld_left = a.slots * a.CK;
+        w_ptr = Wb + (size_t)nc * a.slots * kTcN * wrow_words + ((size_t)w_tap0 * a.CW + w_half) * kTcN + w_row; // item 0
+        a_plane = Ab;                                                       // bit plane of slot 0, word 0
+        pf_plane = Ab + (size_t)kTcPrefetch * KWC * a.NHWp;
 #pragma unroll
-    for (int r = 0; r < RA; r++) {
-        const int g = tid + kTcWorkers * r;
-        a_off[r] = ~0u;
-        if (g < a.rows_a) {
-            const int plane = g / a.Mh, q = g - plane * a.Mh;
-            const long long o = o0 + q;
-            if (o < a.total_o) {
-                const int j = (int)(o % a.Wo);
-                const long long t = o / a.Wo;
-                const int i = (int)(t % a.Ho);
-                const long long n = t / a.Ho;
-                const int rh = plane / a.nrw, rw = plane - rh * a.nrw;
-                a_off[r] = (uint32_t)((n * a.Hrows + (long long)i * a.nrh + rh) * a.Wrow + rw * a.Wq + j);
+        for (int r = 0; r < RA; r++) {
+            const int g = tid + kTcWorkers * r;
+            a_off[r] = ~0u;
+            if (g < a.rows_a) {
+                const int plane = g / a.Mh, q = g - plane * a.Mh;
+                const uint32_t o = (uint32_t)o0 + (uint32_t)q; // candidate indices fit 31 bits (checked on the host)
+                if (o < (uint32_t)a.total_o) {
+                    const uint32_t t = o / (uint32_t)a.Wo, j = o - t * (uint32_t)a.Wo;
+                    const uint32_t n = t / (uint32_t)a.Ho, i = t - n * (uint32_t)a.Ho;
+                    const int rh = plane / a.nrw, rw = plane - rh * a.nrw;
+                    a_off[r] = (n * (uint32_t)a.Hrows + i * (uint32_t)a.nrh + (uint32_t)rh) * (uint32_t)a.Wrow +
+                               (uint32_t)(rw * a.Wq) + j; // < NHWp < 2^32
+                }
             }
         }
-    }
-    const uint32_t *a_plane = Ab;                                          // bit plane of slot 0, word 0
-    const bool pf_on = (a.CW % KWC) == 0;                                // planes are then visited in storage order
-    const uint32_t *pf_plane = Ab + (size_t)kTcPrefetch * KWC * a.NHWp;
-    int ld_ck = 0, ld_left = a.slots * a.CK;
+    };
     auto load_bits = [&]() {
         const int words_left = a.CW - ld_ck * KWC; // words of this chunk that exist
 #pragma unroll
@@ -265,6 +282,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             a_plane += (size_t)KWC * a.NHWp;
         }
         pf_plane += (size_t)KWC * a.NHWp;
+        if (ld_left == 0 && ld_tile + 1 < my_tiles) load_tile(ld_tile + 1); // the next call fetches the next tile
     };
     // per-thread shared-memory offsets of the expansion targets (buffer 0)
     const uint32_t b_dst0 = (uint32_t)(((w_tap0 * 2 * KWC + 2 * w_half) * kTcN + w_row) * 16);
@@ -369,7 +387,8 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     };
 
     bool failed = false;
-    const int n_steps = a.slots * a.CK;
+    const int n_steps = a.slots * a.CK;       // pipeline steps of one tile
+    const int total_steps = my_tiles * n_steps; // ... of this CTA; slots are numbered through all of its tiles
     // The warps run unsynchronised; every dependence is an mbarrier phase.  Phase parities: barrier index b is used
     // by steps (or slots) b, b + 2, ...; its k-th completion has parity k & 1.  A timed-out wait ends the warp's
     // loop; the warps that depend on it time out in turn, so everybody reaches the end of the kernel.
@@ -381,60 +400,20 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         __syncwarp();
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
     };
-    if (warp >= kTcWorkers / 32) {
-        // ---- MMA-issuing warps: operands ready -> accumulator free -> issue -> commit ----
-        int s = 0, ck = 0;
-        for (int step = 0; step < n_steps; step++) {
-            if (!wait_on(&bar_full[step & 1], step >> 1)) { failed = true; break; }
-            if (ck == 0 && s >= 2 && !wait_on(&bar_tfree[s & 1], (s >> 1) - 1)) { failed = true; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            issue_mmas(step, s, ck);
-            if (++ck == a.CK) { ck = 0; s++; }
-        }
-    } else {
-        // ---- expanding / folding warps ----
-        load_bits();
-        expand_bits(0);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        warp_arrive(&bar_full[0]);
-        if (n_steps > 1) load_bits();
-        int s_prev = 0, ck_prev = -1; // slot and chunk of step - 1
-        for (int step = 0; step <= n_steps; step++) {
-            // the previous step's MMAs: its operand buffer is free again and, after the last chunk of a slot, the
-            // slot's counts are complete
-            if (step > 0) {
-                if (!wait_on(&bar_empty[(step - 1) & 1], (step - 1) >> 1)) { failed = true; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            if (step + 1 < n_steps) {
-                expand_bits((step + 1) & 1);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                warp_arrive(&bar_full[(step + 1) & 1]);
-                if (step + 2 < n_steps) load_bits();
-            }
-            // fold the slot that the previous step completed and hand its accumulators back
-            if (ck_prev == a.CK - 1) {
-                slot_epilogue(s_prev & 1);
-                warp_arrive(&bar_tfree[s_prev & 1]);
-            }
-            if (++ck_prev == a.CK) { ck_prev = 0; s_prev++; }
-        }
-    }
-    if (failed && lane == 0) atomicExch(status, 4);
-
-    // a failed warp leaves its share of the output unwritten; the status word reports it
-    if (!failed && warp < kTcWorkers / 32) {
-        // ---- store: row = one candidate of the origin grid; it is an output pixel iff i < OH and j < OW ----
+    // running sums -> int16 outputs of the tile whose last slot has just been folded; a row is one candidate of the
+    // origin grid, it is an output pixel iff i < OH and j < OW
+    auto store_tile = [&](int k) {
+        long long o0;
+        int nc;
+        tile_origin(k, o0, nc);
         if (!a.descale_each) {
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[j] = (acc[j] >> kTcScaleLog2) & kDescaleMask;
         }
-        const long long o = o0 + ((warp >> 2) & 1) * kTcSub + (warp & 3) * 32 + lane;
-        if (o < a.total_o) {
-            const int ow = (int)(o % a.Wo);
-            const long long t = o / a.Wo;
-            const int oh = (int)(t % a.Ho);
-            const long long n = t / a.Ho;
+        const uint32_t o = (uint32_t)o0 + (uint32_t)(((warp >> 2) & 1) * kTcSub + (warp & 3) * 32 + lane);
+        if (o < (uint32_t)a.total_o) {
+            const uint32_t t = o / (uint32_t)a.Wo, n = t / (uint32_t)a.Ho;
+            const int ow = (int)(o - t * (uint32_t)a.Wo), oh = (int)(t - n * (uint32_t)a.Ho);
             if (ow < a.OW && oh < a.OH) {
                 const int co0 = nc * kTcCout;
                 const size_t ohw = (size_t)a.OH * a.OW;
@@ -460,7 +439,57 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 }
             }
         }
+#pragma unroll
+        for (int j = 0; j < 32; j++) acc[j] = 0u;
+    };
+    if (warp >= kTcWorkers / 32) {
+        // ---- MMA-issuing warps: operands ready -> accumulator free -> issue -> commit ----
+        int s = 0, ck = 0; // slot (counted through all tiles) and chunk of the step
+        for (int step = 0; step < total_steps; step++) {
+            if (!wait_on(&bar_full[step & 1], step >> 1)) { failed = true; break; }
+            if (ck == 0 && s >= 2 && !wait_on(&bar_tfree[s & 1], (s >> 1) - 1)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_mmas(step, s, ck);
+            if (++ck == a.CK) { ck = 0; s++; }
+        }
+    } else {
+        // ---- expanding / folding warps ----
+        load_tile(0);
+        load_bits();
+        expand_bits(0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        warp_arrive(&bar_full[0]);
+        if (total_steps > 1) load_bits();
+        int s_prev = 0, ck_prev = -1; // slot (counted through all tiles) and chunk of step - 1
+        int tile_prev = 0, slot_in_tile_prev = 0;
+        for (int step = 0; step <= total_steps; step++) {
+            // the previous step's MMAs: its operand buffer is free again and, after the last chunk of a slot, the
+            // slot's counts are complete
+            if (step > 0) {
+                if (!wait_on(&bar_empty[(step - 1) & 1], (step - 1) >> 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (step + 1 < total_steps) {
+                expand_bits((step + 1) & 1);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                warp_arrive(&bar_full[(step + 1) & 1]);
+                if (step + 2 < total_steps) load_bits();
+            }
+            // fold the slot that the previous step completed and hand its accumulators back
+            if (ck_prev == a.CK - 1) {
+                slot_epilogue(s_prev & 1);
+                warp_arrive(&bar_tfree[s_prev & 1]);
+                if (++slot_in_tile_prev == a.slots) {
+                    store_tile(tile_prev);
+                    tile_prev++;
+                    slot_in_tile_prev = 0;
+                }
+            }
+            if (++ck_prev == a.CK) { ck_prev = 0; s_prev++; }
+        }
     }
+    if (failed && lane == 0) atomicExch(status, 4);
+    // (a warp whose wait timed out leaves its share of the remaining tiles unwritten; the status word reports it)
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -600,7 +629,8 @@ bool conv_tc_supported(const ConvPlan &p)
     if (((long long)p.Kdot << kTcScaleLog2) > 65535) return false;            // 16-bit packed accumulator reads
     if (p.Kdot > (1 << 24)) return false;
     const long long total_o = (long long)p.N * g.Ho * g.Wo;
-    if ((total_o + kTcM - 1) / kTcM > 0x7fffffffLL) return false;
+    if (total_o + kTcM > 0x7fffffffLL) return false;                          // 31-bit candidate indices
+    if ((total_o + kTcM - 1) / kTcM * ((p.Co + kTcCout - 1) / kTcCout) > 0x7fffffffLL) return false; // tile index: int
     if (p.NHWp > 0xfffffffeLL) return false;                                  // 32-bit position offsets
     return true;
 }
@@ -637,6 +667,8 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     a.Ho = g.Ho; a.Wo = g.Wo; a.Mh = g.Mh; a.rows_a = g.rows_a;
     a.slots = slots;
     a.total_o = (long long)p.N * g.Ho * g.Wo;
+    a.tiles_x = (int)((a.total_o + kTcM - 1) / kTcM);
+    a.total_tiles = a.tiles_x * NC;
     a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
     {
         const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;
@@ -644,7 +676,11 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
         a.n_or = (int)cap; // a count never exceeds the dot length, so clamping there changes nothing
     }
     for (int t = 0; t < kTcMaxTaps; t++) a.tap_off[t] = g.tap_off[t];
-    dim3 grid((unsigned)((a.total_o + kTcM - 1) / kTcM), (unsigned)NC);
+    // one persistent CTA per SM (the kernel owns the SM's tensor memory), fewer when there are fewer tiles
+    int dev = 0, sms = 0;
+    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
+    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const unsigned grid = (unsigned)(a.total_tiles < sms ? a.total_tiles : sms);
     const int ra = (g.rows_a + kTcWorkers - 1) / kTcWorkers;
     auto pick = [&](auto khw_tag) {
         constexpr int KHW_T = decltype(khw_tag)::value;
