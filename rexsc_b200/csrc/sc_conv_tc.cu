@@ -59,7 +59,10 @@ struct TcArgs {
     int slots, n_or;
     long long total_o; // candidates = N * Ho * Wo
     int tiles_x;       // candidate tiles = ceil(total_o / kTcM); a CTA walks tiles blockIdx.x, + gridDim.x, ... of the
-    int total_tiles;   // tiles_x * (64-channel output chunks), output chunk = tile index / tiles_x
+    int total_tiles;   // tiles_x * (64-channel output chunks) * split; tile index = (part * chunks + chunk) * tiles_x + x
+    int split;         // 1, or 2: a tile covers half of the time slots and adds its sums into zeroed outputs with
+                       // packed 16-bit atomics -- fills the last wave when there are few tiles per SM
+    int slots_part;    // slots / split
     long long NHWp;
     int out_nhwc;
     int descale_each; // 1: running sums would overflow 16 bits in accumulator units, so every slot is descaled
@@ -142,7 +145,8 @@ __device__ __forceinline__ void spread32(uint32_t h, uint4 &lo16, uint4 &hi16)
 
 // KHW_T: taps known at compile time (9, 1) or 0 for any tap count up to kTcMaxTaps
 // KWC:   32-channel words per pipeline step (TcArgs::KWc);  RA: patch rows per expanding thread (1 .. kTcMaxARows)
-template <int KHW_T, int KWC, int RA>
+// SPLIT: tiles cover a share of the time slots and add into the outputs (TcArgs::split > 1)
+template <int KHW_T, int KWC, int RA, bool SPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__restrict__ Wb,
                   int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status)
@@ -163,10 +167,13 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // Persistent CTA: it owns tiles blockIdx.x, blockIdx.x + gridDim.x, ... and runs them as ONE pipeline, so a tile's
     // first loads / expansion and its last epilogue / store overlap the neighbouring tiles' MMAs.
     const int my_tiles = (a.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    auto tile_origin = [&](int k, long long &o0, int &nc) {
+    const int n_chunks = SPLIT ? a.total_tiles / (a.tiles_x * a.split) : 1;
+    auto tile_origin = [&](int k, long long &o0, int &nc, int &part) {
         const int L = (int)blockIdx.x + k * (int)gridDim.x;
-        nc = L / a.tiles_x;                                  // 64-channel output chunk
-        o0 = (long long)(L - nc * a.tiles_x) * kTcM;         // first candidate of the tile
+        const int t = L / a.tiles_x;
+        o0 = (long long)(L - t * a.tiles_x) * kTcM;          // first candidate of the tile
+        part = SPLIT ? t / n_chunks : 0;                     // which share of the time slots
+        nc = t - part * n_chunks;                            // 64-channel output chunk
     };
 
     // mbarriers (index = operand buffer or accumulator buffer):
@@ -225,14 +232,15 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // point the loads at tile k of this CTA: slot 0, chunk 0
     auto load_tile = [&](int k) {
         long long o0;
-        int nc;
-        tile_origin(k, o0, nc);
+        int nc, part;
+        tile_origin(k, o0, nc, part);
+        const int slot0 = part * a.slots_part;                             // first slot of the tile
         ld_tile = k;
         ld_ck = 0;
-        ld_left = a.slots * a.CK;
-        w_ptr = Wb + (size_t)nc * a.slots * kTcN * wrow_words + ((size_t)w_tap0 * a.CW + w_half) * kTcN + w_row; // item 0
-        a_plane = Ab;                                                       // bit plane of slot 0, word 0
-        pf_plane = Ab + (size_t)kTcPrefetch * KWC * a.NHWp;
+        ld_left = a.slots_part * a.CK;
+        w_ptr = Wb + ((size_t)nc * a.slots + slot0) * kTcN * wrow_words + ((size_t)w_tap0 * a.CW + w_half) * kTcN + w_row;
+        a_plane = Ab + (size_t)slot0 * a.CW * a.NHWp;                       // bit plane of the first slot, word 0
+        pf_plane = a_plane + (size_t)kTcPrefetch * KWC * a.NHWp;
 #pragma unroll
         for (int r = 0; r < RA; r++) {
             const int g = tid + kTcWorkers * r;
@@ -387,7 +395,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     };
 
     bool failed = false;
-    const int n_steps = a.slots * a.CK;       // pipeline steps of one tile
+    const int n_steps = a.slots_part * a.CK;  // pipeline steps of one tile
     const int total_steps = my_tiles * n_steps; // ... of this CTA; slots are numbered through all of its tiles
     // The warps run unsynchronised; every dependence is an mbarrier phase.  Phase parities: barrier index b is used
     // by steps (or slots) b, b + 2, ...; its k-th completion has parity k & 1.  A timed-out wait ends the warp's
@@ -404,8 +412,8 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // origin grid, it is an output pixel iff i < OH and j < OW
     auto store_tile = [&](int k) {
         long long o0;
-        int nc;
-        tile_origin(k, o0, nc);
+        int nc, part;
+        tile_origin(k, o0, nc, part);
         if (!a.descale_each) {
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[j] = (acc[j] >> kTcScaleLog2) & kDescaleMask;
@@ -421,7 +429,13 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 int16_t *dst = (warp >> 3) ? out_neg : out_pos;
                 if (a.out_nhwc) {
                     int16_t *row = dst + m * a.Co + co0;
-                    if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
+                    if (SPLIT) {
+                        // partial sums of this share of the slots: two int16 per 32-bit add, no carry can cross the
+                        // halves because the complete sums fit 16 bits (the host enables this for aligned rows only)
+                        unsigned int *row32 = reinterpret_cast<unsigned int *>(row);
+#pragma unroll
+                        for (int j = 0; j < 32; j++) atomicAdd(row32 + j, acc[j]);
+                    } else if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
                             *reinterpret_cast<uint4 *>(row + 2 * j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
@@ -479,7 +493,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             if (ck_prev == a.CK - 1) {
                 slot_epilogue(s_prev & 1);
                 warp_arrive(&bar_tfree[s_prev & 1]);
-                if (++slot_in_tile_prev == a.slots) {
+                if (++slot_in_tile_prev == a.slots_part) {
                     store_tile(tile_prev);
                     tile_prev++;
                     slot_in_tile_prev = 0;
@@ -668,7 +682,28 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     a.slots = slots;
     a.total_o = (long long)p.N * g.Ho * g.Wo;
     a.tiles_x = (int)((a.total_o + kTcM - 1) / kTcM);
-    a.total_tiles = a.tiles_x * NC;
+    int dev = 0, sms = 0;
+    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
+    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // Few tiles per SM: the last wave of whole tiles leaves SMs idle.  Half-length tiles (each half of the time slots,
+    // summed with atomics) waste less when that saves more than the extra prologues cost.
+    a.split = 1;
+    {
+        const long long tiles = (long long)a.tiles_x * NC;
+        const double whole = (double)((tiles + sms - 1) / sms), halves = (double)((2 * tiles + sms - 1) / sms) / 2.0;
+        const bool rows_ok = d.out_channels_last && (p.Co % kTcCout) == 0;
+        // (measured: tiles of strided layers -- several patch rows per thread, 32-channel steps -- lose more at the extra
+        // tile switches than the fuller wave gains)
+        const bool long_tiles = g.rows_a <= kTcWorkers && (slots / 2) * g.CK >= 32;
+        if (rows_ok && long_tiles && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL) a.split = 2;
+    }
+    a.slots_part = slots / a.split;
+    a.total_tiles = a.tiles_x * NC * a.split;
+    if (a.split > 1) {
+        const size_t out_bytes = (size_t)p.M * p.Co * sizeof(int16_t);
+        REXSC_CUDA_CHECK(cudaMemsetAsync(d_pos, 0, out_bytes, st));
+        REXSC_CUDA_CHECK(cudaMemsetAsync(d_neg, 0, out_bytes, st));
+    }
     a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
     {
         const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;
@@ -677,15 +712,14 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     }
     for (int t = 0; t < kTcMaxTaps; t++) a.tap_off[t] = g.tap_off[t];
     // one persistent CTA per SM (the kernel owns the SM's tensor memory), fewer when there are fewer tiles
-    int dev = 0, sms = 0;
-    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
-    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const unsigned grid = (unsigned)(a.total_tiles < sms ? a.total_tiles : sms);
     const int ra = (g.rows_a + kTcWorkers - 1) / kTcWorkers;
     auto pick = [&](auto khw_tag) {
         constexpr int KHW_T = decltype(khw_tag)::value;
-        if (g.KWc == 2) return ra == 1 ? sc_conv_tc_kernel<KHW_T, 2, 1> : sc_conv_tc_kernel<KHW_T, 2, kTcMaxARows>;
-        return ra == 1 ? sc_conv_tc_kernel<KHW_T, 1, 1> : sc_conv_tc_kernel<KHW_T, 1, kTcMaxARows>;
+        if (a.split > 1) // enabled for one-row-per-thread geometries only
+            return g.KWc == 2 ? sc_conv_tc_kernel<KHW_T, 2, 1, true> : sc_conv_tc_kernel<KHW_T, 1, 1, true>;
+        if (g.KWc == 2) return ra == 1 ? sc_conv_tc_kernel<KHW_T, 2, 1, false> : sc_conv_tc_kernel<KHW_T, 2, kTcMaxARows, false>;
+        return ra == 1 ? sc_conv_tc_kernel<KHW_T, 1, 1, false> : sc_conv_tc_kernel<KHW_T, 1, kTcMaxARows, false>;
     };
     auto kernel = p.KHW == 9 ? pick(std::integral_constant<int, 9>{})
                 : p.KHW == 1 ? pick(std::integral_constant<int, 1>{}) : pick(std::integral_constant<int, 0>{});
