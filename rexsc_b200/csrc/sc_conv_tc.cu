@@ -219,7 +219,9 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // loads walk the steps in order, so the step-dependent part of every address is a running pointer.
     //   weights: item e = tid + 512*i, row = e & 127, (tap, word) = e >> 7  -> wbits[i]
     //   patch:   row g = tid + 512*r of the residue planes                  -> abits[r][word]
-    uint32_t wbits[kTcMaxBWords], abits[RA][KWC];
+    // weight words per thread and step: ceil(taps * words / 4) when the tap count is known at compile time
+    constexpr int kMyB = KHW_T ? (KHW_T * KWC + 3) / 4 : kTcMaxBWords;
+    uint32_t wbits[kMyB], abits[RA][KWC];
     const int w_row = tid & (kTcN - 1), w_rest0 = tid >> 7;               // (tap, word) index of item 0
     const int w_half = KWC == 2 ? (w_rest0 & 1) : 0;
     const int w_tap0 = KWC == 2 ? (w_rest0 >> 1) : w_rest0;
@@ -261,7 +263,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     auto load_bits = [&]() {
         const int words_left = a.CW - ld_ck * KWC; // words of this chunk that exist
 #pragma unroll
-        for (int i = 0; i < kTcMaxBWords; i++) {
+        for (int i = 0; i < kMyB; i++) {
             const bool ok = w_rest0 + 4 * i < w_items && w_half < words_left;
             wbits[i] = ok ? __ldg(w_ptr + i * w_item_stride) : 0u;
         }
@@ -298,7 +300,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     auto expand_bits = [&](int buf) {
         uint8_t *b_s = b_buf(buf) + b_dst0, *a_s = a_buf(buf) + (uint32_t)tid * 16;
 #pragma unroll
-        for (int i = 0; i < kTcMaxBWords; i++) {
+        for (int i = 0; i < kMyB; i++) {
             if (w_rest0 + 4 * i < w_items) {
                 uint8_t *dst = b_s + i * (8 * kTcN * 16); // 4 (tap, word) pairs = 8 K-columns further
                 uint4 lo16, hi16;
