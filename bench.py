@@ -505,7 +505,7 @@ def main():
             "metric": "sc_resnet18_or2_L32_sc_forward_img_per_s", "value": value, "unit": "img/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms"] / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u32 bit-streams / int8 0-1 operands / int16", "data": "synthetic",
+            "dtype": "u32 bit-streams / int8 tensor-core operands, int32 accumulators / int16 sums", "data": "synthetic",
             "config": {
                 "workload": WORKLOAD,
                 "batch_per_gpu": BATCH, "parallelism": f"batch-sharded x{world}, no data-path collective",
