@@ -410,16 +410,31 @@ __device__ __forceinline__ void transpose32_regs(uint32_t (&v)[32])
     }
 }
 
-template <typename T, bool NHWC>
+// SMEM_LUT: the stream table (a few KB at the common stream lengths) is copied into shared memory first.  A warp's 32
+// lookups are a random gather; from L1 that costs one tag pass per distinct 128-byte line (about 20 per load for a
+// 4 KB table), from shared memory one pass per bank conflict (about 3).  Each warp then works through kItemsPerWarp
+// items so that the copy is amortised.
+constexpr int kActItemsPerWarp = 4;
+template <typename T, bool NHWC, bool SMEM_LUT>
 __global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a, const T *__restrict__ x,
-                                                              const uint32_t *__restrict__ lut, uint32_t *__restrict__ Ab,
+                                                              const uint32_t *__restrict__ lut_g, uint32_t *__restrict__ Ab,
                                                               int CW, long long items)
 {
     __shared__ uint8_t q_s[8][32][36];   // [warp][pixel][channel], padded: a lane's row starts in its own bank
     __shared__ long long xb_s[8][32];    // [warp][pixel] input offset of the pixel's channel 0
+    extern __shared__ __align__(16) uint32_t lut_s[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long item = (long long)blockIdx.x * 8 + warp; // neighbouring warps: the channel words of the same pixels
-    if (item >= items) return;
+    if (SMEM_LUT) {
+        const int lut_words = a.period * a.nvals * a.words;
+        for (int i = threadIdx.x; i < lut_words; i += blockDim.x) lut_s[i] = __ldg(lut_g + i);
+        __syncthreads();
+    }
+    const uint32_t *lut = SMEM_LUT ? lut_s : lut_g;
+    const int n_iter = SMEM_LUT ? kActItemsPerWarp : 1;
+    for (int it = 0; it < n_iter; it++) {
+    // neighbouring warps: the channel words of the same pixels
+    const long long item = ((long long)blockIdx.x * n_iter + it) * 8 + warp;
+    if (item >= items) return; // warp-uniform, and no block-wide barrier follows
     const int cw = (int)(item % CW);
     const long long P0 = (item / CW) * 32;
     const int c0 = cw * 32;
@@ -480,7 +495,8 @@ __global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a
             const int q = q_s[warp][lane][cc];
             uint32_t phase = cph + pix_mod;
             if (phase >= period) phase -= period;
-            v[cc] = q > 0 ? __ldg(lut + ((size_t)phase * a.nvals + q) * a.words + wd) : 0u;
+            v[cc] = q > 0 ? (SMEM_LUT ? lut[(phase * (uint32_t)a.nvals + (uint32_t)q) * (uint32_t)a.words + (uint32_t)wd]
+                                      : __ldg(lut + ((size_t)phase * a.nvals + q) * a.words + wd)) : 0u;
             cph += step_mod;
             if (cph >= period) cph -= period;
         }
@@ -494,6 +510,8 @@ __global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a
                 dst += slot_stride;
             }
         }
+    }
+    __syncwarp(); // the warp's tiles are rewritten by its next item
     }
 }
 
@@ -509,15 +527,18 @@ int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     a.scale = (float)p.nvals;
     const int CW = (p.C + 31) / 32;
     const long long items = ((p.NHWp + 31) / 32) * CW;
-    const long long blocks = (items + 7) / 8;
+    const size_t lut_bytes = (size_t)p.period * p.nvals * p.words * sizeof(uint32_t);
+    const bool smem_lut = lut_bytes <= 16 * 1024; // larger tables (stream lengths above 64) stay in global memory / L1
+    const int per_warp = smem_lut ? kActItemsPerWarp : 1;
+    const long long blocks = (items + 8 * per_warp - 1) / (8 * per_warp);
     if (blocks > 0x7fffffffLL) return REXSC_E_TOO_LONG;
     const bool nhwc = d.act_channels_last != 0;
+#define REXSC_ACT_BITS2(T, NHWC_, SM_)                                                                                  \
+    expand_act_bits_kernel<T, NHWC_, SM_><<<(unsigned)blocks, 256, SM_ ? lut_bytes : 0, st>>>((a), (const T *)d_act, d_lut, d_Ab, CW, items)
 #define REXSC_ACT_BITS(T)                                                                                              \
     do {                                                                                                               \
-        if (nhwc)                                                                                                      \
-            expand_act_bits_kernel<T, true><<<(unsigned)blocks, 256, 0, st>>>(a, (const T *)d_act, d_lut, d_Ab, CW, items); \
-        else                                                                                                           \
-            expand_act_bits_kernel<T, false><<<(unsigned)blocks, 256, 0, st>>>(a, (const T *)d_act, d_lut, d_Ab, CW, items); \
+        if (nhwc) { if (smem_lut) REXSC_ACT_BITS2(T, true, true); else REXSC_ACT_BITS2(T, true, false); }              \
+        else { if (smem_lut) REXSC_ACT_BITS2(T, false, true); else REXSC_ACT_BITS2(T, false, false); }                 \
     } while (0)
     switch (d.act_dtype) {
     case REXSC_F32: REXSC_ACT_BITS(float); break;
@@ -526,6 +547,7 @@ int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     default: return REXSC_E_BAD_ARG;
     }
 #undef REXSC_ACT_BITS
+#undef REXSC_ACT_BITS2
     REXSC_LAUNCH_CHECK("expand_act_bits_kernel");
     return REXSC_OK;
 }
