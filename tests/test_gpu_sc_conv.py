@@ -385,3 +385,37 @@ def test_split_expand_keeps_the_other_operand(ops, kernel):
         assert lib.rexsc_sc_conv2d_fwd(C.byref(d), vp(x), vp(w), vp(rpos), vp(rneg), vp(ws2), nbytes, st) == 0
         torch.cuda.synchronize()
         assert torch.equal(pos, rpos) and torch.equal(neg, rneg)
+
+
+def test_randomised_tensor_kernel_vs_direct(ops):
+    """40 seeded random layer shapes in the tensor-core kernel's range (32..256 input channels, 1x1 / 2x2 / 3x3
+    filters, stride 1 or 2, ragged output channels, up to 40 images): persistent tile loops with partial last tiles,
+    slot-split tiles, residue planes and odd channel-word counts all occur.  The direct kernel is the reference."""
+    import random
+
+    rng = random.Random(7)
+    ran = 0
+    for trial in range(40):
+        K = rng.choice([1, 3, 3, 3, 2])
+        stride = rng.choice([1, 1, 2])
+        pad = rng.choice([0, 1]) if K > 1 else 0
+        Cin = rng.choice([32, 48, 64, 96, 128, 160, 256])
+        Cout = rng.choice([8, 64, 64, 128, 192, 70])
+        H, W, N = rng.randint(max(K, 4), 40), rng.randint(max(K, 4), 40), rng.randint(1, 40)
+        L = rng.choice([32, 32, 64])
+        or_n = rng.choice([1, 2, 2, 3, 51201])
+        cl = rng.random() < 0.7
+        g = torch.Generator(device="cuda").manual_seed(trial)
+        x = torch.rand(N, Cin, H, W, device="cuda", generator=g)
+        w = (torch.randn(Cout, Cin, K, K, device="cuda", generator=g) * 0.05).clamp(-1, 1)
+        if cl:
+            x = x.contiguous(memory_format=torch.channels_last)
+            w = w.contiguous(memory_format=torch.channels_last)
+        got = _run_or_skip_unsupported(lambda: run_ours(ops, x, w, L, pad, stride, or_n, True, "tensor"), "tensor")
+        if got is None:
+            continue
+        ref = run_ours(ops, x, w, L, pad, stride, or_n, True, "direct")
+        what = f"trial {trial}: {(N, Cin, H, W, Cout, K, pad, stride, L, or_n, cl)}"
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), what
+        ran += 1
+    assert ran >= 30
