@@ -697,7 +697,10 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
         // (measured: tiles of strided layers -- several patch rows per thread, 32-channel steps -- lose more at the extra
         // tile switches than the fuller wave gains)
         const bool long_tiles = g.rows_a <= kTcWorkers && (slots / 2) * g.CK >= 32;
-        if (rows_ok && long_tiles && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL) a.split = 2;
+        // and the atomic adds cost about as much as they save once the outputs are tens of MB (measured at 28x28)
+        const bool small_out = (size_t)p.M * p.Co * sizeof(int16_t) <= (size_t)16 << 20;
+        if (rows_ok && long_tiles && small_out && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL)
+            a.split = 2;
     }
     a.slots_part = slots / a.split;
     a.total_tiles = a.tiles_x * NC * a.split;
