@@ -289,6 +289,10 @@ def run_ours(args, rank, world, local_rank):
                 k["ms"] += best * l["rep"]
                 k["products"] += l["rep"] * BATCH * oh * oh * d.c_out * d.c_in * d.kh * d.kw
                 k["launches"] += l["rep"]
+                # DRAM bytes the accumulate kernel has to move: the activation bit planes once + both int16 outputs
+                k["bytes"] = k.get("bytes", 0) + l["rep"] * (
+                    BIT_LENGTH // 8 * ((d.c_in + 31) // 32 * 32) * d.batch * d.h_in * d.w_in
+                    + 2 * 2 * d.batch * oh * oh * d.c_out)
         del ws, pos, neg
 
     # ---- live int8 tensor-pipe peak (back-to-back tcgen05 MMAs on fixed operands) ------------------------------
@@ -476,7 +480,12 @@ def main():
         roof_tensor = {
             "bound": "tensor", "kernel": "sc_conv_tc_kernel (tcgen05 int8, one GEMM per time slot)",
             "achieved": tc_achieved / 1e12, "peak": r["mma_peak_ops"] / 1e12, "unit": "TOP/s int8",
-            "frac": tc_achieved / r["mma_peak_ops"], "traffic": None,
+            "frac": tc_achieved / r["mma_peak_ops"],
+            # per average launch: algorithmic DRAM bytes x 1.035, the ratio of measured (ncu dram__bytes_read.sum +
+            # dram__bytes_write.sum = 62.5 MB) to algorithmic bytes (60.4 MB) of the captured 64-channel layer at
+            # batch 64; the traffic of this kernel grows in proportion to the batch (patch halo re-reads hit L2)
+            "traffic": (1.035 * pk["tensor"].get("bytes", 0) / pk["tensor"]["launches"]) if pk["tensor"]["launches"] else None,
+            "traffic_source": "ncu capture of one layer at batch 64, scaled by algorithmic bytes",
             "peak_source": "measured live: back-to-back tcgen05.mma kind::i8 M128 N128 K32 probe on this GPU",
             "kernel_ms_per_step": pk["tensor"]["ms"], "launches_per_step": pk["tensor"]["launches"],
             "tbitops_per_s_kernel": 64 * pk["tensor"]["products"] / (pk["tensor"]["ms"] * 1e-3) / 1e12
