@@ -149,6 +149,78 @@ def conv2d_generic_general_split_acc(input: torch.Tensor, weight: torch.Tensor, 
     return [pos, neg]
 
 
+class PreparedConv:
+    """SC conv2d whose weight streams are generated once and reused for every activation tensor of one shape
+    (not in the reference, which regenerates both operands' streams on every call -- its results are the same).
+
+    For evaluation / inference loops where the weights do not change between calls::
+
+        conv = ops.PreparedConv(weight, input.shape, input.dtype, channels_last, bit_length, lfsr_length, padding,
+                                stride, prog_load, bin_config, gen_config, xnor)
+        pos, neg = conv(input)          # as often as needed; build a new object after the weights change
+
+    The object owns its workspace (activation + weight streams of that layer)."""
+
+    def __init__(self, weight: torch.Tensor, input_shape, input_dtype, channels_last: bool, bit_length: int,
+                 lfsr_length: int, padding: Sequence[int], stride: Sequence[int], prog_load: Sequence[int],
+                 bin_config: int, gen_config: int, xnor: bool):
+        _require_cuda(weight, "PreparedConv")
+        if weight.dim() != 4 or len(input_shape) != 4 or int(input_shape[1]) != weight.size(1):
+            raise ValueError("PreparedConv: expected input shape [N,C,H,W] and weight [Co,C,KH,KW]")
+        if input_dtype not in _DTYPES:
+            raise ValueError("PreparedConv: activations must be float32, float16 or bfloat16")
+        lib = _lib.load()
+        self._dev = weight.device
+        self._shape = tuple(int(v) for v in input_shape)
+        self._dtype = input_dtype
+        self._cl = bool(channels_last)
+        with torch.cuda.device(self._dev):
+            w_cl = _is_channels_last(weight)
+            w = _dense(_float_kind(weight), w_cl)
+            d = _lib.ScConvDesc()
+            d.batch, d.c_in, d.h_in, d.w_in = self._shape
+            d.c_out, _, d.kh, d.kw = w.shape
+            d.pad_w, d.pad_h = int(padding[0]), int(padding[1])
+            d.stride_h, d.stride_w = int(stride[0]), int(stride[1])
+            d.act_dtype, d.act_channels_last = _DTYPES[input_dtype], int(self._cl)
+            d.w_dtype, d.w_channels_last = _DTYPES[w.dtype], int(w_cl)
+            d.out_channels_last = int(self._cl)
+            d.bit_length, d.lfsr_length = int(bit_length), int(lfsr_length)
+            d.bin_config, d.gen_config, d.xnor = int(bin_config), int(gen_config), int(bool(xnor))
+            d.prog_total_width, d.prog_load_width, d.prog_load_wait = (int(v) for v in prog_load)
+            d.linear_seeds = 0
+            d.kernel = _kernel()
+            nbytes = lib.rexsc_sc_conv2d_workspace_size(C.byref(d))
+            if nbytes == 0:
+                raise ValueError("PreparedConv: unsupported shape or configuration")
+            self._d = d
+            self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self._dev)
+            self._oh = (d.h_in + 2 * d.pad_h - d.kh) // d.stride_h + 1
+            self._ow = (d.w_in + 2 * d.pad_w - d.kw) // d.stride_w + 1
+            rc = lib.rexsc_sc_conv2d_expand(C.byref(d), None, _ptr(w), _ptr(self._ws), nbytes, _stream(self._dev))
+            _lib.check(rc, "rexsc_sc_conv2d_expand (weights)")
+
+    def __call__(self, input: torch.Tensor) -> List[torch.Tensor]:
+        _require_cuda(input, "PreparedConv")
+        fmt = torch.channels_last if self._cl else torch.contiguous_format
+        if (tuple(input.shape) != self._shape or input.dtype != self._dtype or input.device != self._dev
+                or not input.is_contiguous(memory_format=fmt)):
+            raise ValueError("PreparedConv: the input does not match the shape, dtype, device or memory format the "
+                             "object was prepared for")
+        lib = _lib.load()
+        d = self._d
+        with torch.cuda.device(self._dev):
+            pos = torch.empty((d.batch, d.c_out, self._oh, self._ow), dtype=torch.int16, device=self._dev,
+                              memory_format=fmt)
+            neg = torch.empty_like(pos)
+            st = _stream(self._dev)
+            rc = lib.rexsc_sc_conv2d_expand(C.byref(d), _ptr(input), None, _ptr(self._ws), self._ws.numel(), st)
+            _lib.check(rc, "rexsc_sc_conv2d_expand (activations)")
+            rc = lib.rexsc_sc_conv2d_accumulate(C.byref(d), _ptr(pos), _ptr(neg), _ptr(self._ws), self._ws.numel(), st)
+            _lib.check(rc, "rexsc_sc_conv2d_accumulate")
+        return [pos, neg]
+
+
 def conv2d_generic_general_acc(input, weight, bit_length, lfsr_length, z_units, padding, stride, prog_load,
                                bin_config, gen_config, xnor, mux) -> torch.Tensor:
     """SC conv2d forward, returns pos - neg as int16 (sc_cuda.cpp:73-85)."""

@@ -419,3 +419,23 @@ def test_randomised_tensor_kernel_vs_direct(ops):
         assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), what
         ran += 1
     assert ran >= 30
+
+
+@pytest.mark.parametrize("kernel", ["auto", "tiled", "direct"])
+def test_prepared_conv_reuses_weight_streams(ops, kernel):
+    """ops.PreparedConv expands the weights once; every call equals the one-shot op on the same tensors."""
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(64, 64, 3, 3, generator=g) * 0.1).clamp(-1, 1).cuda().contiguous(memory_format=torch.channels_last)
+    xs = [torch.rand(5, 64, 12, 12, generator=g).cuda().contiguous(memory_format=torch.channels_last) for _ in range(3)]
+    args = (32, -1, (1, 1), (2, 2), PROG, 1, 1, True)
+    ops.set_conv_kernel(kernel)
+    try:
+        conv = ops.PreparedConv(w, xs[0].shape, xs[0].dtype, True, *args)
+        for x in xs:
+            pos, neg = conv(x)
+            rpos, rneg = ops.conv2d_generic_general_split_acc(x, w, 32, -1, 16, (1, 1), (2, 2), PROG, 1, 1, True, False)
+            assert torch.equal(pos, rpos) and torch.equal(neg, rneg)
+        with pytest.raises(ValueError):
+            conv(xs[0][:, :, :11])   # another shape needs another object
+    finally:
+        ops.set_conv_kernel("auto")
