@@ -197,6 +197,37 @@ int rexsc_orn_bias_std_bwd(const float *d_grad_out, const void *d_in, int32_t in
                            float *d_grad_in, int64_t n_elem, int32_t or_n, void *stream);
 
 /*
+ * Caller arithmetic on the SC conv's int16 counts, one pass instead of five.  Replaces, in the caller of
+ * conv2d_generic_general_split_acc, `result_pos.to(dtype)`, `result_neg.to(dtype)` (utils_functional.py:1181-1182),
+ * `result_pos / bit_length`, `result_neg / bit_length` (:1273-1274) and `result_pos_value - result_neg_value`
+ * (:1324).  out_dtype REXSC_F32 or REXSC_F16 (the dtype under autocast); bit_length must be a power of two, which
+ * makes every scaling exact, so the outputs equal the eager sequence bit for bit (fp16 rounds counts above 2048 and
+ * the difference, as eager does).  Any of the three outputs may be null, not all:
+ *   val_pos[i] = dtype(pos[i]) / L     val_neg[i] = dtype(neg[i]) / L     val_diff[i] = val_pos[i] - val_neg[i]
+ */
+int rexsc_sc_counts_to_value(const int16_t *d_pos, const int16_t *d_neg, int32_t bit_length, int32_t out_dtype,
+                             void *d_val_pos, void *d_val_neg, void *d_val_diff, int64_t n_elem, void *stream);
+
+/*
+ * Calibration statistics on the device.  Replaces the 30 masked mean / std passes of compute_bias_std_coef
+ * (utils_functional.py:901-925) over a_bit = cat(pos, neg) / L and a_act = cat(guide_pos, guide_neg): for each of the
+ * 30 windows [e_i, e_i + 0.1) of the guide value, e = numpy.linspace(0, max(a_bit), 30) rounded to fp32 as the
+ * tensor comparison does, the number of elements, the sum of err = a_bit - a_act (fp32) and the sum of err^2.
+ * The least-squares fit of the two 5th-order polynomials stays with the caller.  Three launches (clear, maximum,
+ * windows), no host synchronisation, d_stats is the only memory written:
+ *   double sums[30][3]  {count, sum err, sum err^2} per window     (offset 0)
+ *   int32  max_count    largest count of either sign               (offset 720)
+ *   int32  reserved
+ * d_stats: REXSC_CALIB_STATS_BYTES of device memory, 8-byte aligned.  guide_dtype REXSC_F32 or REXSC_F16.
+ * counts_via_half != 0 rounds each count to fp16 first, as `.to(float16)` under autocast does (exact up to 2048).
+ */
+#define REXSC_CALIB_BINS 30
+#define REXSC_CALIB_STATS_BYTES (REXSC_CALIB_BINS * 3 * 8 + 8)
+int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos, const void *d_guide_neg,
+                         int32_t guide_dtype, int32_t bit_length, int32_t counts_via_half, int64_t n_elem,
+                         void *d_stats, void *stream);
+
+/*
  * FXP fixed-point conv with saturating accumulation.  Replaces conv2d_saturate_acc
  * (torch_c/sc-extension/fixed_cuda.cpp:24-34) and conv2d_saturate_cuda / compute_saturate_general
  * (fixed_cuda_kernel.cu:82-347).  Pad + quantise (round-half-even) + saturating accumulate.

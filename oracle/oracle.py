@@ -190,5 +190,55 @@ def bias_std_backward(grad: torch.Tensor, s: torch.Tensor, or_n: int, bias_coef)
     return torch.from_numpy(out)
 
 
+def counts_to_value(pos: torch.Tensor, neg: torch.Tensor, bit_length: int, dtype=torch.float32):
+    """The caller's arithmetic on the int16 counts, step by step as eager PyTorch runs it
+    (utils_functional.py:1181-1182 casts, :1273-1274 divisions, :1324 difference)."""
+    vp = pos.to(dtype=dtype) / bit_length
+    vn = neg.to(dtype=dtype) / bit_length
+    return vp, vn, vp - vn
+
+
+def calib_windows(a_bit: np.ndarray, a_act: np.ndarray):
+    """Window statistics of compute_bias_std_coef (utils_functional.py:901-925) in numpy: for each start of
+    ``linspace(0, max(a_bit), 30)`` the elements with ``start <= a_act < start + 0.1`` (scalar rounded to the
+    tensor's fp32 as torch's comparison does), ``err = a_bit - a_act`` in fp32, its count, mean and unbiased
+    standard deviation (accumulated in float64).  Returns ``(starts, count, mean, std)``; mean / std are NaN
+    where the reference skips the window (fewer than two elements)."""
+    a_bit = np.asarray(a_bit, dtype=np.float32).reshape(-1)
+    a_act = np.asarray(a_act, dtype=np.float32).reshape(-1)
+    starts = np.linspace(0, float(a_bit.max()) if a_bit.size else 0.0, 30)
+    count = np.zeros(30, dtype=np.int64)
+    mean = np.full(30, np.nan)
+    std = np.full(30, np.nan)
+    err_all = (a_bit - a_act).astype(np.float32)
+    for i, start in enumerate(starts):
+        sel = (a_act >= np.float32(start)) & (a_act < np.float32(start + 0.1))
+        err = err_all[sel].astype(np.float64)
+        count[i] = err.size
+        if err.size > 1:
+            mean[i] = err.mean()
+            std[i] = err.std(ddof=1)
+    return starts, count, mean, std
+
+
+def compute_bias_std_coef(or_n: int, a_bit: torch.Tensor, a_act: torch.Tensor, order: int = 5):
+    """compute_bias_std_coef (utils_functional.py:901-950) on top of calib_windows: polynomial least-squares fits
+    of the per-window bias and standard deviation over the window starts; the bias fit is skipped (zeros) when
+    ``order >= valid_windows // 5``."""
+    if or_n < 0:
+        return torch.zeros(order + 1), torch.zeros(order + 1)
+    starts, count, mean, std = calib_windows(a_bit.float().numpy(), a_act.float().numpy())
+    valid = count > 1
+    basis = torch.from_numpy(np.stack([starts[valid] ** i for i in range(order + 1)], axis=1)).float()
+    bias_bins = torch.from_numpy(mean[valid]).float()
+    std_bins = torch.from_numpy(std[valid]).float()
+    if order >= int(valid.sum()) // 5:
+        bias_coef = torch.zeros(order + 1)
+    else:
+        bias_coef = torch.linalg.lstsq(basis, bias_bins)[0]
+    std_coef = torch.linalg.lstsq(basis, std_bins)[0]
+    return bias_coef, std_coef
+
+
 def num_threads() -> int:
     return lib().rexo_num_threads()

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "librexsc_b200.so")
 SOURCES = ["capi.cu", "sc_stream.cu", "sc_conv_direct.cu", "sc_conv_tiled.cu", "pointwise.cu", "fxp_conv.cu",
-           "sc_conv_static.cu", "fxp_conv_umma.cu", "sc_conv_tc.cu"]
+           "sc_conv_static.cu", "fxp_conv_umma.cu", "sc_conv_tc.cu", "caller_fused.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -1,0 +1,331 @@
+// Arithmetic the front end runs on the SC conv's int16 counts right after the op, as single HBM-streaming passes:
+//
+//   counts -> values   result.to(dtype) / bit_length for both signs and their difference
+//                      (utils_functional.py:1181-1182, 1273-1274, 1316-1324: two casts, two divisions and a
+//                      subtraction, five full-tensor passes in eager PyTorch)
+//   calibration bins   count, sum and sum of squares of err = counts / L - guide over the 30 overlapping windows
+//                      [e_i, e_i + 0.1) of the guide value, e = linspace(0, max(counts) / L, 30)
+//                      (compute_bias_std_coef, utils_functional.py:901-925: 30 masked gathers, each followed by a
+//                      mean and a std reduction and a host synchronisation)
+//
+// Both are bound by HBM: 4 B of counts in and 4-12 B of values out per element for the first, 4 B of counts
+// (twice: once for the maximum, once for the bins) and the guide values for the second.
+#include "common.cuh"
+
+namespace rexsc {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kBins = 30;           // np.linspace(0, max, 30) in the reference
+constexpr int kStatWarps = 4;       // warps per CTA of the bin kernel (each owns a private table)
+constexpr long long kGridCap = 148LL * 8 * 2;
+
+__device__ __forceinline__ void unpack8(const uint4 &v, int (&c)[8])
+{
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        c[2 * k] = (int)(int16_t)(w[k] & 0xffffu);
+        c[2 * k + 1] = (int)(int16_t)(w[k] >> 16);
+    }
+}
+
+// count -> float exactly as `.to(dtype)` gives it: fp16 rounds counts above 2048 to even, fp32 is exact
+template <bool HALF> __device__ __forceinline__ float count_as(int c)
+{
+    return HALF ? __half2float(__int2half_rn(c)) : (float)c;
+}
+
+template <typename OUT> __device__ __forceinline__ void store8(OUT *p, long long i, const float (&v)[8]);
+template <> __device__ __forceinline__ void store8<float>(float *p, long long i, const float (&v)[8])
+{
+    __stcs(reinterpret_cast<float4 *>(p + i), make_float4(v[0], v[1], v[2], v[3]));
+    __stcs(reinterpret_cast<float4 *>(p + i) + 1, make_float4(v[4], v[5], v[6], v[7]));
+}
+template <> __device__ __forceinline__ void store8<__half>(__half *p, long long i, const float (&v)[8])
+{
+    uint4 t;
+    *reinterpret_cast<__half2 *>(&t.x) = __floats2half2_rn(v[0], v[1]);
+    *reinterpret_cast<__half2 *>(&t.y) = __floats2half2_rn(v[2], v[3]);
+    *reinterpret_cast<__half2 *>(&t.z) = __floats2half2_rn(v[4], v[5]);
+    *reinterpret_cast<__half2 *>(&t.w) = __floats2half2_rn(v[6], v[7]);
+    __stcs(reinterpret_cast<uint4 *>(p + i), t);
+}
+template <typename OUT> __device__ __forceinline__ OUT to_out(float v);
+template <> __device__ __forceinline__ float to_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half to_out<__half>(float v) { return __float2half_rn(v); }
+template <typename OUT> __device__ __forceinline__ float round_out(float v);
+template <> __device__ __forceinline__ float round_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_out<__half>(float v) { return __half2float(__float2half_rn(v)); }
+
+// ---- counts -> values --------------------------------------------------------------------------------------
+// Eight elements per thread per iteration: one 128-bit load per sign, 128-bit stores.  `inv_l` is a power of two,
+// so every product is exact and the only roundings are the ones the eager sequence has (count -> fp16 above 2048,
+// the fp16 difference).
+template <typename OUT>
+__global__ void __launch_bounds__(kThreads)
+counts_to_value_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ neg, OUT *__restrict__ vpos,
+                       OUT *__restrict__ vneg, OUT *__restrict__ vdiff, long long n, float inv_l, int vec_ok)
+{
+    constexpr bool HALF = sizeof(OUT) == 2;
+    const long long n_groups = (n + 7) >> 3;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        const long long i = g << 3;
+        const int valid = (int)(n - i < 8 ? n - i : 8);
+        int cp[8], cn[8];
+        if (vec_ok && valid == 8) {
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(pos + i)), cp);
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(neg + i)), cn);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                cp[k] = k < valid ? pos[i + k] : 0;
+                cn[k] = k < valid ? neg[i + k] : 0;
+            }
+        }
+        float a[8], b[8], d[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            a[k] = round_out<OUT>(count_as<HALF>(cp[k]) * inv_l);
+            b[k] = round_out<OUT>(count_as<HALF>(cn[k]) * inv_l);
+            d[k] = a[k] - b[k];
+        }
+        if (vec_ok && valid == 8) {
+            if (vpos) store8<OUT>(vpos, i, a);
+            if (vneg) store8<OUT>(vneg, i, b);
+            if (vdiff) store8<OUT>(vdiff, i, d);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+                if (k < valid) {
+                    if (vpos) vpos[i + k] = to_out<OUT>(a[k]);
+                    if (vneg) vneg[i + k] = to_out<OUT>(b[k]);
+                    if (vdiff) vdiff[i + k] = to_out<OUT>(d[k]);
+                }
+        }
+    }
+}
+
+__device__ __forceinline__ void load8g(const float *p, long long i, float (&v)[8])
+{
+    const float4 a = __ldcs(reinterpret_cast<const float4 *>(p + i));
+    const float4 b = __ldcs(reinterpret_cast<const float4 *>(p + i) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8g(const __half *p, long long i, float (&v)[8])
+{
+    const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p + i));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+    }
+}
+
+// ---- calibration bins ----------------------------------------------------------------------------------------
+// Result block in device memory (REXSC_CALIB_STATS_BYTES):
+//   double sums[30][3]   per window: number of elements, sum of err, sum of err^2
+//   int32  max_count     largest count of either sign
+//   int32  reserved
+struct CalibStats {
+    double sums[kBins][3];
+    int max_count;
+    int reserved;
+};
+static_assert(sizeof(CalibStats) == REXSC_CALIB_STATS_BYTES, "result block size is part of the C ABI");
+
+__global__ void __launch_bounds__(kThreads)
+max_count_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ neg, long long n, int vec_ok,
+                 CalibStats *__restrict__ out)
+{
+    int m = 0;
+    const long long n_groups = (n + 7) >> 3;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        const long long i = g << 3;
+        const int valid = (int)(n - i < 8 ? n - i : 8);
+        if (vec_ok && valid == 8) {
+            int cp[8], cn[8];
+            unpack8(__ldg(reinterpret_cast<const uint4 *>(pos + i)), cp);
+            unpack8(__ldg(reinterpret_cast<const uint4 *>(neg + i)), cn);
+#pragma unroll
+            for (int k = 0; k < 8; k++) m = max(m, max(cp[k], cn[k]));
+        } else {
+            for (int k = 0; k < valid; k++) m = max(m, max((int)pos[i + k], (int)neg[i + k]));
+        }
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0 && m > 0) atomicMax(&out->max_count, m);
+}
+
+// Window edges exactly as the reference's host code makes them: numpy's linspace in float64 (i * (max / 29), the
+// last one set to max), `start + 0.1` in float64, and the comparison against an fp32 tensor with the scalar
+// converted to fp32.
+__device__ __forceinline__ void window_edges(int i, double top, float &lo, float &hi)
+{
+    const double step = top / (double)(kBins - 1);
+    const double e = i == kBins - 1 ? top : __dmul_rn((double)i, step);
+    lo = (float)e;
+    hi = (float)__dadd_rn(e, 0.1);
+}
+
+template <typename G, bool HALF>
+__global__ void __launch_bounds__(kStatWarps * 32)
+calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ neg, const G *__restrict__ gpos,
+                  const G *__restrict__ gneg, long long n, float inv_l, int vec_ok, int gvec_ok,
+                  CalibStats *__restrict__ out)
+{
+    // One private table per warp, one column per lane: tab[warp][bin][which][lane].  A lane only ever touches its
+    // own column (bank = lane), so the read-modify-writes need neither atomics nor conflict resolution.
+    __shared__ float tab[kStatWarps][kBins][3][32];
+    __shared__ float s_lo[kBins], s_hi[kBins];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int k = threadIdx.x; k < kStatWarps * kBins * 3 * 32; k += blockDim.x) (&tab[0][0][0][0])[k] = 0.f;
+    const double top = (double)count_as<HALF>(out->max_count) * (double)inv_l;
+    if (threadIdx.x < kBins) window_edges(threadIdx.x, top, s_lo[threadIdx.x], s_hi[threadIdx.x]);
+    __syncthreads();
+    const float step = (float)(top / (double)(kBins - 1));
+    const float inv_step = step > 0.f ? 1.f / step : 0.f;
+
+    float(*mine)[3][32] = tab[warp];
+    auto add = [&](float x, float abit) {
+        // candidate windows from the approximate position, decided by the exact edges
+        int hi_i = kBins - 1, lo_i = 0;
+        if (step > 0.f) {
+            const float q = x * inv_step;
+            if (!(q > -1.f)) return;              // below every window (or NaN)
+            if (q < (float)(kBins - 1)) hi_i = (int)q + 1;
+            const float ql = (x - 0.1f) * inv_step;
+            if (ql >= (float)(kBins + 1)) return; // above every window
+            if (ql > 1.f) lo_i = (int)ql - 1;
+        }
+        const float err = abit - x;
+        for (int b = lo_i; b <= hi_i; b++)
+            if (x >= s_lo[b] && x < s_hi[b]) {
+                mine[b][0][lane] += 1.f;
+                mine[b][1][lane] += err;
+                mine[b][2][lane] = fmaf(err, err, mine[b][2][lane]);
+            }
+    };
+
+    const long long n_groups = (n + 7) >> 3;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+        const long long i = g << 3;
+        const int valid = (int)(n - i < 8 ? n - i : 8);
+        int cp[8], cn[8];
+        float xp[8], xn[8];
+        if (vec_ok && valid == 8) {
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(pos + i)), cp);
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(neg + i)), cn);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                cp[k] = k < valid ? pos[i + k] : 0;
+                cn[k] = k < valid ? neg[i + k] : 0;
+            }
+        }
+        if (gvec_ok && valid == 8) {
+            load8g(gpos, i, xp);
+            load8g(gneg, i, xn);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                xp[k] = k < valid ? load_as_float<G>(gpos, i + k) : 0.f;
+                xn[k] = k < valid ? load_as_float<G>(gneg, i + k) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            if (k < valid) {
+                add(xp[k], count_as<HALF>(cp[k]) * inv_l);
+                add(xn[k], count_as<HALF>(cn[k]) * inv_l);
+            }
+    }
+    __syncthreads();
+    // fold lanes and warps in double, one atomic per CTA per entry
+    for (int e = threadIdx.x; e < kBins * 3; e += blockDim.x) {
+        double s = 0.0;
+        for (int w = 0; w < kStatWarps; w++)
+            for (int l = 0; l < 32; l++) s += (double)tab[w][e / 3][e % 3][l];
+        if (s != 0.0) atomicAdd(&out->sums[e / 3][e % 3], s);
+    }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+inline unsigned grid_for(long long n, int threads)
+{
+    long long blocks = ((n + 7) / 8 + threads - 1) / threads;
+    if (blocks > kGridCap) blocks = kGridCap;
+    return (unsigned)(blocks < 1 ? 1 : blocks);
+}
+
+} // namespace
+
+} // namespace rexsc
+
+using namespace rexsc;
+
+extern "C" int rexsc_sc_counts_to_value(const int16_t *d_pos, const int16_t *d_neg, int32_t bit_length,
+                                        int32_t out_dtype, void *d_val_pos, void *d_val_neg, void *d_val_diff,
+                                        int64_t n_elem, void *stream)
+{
+    if (n_elem < 0 || (!d_val_pos && !d_val_neg && !d_val_diff)) return REXSC_E_BAD_ARG;
+    if (!pow2(bit_length)) return REXSC_E_UNSUPPORTED; // the scaling is exact only for power-of-two stream lengths
+    if (out_dtype != REXSC_F32 && out_dtype != REXSC_F16) return REXSC_E_UNSUPPORTED;
+    if (n_elem == 0) return REXSC_OK;
+    if (!d_pos || !d_neg) return REXSC_E_BAD_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = aligned16(d_pos) && aligned16(d_neg) && aligned16(d_val_pos) && aligned16(d_val_neg) &&
+                    aligned16(d_val_diff);
+    const float inv_l = 1.f / (float)bit_length;
+    const unsigned grid = grid_for(n_elem, kThreads);
+    if (out_dtype == REXSC_F32)
+        counts_to_value_kernel<float><<<grid, kThreads, 0, st>>>(d_pos, d_neg, (float *)d_val_pos, (float *)d_val_neg,
+                                                                 (float *)d_val_diff, n_elem, inv_l, vec);
+    else
+        counts_to_value_kernel<__half><<<grid, kThreads, 0, st>>>(d_pos, d_neg, (__half *)d_val_pos,
+                                                                  (__half *)d_val_neg, (__half *)d_val_diff, n_elem,
+                                                                  inv_l, vec);
+    REXSC_LAUNCH_CHECK("counts_to_value_kernel");
+    return REXSC_OK;
+}
+
+extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos,
+                                    const void *d_guide_neg, int32_t guide_dtype, int32_t bit_length,
+                                    int32_t counts_via_half, int64_t n_elem, void *d_stats, void *stream)
+{
+    if (n_elem < 0 || !d_stats || (reinterpret_cast<uintptr_t>(d_stats) & 7)) return REXSC_E_BAD_ARG;
+    if (!pow2(bit_length)) return REXSC_E_UNSUPPORTED;
+    if (n_elem > 0 && (!d_pos || !d_neg || !d_guide_pos || !d_guide_neg)) return REXSC_E_BAD_ARG;
+    if (guide_dtype != REXSC_F32 && guide_dtype != REXSC_F16) return REXSC_E_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    CalibStats *out = (CalibStats *)d_stats;
+    REXSC_CUDA_CHECK(cudaMemsetAsync(out, 0, sizeof(CalibStats), st));
+    if (n_elem == 0) return REXSC_OK;
+    const int vec = aligned16(d_pos) && aligned16(d_neg);
+    const int gvec = aligned16(d_guide_pos) && aligned16(d_guide_neg);
+    const float inv_l = 1.f / (float)bit_length;
+    max_count_kernel<<<grid_for(n_elem, kThreads), kThreads, 0, st>>>(d_pos, d_neg, n_elem, vec, out);
+    REXSC_LAUNCH_CHECK("max_count_kernel");
+    const unsigned grid = grid_for(n_elem, kStatWarps * 32);
+#define REXSC_CALIB_LAUNCH(G, H)                                                                                  \
+    calib_bins_kernel<G, H><<<grid, kStatWarps * 32, 0, st>>>(d_pos, d_neg, (const G *)d_guide_pos,               \
+                                                              (const G *)d_guide_neg, n_elem, inv_l, vec, gvec, out)
+    if (guide_dtype == REXSC_F32) {
+        if (counts_via_half) REXSC_CALIB_LAUNCH(float, true);
+        else REXSC_CALIB_LAUNCH(float, false);
+    } else {
+        if (counts_via_half) REXSC_CALIB_LAUNCH(__half, true);
+        else REXSC_CALIB_LAUNCH(__half, false);
+    }
+#undef REXSC_CALIB_LAUNCH
+    REXSC_LAUNCH_CHECK("calib_bins_kernel");
+    return REXSC_OK;
+}

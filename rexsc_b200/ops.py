@@ -440,6 +440,105 @@ def or_approx_n_backward_bias_std_acc(grad_output: torch.Tensor, input: torch.Te
     return out
 
 
+# ---- caller arithmetic on the SC counts (one pass each) ------------------------------------------------------
+def sc_counts_to_value(result_pos: torch.Tensor, result_neg: torch.Tensor, bit_length: int,
+                       dtype: torch.dtype = torch.float32, split: bool = True, diff: bool = False):
+    """``result.to(dtype) / bit_length`` for both signs and, with ``diff``, their difference, in one pass over the
+    int16 counts instead of the caller's two casts, two divisions and subtraction
+    (utils_functional.py:1181-1182,1273-1274,1324).  Bit-identical to that eager sequence.  Returns
+    ``(val_pos, val_neg)``, ``val_diff`` or ``(val_pos, val_neg, val_diff)`` with the strides of ``result_pos``."""
+    _require_cuda(result_pos, "sc_counts_to_value")
+    _require_cuda(result_neg, "sc_counts_to_value")
+    if result_pos.dtype != torch.int16 or result_neg.dtype != torch.int16:
+        raise ValueError("sc_counts_to_value: counts must be the int16 tensors the SC conv returns")
+    if result_pos.shape != result_neg.shape:
+        raise ValueError("sc_counts_to_value: pos and neg differ in shape")
+    if dtype not in (torch.float32, torch.float16):
+        raise ValueError("sc_counts_to_value: dtype must be float32 or float16")
+    if not (split or diff):
+        raise ValueError("sc_counts_to_value: nothing to compute")
+    lib = _lib.load()
+    dev = result_pos.device
+    with torch.cuda.device(dev):
+        p = _flat_dense(result_pos)
+        n = _match_layout(result_neg, p)
+        vp = torch.empty_like(p, dtype=dtype) if split else None
+        vn = torch.empty_like(p, dtype=dtype) if split else None
+        vd = torch.empty_like(p, dtype=dtype) if diff else None
+        null = C.c_void_p(0)
+        _lib.check(lib.rexsc_sc_counts_to_value(_ptr(p), _ptr(n), int(bit_length), _DTYPES[dtype],
+                                                _ptr(vp) if split else null, _ptr(vn) if split else null,
+                                                _ptr(vd) if diff else null, p.numel(), _stream(dev)),
+                   "rexsc_sc_counts_to_value")
+    if split and diff:
+        return vp, vn, vd
+    return (vp, vn) if split else vd
+
+
+CALIB_BINS = 30
+
+
+def sc_calib_stats(result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos: torch.Tensor,
+                   value_neg: torch.Tensor, bit_length: int, counts_via_half: bool = False) -> torch.Tensor:
+    """Per-window statistics of ``err = counts / bit_length - value`` for the calibration fit, computed on the
+    device without a host synchronisation (replaces the masked passes of compute_bias_std_coef,
+    utils_functional.py:917-925).  Returns a float64 CUDA tensor ``[31, 3]``: rows 0..29 are
+    ``(count, sum err, sum err^2)`` of the windows ``[e_i, e_i + 0.1)``, ``e = linspace(0, max(counts)/L, 30)``;
+    row 30 holds the largest count in its first 4 bytes (read it with :func:`calib_max_count`)."""
+    for t in (result_pos, result_neg, value_pos, value_neg):
+        _require_cuda(t, "sc_calib_stats")
+    if result_pos.dtype != torch.int16 or result_neg.dtype != torch.int16:
+        raise ValueError("sc_calib_stats: counts must be int16")
+    if not (result_pos.shape == result_neg.shape == value_pos.shape == value_neg.shape):
+        raise ValueError("sc_calib_stats: counts and values differ in shape")
+    lib = _lib.load()
+    dev = result_pos.device
+    with torch.cuda.device(dev):
+        p = _flat_dense(result_pos)
+        n = _match_layout(result_neg, p)
+        gdt = torch.float16 if value_pos.dtype == torch.float16 and value_neg.dtype == torch.float16 else torch.float32
+        gp = _match_layout(value_pos.detach().to(gdt), p)
+        gn = _match_layout(value_neg.detach().to(gdt), p)
+        stats = torch.empty((CALIB_BINS * 3 + 1,), dtype=torch.float64, device=dev)
+        _lib.check(lib.rexsc_sc_calib_stats(_ptr(p), _ptr(n), _ptr(gp), _ptr(gn), _DTYPES[gdt], int(bit_length),
+                                            1 if counts_via_half else 0, p.numel(), _ptr(stats), _stream(dev)),
+                   "rexsc_sc_calib_stats")
+    return stats
+
+
+def compute_bias_std_coef(or_n: int, result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos: torch.Tensor,
+                          value_neg: torch.Tensor, bit_length: int, order: int = 5,
+                          counts_via_half: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Calibration fit with the same result as compute_bias_std_coef (utils_functional.py:901-950) called on
+    ``cat(pos, neg) / bit_length`` and ``cat(value_pos, value_neg)``, taking the int16 counts and the guide values
+    directly.  The window statistics come from one device pass (:func:`sc_calib_stats`) and one 728-byte read-back;
+    windows with fewer than two elements are left out and the two least-squares fits run in torch, as there."""
+    import numpy as np
+    dev = result_pos.device
+    if or_n < 0:
+        return torch.zeros(order + 1, device=dev), torch.zeros(order + 1, device=dev)
+    raw = sc_calib_stats(result_pos, result_neg, value_pos, value_neg, bit_length, counts_via_half).cpu()
+    max_count = int(raw[CALIB_BINS * 3:].view(torch.int32)[0])
+    top = float(torch.tensor(max_count, dtype=torch.float16 if counts_via_half else torch.float32)) / bit_length
+    sums = raw[:CALIB_BINS * 3].view(CALIB_BINS, 3).numpy()
+    output_range = np.linspace(0, top, CALIB_BINS)
+    valid = sums[:, 0] > 1
+    cnt = sums[valid, 0]
+    mean = sums[valid, 1] / cnt
+    var = np.maximum(sums[valid, 2] - cnt * mean * mean, 0.0) / (cnt - 1)
+    bias_bins = torch.tensor(mean, dtype=torch.float32, device=dev)
+    std_bins = torch.tensor(np.sqrt(var), dtype=torch.float32, device=dev)
+    output_range = output_range[valid]
+    basis = torch.from_numpy(np.stack([output_range ** i for i in range(order + 1)], axis=1)).to(dev).float()
+    n_valid = int(valid.sum())
+    if order >= n_valid // 5:
+        bias_coef = torch.zeros(order + 1, device=dev)
+    else:
+        bias_coef = torch.linalg.lstsq(basis, bias_bins)[0]
+    std_coef = torch.linalg.lstsq(basis, std_bins)[0]
+    return bias_coef, std_coef
+
+
 # ---- FXP conv -------------------------------------------------------------------------------------------
 def conv2d_saturate_acc(input: torch.Tensor, weight: torch.Tensor, add_config: int, precision_in: int,
                         precision_out: int, padding: Sequence[int], stride: Sequence[int]) -> torch.Tensor:
