@@ -338,7 +338,34 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     pw_gbs = nbytes_pw * 5 / (e0.elapsed_time(e1) * 1e-3) / 1e9
 
+    # ---- caller arithmetic on the counts of the largest layer (> L2): counts -> fp16 values, calibration windows ----
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    val = [torch.rand(gbig.shape, device=dev, generator=gen).contiguous(memory_format=torch.channels_last) ** 2 * 1.9
+           for _ in range(2)]
+    cnt = [torch.round((v * (1 - 0.04 * v) + 0.05 * torch.randn(v.shape, device=dev, generator=gen).contiguous(
+        memory_format=torch.channels_last)) * BIT_LENGTH).clamp(0, OR_N * BIT_LENGTH).to(torch.int16) for v in val]
+
+    def gbs(fn, nbytes, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return nbytes * reps / (a.elapsed_time(b) * 1e-3) / 1e9
+
+    n_el = gbig.numel()
+    # int16 pos + neg in, fp16 pos / neg values out (what the front end builds under autocast)
+    c2v_gbs = gbs(lambda: ops.sc_counts_to_value(cnt[0], cnt[1], BIT_LENGTH, torch.float16), n_el * (4 + 4))
+    # counts read twice (maximum, then windows) + both fp32 guide tensors once
+    calib_gbs = gbs(lambda: ops.sc_calib_stats(cnt[0], cnt[1], val[0], val[1], BIT_LENGTH), n_el * (4 + 4 + 8))
+    del val, cnt
+
     return {
+        "c2v_gbs": c2v_gbs, "calib_gbs": calib_gbs,
         "ms": ms, "launches": n_launch, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "h2d": h2d, "d2h": d2h,
         "clocks": clocks, "per_kernel": per_kernel, "exp_ms": exp_ms, "exp_bytes": exp_bytes, "lop3_peak": lop3_peak,
         "mma_peak_ops": mma_peak_ops, "pw_gbs": pw_gbs,
@@ -532,6 +559,14 @@ def main():
                 "peak": _hbm_peak(), "frac": r["pw_gbs"] / _hbm_peak(), "peak_source": _hbm_peak_source(),
             },
         }
+        line["roofline_caller_passes"] = [
+            {"bound": "hbm", "kernel": "counts_to_value_kernel<half> (int16 counts -> fp16 values, both signs)",
+             "achieved": r["c2v_gbs"], "unit": "GB/s", "peak": _hbm_peak(), "frac": r["c2v_gbs"] / _hbm_peak(),
+             "peak_source": _hbm_peak_source()},
+            {"bound": "hbm", "kernel": "max_count_kernel + calib_bins_kernel<float> (calibration window statistics)",
+             "achieved": r["calib_gbs"], "unit": "GB/s", "peak": _hbm_peak(), "frac": r["calib_gbs"] / _hbm_peak(),
+             "peak_source": _hbm_peak_source()},
+        ]
         if secondary is not roof_expand:
             line["roofline_expand"] = roof_expand
         if world == 1 and not args.no_cpu_baseline:

@@ -145,14 +145,34 @@ max_count_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ ne
 {
     int m = 0;
     const long long n_groups = (n + 7) >> 3;
+    const long long n_full = n >> 3; // groups that hold eight elements
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+    long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec_ok) {
+        // four groups (eight 128-bit loads) in flight per thread
+        for (; g + 3 * stride < n_full; g += 4 * stride) {
+            uint4 v[8];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                v[2 * u] = __ldcs(reinterpret_cast<const uint4 *>(pos + ((g + u * stride) << 3)));
+                v[2 * u + 1] = __ldcs(reinterpret_cast<const uint4 *>(neg + ((g + u * stride) << 3)));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                // packed signed 16-bit maxima, two counts per instruction
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                uint32_t t = __vmaxs2(__vmaxs2(w[0], w[1]), __vmaxs2(w[2], w[3]));
+                m = max(m, max((int)(int16_t)(t & 0xffffu), (int)(int16_t)(t >> 16)));
+            }
+        }
+    }
+    for (; g < n_groups; g += stride) {
         const long long i = g << 3;
         const int valid = (int)(n - i < 8 ? n - i : 8);
         if (vec_ok && valid == 8) {
             int cp[8], cn[8];
-            unpack8(__ldg(reinterpret_cast<const uint4 *>(pos + i)), cp);
-            unpack8(__ldg(reinterpret_cast<const uint4 *>(neg + i)), cn);
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(pos + i)), cp);
+            unpack8(__ldcs(reinterpret_cast<const uint4 *>(neg + i)), cn);
 #pragma unroll
             for (int k = 0; k < 8; k++) m = max(m, max(cp[k], cn[k]));
         } else {
@@ -174,52 +194,68 @@ __device__ __forceinline__ void window_edges(int i, double top, float &lo, float
     hi = (float)__dadd_rn(e, 0.1);
 }
 
+// The 30 start edges and the 30 end edges cut the axis into 61 cells; an element with `cl` start edges and `ch`
+// end edges at or below its guide value lies in the windows ch <= b < cl and in cell cl + ch.  The kernel adds
+// every element to exactly one cell and turns cells into windows once per CTA at the end.
+constexpr int kCells = 2 * kBins + 1;
+
 template <typename G, bool HALF>
 __global__ void __launch_bounds__(kStatWarps * 32)
 calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ neg, const G *__restrict__ gpos,
                   const G *__restrict__ gneg, long long n, float inv_l, int vec_ok, int gvec_ok,
                   CalibStats *__restrict__ out)
 {
-    // One private table per warp, one column per lane: tab[warp][bin][which][lane].  A lane only ever touches its
+    // One private table per warp, one column per lane: tab[warp][cell][which][lane].  A lane only ever touches its
     // own column (bank = lane), so the read-modify-writes need neither atomics nor conflict resolution.
-    __shared__ float tab[kStatWarps][kBins][3][32];
-    __shared__ float s_lo[kBins], s_hi[kBins];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float(*tab)[kCells][3][32] = reinterpret_cast<float(*)[kCells][3][32]>(smem_raw);
+    // edge tables with one sentinel on each side: e_lo[j + 1] = start of window j, e_lo[0] = -inf, e_lo[31] = NaN
+    __shared__ float e_lo[kBins + 2], e_hi[kBins + 2];
+    __shared__ int cell_cl[kCells], cell_ch[kCells];
+    __shared__ double cell_sum[kCells][3];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int k = threadIdx.x; k < kStatWarps * kBins * 3 * 32; k += blockDim.x) (&tab[0][0][0][0])[k] = 0.f;
+    for (int k = threadIdx.x; k < kStatWarps * kCells * 3 * 32; k += blockDim.x) (&tab[0][0][0][0])[k] = 0.f;
     const double top = (double)count_as<HALF>(out->max_count) * (double)inv_l;
-    if (threadIdx.x < kBins) window_edges(threadIdx.x, top, s_lo[threadIdx.x], s_hi[threadIdx.x]);
+    if (threadIdx.x < kBins) window_edges(threadIdx.x, top, e_lo[threadIdx.x + 1], e_hi[threadIdx.x + 1]);
+    if (threadIdx.x == 0) {
+        e_lo[0] = e_hi[0] = -INFINITY;
+        e_lo[kBins + 1] = e_hi[kBins + 1] = NAN; // NaN <= x is false for every x
+    }
     __syncthreads();
-    const float step = (float)(top / (double)(kBins - 1));
-    const float inv_step = step > 0.f ? 1.f / step : 0.f;
-
-    float(*mine)[3][32] = tab[warp];
-    auto add = [&](float x, float abit) {
-        // candidate windows from the approximate position, decided by the exact edges
-        int hi_i = kBins - 1, lo_i = 0;
-        if (step > 0.f) {
-            const float q = x * inv_step;
-            if (!(q > -1.f)) return;              // below every window (or NaN)
-            if (q < (float)(kBins - 1)) hi_i = (int)q + 1;
-            const float ql = (x - 0.1f) * inv_step;
-            if (ql >= (float)(kBins + 1)) return; // above every window
-            if (ql > 1.f) lo_i = (int)ql - 1;
+    if (threadIdx.x == 0) {
+        // walk the merged edge list: cell c lies after c edges, i of them starts and j ends
+        int i = 0, j = 0;
+        for (int c = 0; c < kCells; c++) {
+            cell_cl[c] = i;
+            cell_ch[c] = j;
+            if (i < kBins && (j >= kBins || e_lo[i + 1] <= e_hi[j + 1])) i++;
+            else j++;
         }
-        const float err = abit - x;
-        for (int b = lo_i; b <= hi_i; b++)
-            if (x >= s_lo[b] && x < s_hi[b]) {
-                mine[b][0][lane] += 1.f;
-                mine[b][1][lane] += err;
-                mine[b][2][lane] = fmaf(err, err, mine[b][2][lane]);
-            }
+    }
+    const float step = (float)(top / (double)(kBins - 1));
+    const bool flat = !(step > 0.f);             // every count is zero: all windows are [0, 0.1)
+    const float inv_step = flat ? 0.f : 1.f / step;
+    const float lo0 = e_lo[1], hi0 = e_hi[1];
+
+    // number of edges of a sentinel-padded table that are <= x, from an estimate that is off by at most one
+    auto edges_below = [&](const float *tbl, float q, float x) -> int {
+        int cand = q >= (float)(kBins - 1) ? kBins - 1 : (q > 0.f ? (int)q : 0);
+        const int c = cand - 1 + (tbl[cand] <= x) + (tbl[cand + 1] <= x) + (tbl[cand + 2] <= x);
+        return max(c, 0);
+    };
+    auto cell_of = [&](float x) -> int {
+        if (flat) return (x >= lo0 ? kBins : 0) + (x >= hi0 ? kBins : 0);
+        return edges_below(e_lo, x * inv_step, x) + edges_below(e_hi, (x - 0.1f) * inv_step, x);
     };
 
+    float(*mine)[3][32] = tab[warp];
     const long long n_groups = (n + 7) >> 3;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
         const long long i = g << 3;
         const int valid = (int)(n - i < 8 ? n - i : 8);
         int cp[8], cn[8];
-        float xp[8], xn[8];
+        float x[16];
         if (vec_ok && valid == 8) {
             unpack8(__ldcs(reinterpret_cast<const uint4 *>(pos + i)), cp);
             unpack8(__ldcs(reinterpret_cast<const uint4 *>(neg + i)), cn);
@@ -231,31 +267,51 @@ calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ n
             }
         }
         if (gvec_ok && valid == 8) {
-            load8g(gpos, i, xp);
-            load8g(gneg, i, xn);
+            load8g(gpos, i, *reinterpret_cast<float(*)[8]>(&x[0]));
+            load8g(gneg, i, *reinterpret_cast<float(*)[8]>(&x[8]));
         } else {
 #pragma unroll
             for (int k = 0; k < 8; k++) {
-                xp[k] = k < valid ? load_as_float<G>(gpos, i + k) : 0.f;
-                xn[k] = k < valid ? load_as_float<G>(gneg, i + k) : 0.f;
+                // a guide value of NaN lands in cell 0, which belongs to no window
+                x[k] = k < valid ? load_as_float<G>(gpos, i + k) : NAN;
+                x[8 + k] = k < valid ? load_as_float<G>(gneg, i + k) : NAN;
             }
         }
+        int cell[16];
 #pragma unroll
-        for (int k = 0; k < 8; k++)
-            if (k < valid) {
-                add(xp[k], count_as<HALF>(cp[k]) * inv_l);
-                add(xn[k], count_as<HALF>(cn[k]) * inv_l);
-            }
+        for (int k = 0; k < 16; k++) cell[k] = cell_of(x[k]);
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            const float err = count_as<HALF>(k < 8 ? cp[k] : cn[k - 8]) * inv_l - x[k];
+            float *col = &mine[cell[k]][0][lane];
+            col[0] += 1.f;
+            col[32] += err;
+            col[64] = fmaf(err, err, col[64]);
+        }
     }
     __syncthreads();
-    // fold lanes and warps in double, one atomic per CTA per entry
-    for (int e = threadIdx.x; e < kBins * 3; e += blockDim.x) {
+    // cells: every warp folds its share of the 183 entries over the 4 tables and the 32 columns, in double
+    for (int e = warp; e < kCells * 3; e += kStatWarps) {
         double s = 0.0;
-        for (int w = 0; w < kStatWarps; w++)
-            for (int l = 0; l < 32; l++) s += (double)tab[w][e / 3][e % 3][l];
-        if (s != 0.0) atomicAdd(&out->sums[e / 3][e % 3], s);
+#pragma unroll
+        for (int w = 0; w < kStatWarps; w++) s += (double)tab[w][e / 3][e % 3][lane];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (lane == 0) cell_sum[e / 3][e % 3] = s;
+    }
+    __syncthreads();
+    // windows from cells, one atomic per CTA per entry.  Cell 0 (below every window) also collects the NaN
+    // padding of a ragged tail; it is part of no window.
+    for (int e = threadIdx.x; e < kBins * 3; e += blockDim.x) {
+        const int b = e / 3, k = e % 3;
+        double s = 0.0;
+        for (int c = 1; c < kCells; c++)
+            if (cell_ch[c] <= b && b < cell_cl[c]) s += cell_sum[c][k];
+        if (s != 0.0) atomicAdd(&out->sums[b][k], s);
     }
 }
+
+constexpr size_t kStatSmem = (size_t)kStatWarps * kCells * 3 * 32 * sizeof(float);
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
@@ -302,7 +358,8 @@ extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, 
                                     int32_t counts_via_half, int64_t n_elem, void *d_stats, void *stream)
 {
     if (n_elem < 0 || !d_stats || (reinterpret_cast<uintptr_t>(d_stats) & 7)) return REXSC_E_BAD_ARG;
-    if (!pow2(bit_length)) return REXSC_E_UNSUPPORTED;
+    // up to 4096 the fp32 estimate of an element's window is within one of the exact answer (the kernel relies on it)
+    if (!pow2(bit_length) || bit_length > 4096) return REXSC_E_UNSUPPORTED;
     if (n_elem > 0 && (!d_pos || !d_neg || !d_guide_pos || !d_guide_neg)) return REXSC_E_BAD_ARG;
     if (guide_dtype != REXSC_F32 && guide_dtype != REXSC_F16) return REXSC_E_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
@@ -314,10 +371,16 @@ extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, 
     const float inv_l = 1.f / (float)bit_length;
     max_count_kernel<<<grid_for(n_elem, kThreads), kThreads, 0, st>>>(d_pos, d_neg, n_elem, vec, out);
     REXSC_LAUNCH_CHECK("max_count_kernel");
-    const unsigned grid = grid_for(n_elem, kStatWarps * 32);
+    // two CTAs fit an SM (94 KB of tables each): one persistent wave, one fold per CTA
+    unsigned grid = grid_for(n_elem, kStatWarps * 32);
+    if (grid > 148u * 2u) grid = 148u * 2u;
 #define REXSC_CALIB_LAUNCH(G, H)                                                                                  \
-    calib_bins_kernel<G, H><<<grid, kStatWarps * 32, 0, st>>>(d_pos, d_neg, (const G *)d_guide_pos,               \
-                                                              (const G *)d_guide_neg, n_elem, inv_l, vec, gvec, out)
+    do {                                                                                                          \
+        REXSC_CUDA_CHECK(cudaFuncSetAttribute(calib_bins_kernel<G, H>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                              (int)kStatSmem));                                                   \
+        calib_bins_kernel<G, H><<<grid, kStatWarps * 32, kStatSmem, st>>>(                                        \
+            d_pos, d_neg, (const G *)d_guide_pos, (const G *)d_guide_neg, n_elem, inv_l, vec, gvec, out);         \
+    } while (0)
     if (guide_dtype == REXSC_F32) {
         if (counts_via_half) REXSC_CALIB_LAUNCH(float, true);
         else REXSC_CALIB_LAUNCH(float, false);
