@@ -108,24 +108,38 @@ counts_to_value_kernel(const int16_t *__restrict__ pos, const int16_t *__restric
     }
 }
 
-__device__ __forceinline__ void load8g(const float *p, long long i, float (&v)[8])
-{
-    const float4 a = __ldcs(reinterpret_cast<const float4 *>(p + i));
-    const float4 b = __ldcs(reinterpret_cast<const float4 *>(p + i) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8g(const __half *p, long long i, float (&v)[8])
-{
-    const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p + i));
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
-        v[2 * k] = f.x;
-        v[2 * k + 1] = f.y;
+// eight guide values as loaded (registers of a prefetched group) and as floats
+template <typename G> struct Guide8;
+template <> struct Guide8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float *p, long long i)
+    {
+        a = __ldcs(reinterpret_cast<const float4 *>(p + i));
+        b = __ldcs(reinterpret_cast<const float4 *>(p + i) + 1);
     }
-}
+    __device__ __forceinline__ void unpack(float *v) const
+    {
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+};
+template <> struct Guide8<__half> {
+    uint4 t;
+    __device__ __forceinline__ void load(const __half *p, long long i)
+    {
+        t = __ldcs(reinterpret_cast<const uint4 *>(p + i));
+    }
+    __device__ __forceinline__ void unpack(float *v) const
+    {
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+            v[2 * k] = f.x;
+            v[2 * k + 1] = f.y;
+        }
+    }
+};
 
 // ---- calibration bins ----------------------------------------------------------------------------------------
 // Result block in device memory (REXSC_CALIB_STATS_BYTES):
@@ -249,45 +263,98 @@ calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ n
     };
 
     float(*mine)[3][32] = tab[warp];
+    // sixteen elements (eight of each sign) into the warp's table
+    auto accumulate = [&](const int (&cp)[8], const int (&cn)[8], const float (&x)[16]) {
+        int cell[16];
+#pragma unroll
+        for (int k = 0; k < 16; k++) cell[k] = cell_of(x[k]);
+        // Table updates four elements at a time: the four columns are loaded together (one shared-memory round trip
+        // instead of four dependent ones); an element whose cell equals an earlier one of the group continues from
+        // that element's updated values in registers, and the stores go out in order so the last one stands.
+#pragma unroll
+        for (int k0 = 0; k0 < 16; k0 += 4) {
+            float *col[4];
+            float c[4], s1[4], s2[4], err[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int k = k0 + j;
+                err[j] = count_as<HALF>(k < 8 ? cp[k] : cn[k - 8]) * inv_l - x[k];
+                col[j] = &mine[cell[k]][0][lane];
+                c[j] = col[j][0];
+                s1[j] = col[j][32];
+                s2[j] = col[j][64];
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+#pragma unroll
+                for (int i = 0; i < j; i++) {   // later i overrides earlier: it already carries their sums
+                    const bool same = cell[k0 + i] == cell[k0 + j];
+                    c[j] = same ? c[i] : c[j];
+                    s1[j] = same ? s1[i] : s1[j];
+                    s2[j] = same ? s2[i] : s2[j];
+                }
+                c[j] += 1.f;
+                s1[j] += err[j];
+                s2[j] = fmaf(err[j], err[j], s2[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                col[j][0] = c[j];
+                col[j][32] = s1[j];
+                col[j][64] = s2[j];
+            }
+        }
+    };
+
     const long long n_groups = (n + 7) >> 3;
+    const long long n_full = n >> 3;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += stride) {
+    long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec_ok && gvec_ok) {
+        // whole groups through 128-bit loads, the next group's loads in flight while this one is processed (two
+        // warps per scheduler do not hide a DRAM round trip by themselves)
+        uint4 rp, rn;
+        Guide8<G> qp, qn;
+        if (g < n_full) {
+            rp = __ldcs(reinterpret_cast<const uint4 *>(pos + (g << 3)));
+            rn = __ldcs(reinterpret_cast<const uint4 *>(neg + (g << 3)));
+            qp.load(gpos, g << 3);
+            qn.load(gneg, g << 3);
+        }
+        for (; g < n_full; g += stride) {
+            const uint4 cur_p = rp, cur_n = rn;
+            const Guide8<G> cur_qp = qp, cur_qn = qn;
+            const long long nxt = g + stride;
+            if (nxt < n_full) {
+                rp = __ldcs(reinterpret_cast<const uint4 *>(pos + (nxt << 3)));
+                rn = __ldcs(reinterpret_cast<const uint4 *>(neg + (nxt << 3)));
+                qp.load(gpos, nxt << 3);
+                qn.load(gneg, nxt << 3);
+            }
+            int cp[8], cn[8];
+            float x[16];
+            unpack8(cur_p, cp);
+            unpack8(cur_n, cn);
+            cur_qp.unpack(&x[0]);
+            cur_qn.unpack(&x[8]);
+            accumulate(cp, cn, x);
+        }
+    }
+    // unaligned inputs and the ragged last group: element-wise loads
+    for (; g < n_groups; g += stride) {
         const long long i = g << 3;
         const int valid = (int)(n - i < 8 ? n - i : 8);
         int cp[8], cn[8];
         float x[16];
-        if (vec_ok && valid == 8) {
-            unpack8(__ldcs(reinterpret_cast<const uint4 *>(pos + i)), cp);
-            unpack8(__ldcs(reinterpret_cast<const uint4 *>(neg + i)), cn);
-        } else {
 #pragma unroll
-            for (int k = 0; k < 8; k++) {
-                cp[k] = k < valid ? pos[i + k] : 0;
-                cn[k] = k < valid ? neg[i + k] : 0;
-            }
+        for (int k = 0; k < 8; k++) {
+            cp[k] = k < valid ? pos[i + k] : 0;
+            cn[k] = k < valid ? neg[i + k] : 0;
+            // padding gets a guide value of NaN, which lands in cell 0; that cell belongs to no window
+            x[k] = k < valid ? load_as_float<G>(gpos, i + k) : NAN;
+            x[8 + k] = k < valid ? load_as_float<G>(gneg, i + k) : NAN;
         }
-        if (gvec_ok && valid == 8) {
-            load8g(gpos, i, *reinterpret_cast<float(*)[8]>(&x[0]));
-            load8g(gneg, i, *reinterpret_cast<float(*)[8]>(&x[8]));
-        } else {
-#pragma unroll
-            for (int k = 0; k < 8; k++) {
-                // a guide value of NaN lands in cell 0, which belongs to no window
-                x[k] = k < valid ? load_as_float<G>(gpos, i + k) : NAN;
-                x[8 + k] = k < valid ? load_as_float<G>(gneg, i + k) : NAN;
-            }
-        }
-        int cell[16];
-#pragma unroll
-        for (int k = 0; k < 16; k++) cell[k] = cell_of(x[k]);
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const float err = count_as<HALF>(k < 8 ? cp[k] : cn[k - 8]) * inv_l - x[k];
-            float *col = &mine[cell[k]][0][lane];
-            col[0] += 1.f;
-            col[32] += err;
-            col[64] = fmaf(err, err, col[64]);
-        }
+        accumulate(cp, cn, x);
     }
     __syncthreads();
     // cells: every warp folds its share of the 183 entries over the 4 tables and the 32 columns, in double
@@ -369,7 +436,10 @@ extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, 
     const int vec = aligned16(d_pos) && aligned16(d_neg);
     const int gvec = aligned16(d_guide_pos) && aligned16(d_guide_neg);
     const float inv_l = 1.f / (float)bit_length;
-    max_count_kernel<<<grid_for(n_elem, kThreads), kThreads, 0, st>>>(d_pos, d_neg, n_elem, vec, out);
+    // at least four groups per thread where the input allows, so that the unrolled loop of the kernel runs
+    unsigned max_grid = grid_for((n_elem + 3) / 4, kThreads);
+    if (max_grid > 148u * 8u) max_grid = 148u * 8u;
+    max_count_kernel<<<max_grid, kThreads, 0, st>>>(d_pos, d_neg, n_elem, vec, out);
     REXSC_LAUNCH_CHECK("max_count_kernel");
     // two CTAs fit an SM (94 KB of tables each): one persistent wave, one fold per CTA
     unsigned grid = grid_for(n_elem, kStatWarps * 32);
