@@ -226,6 +226,20 @@ int rexsc_sc_counts_to_value(const int16_t *d_pos, const int16_t *d_neg, int32_t
 int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos, const void *d_guide_neg,
                          int32_t guide_dtype, int32_t bit_length, int32_t counts_via_half, int64_t n_elem,
                          void *d_stats, void *stream);
+/*
+ * The two stages of rexsc_sc_calib_stats as separate calls, for callers that calibrate over a batch sharded across
+ * GPUs (the reference calibrates on one GPU's batch, utils_functional.py:1290-1298; no counterpart there):
+ *   max      clears d_stats and writes the largest count of this shard into max_count;
+ *   windows  reads max_count from d_stats and ADDS this shard's window sums to sums[][].
+ * Between the two, a data-parallel caller all-reduces max_count (MAX) so that every rank uses the same windows; after
+ * windows it all-reduces sums (SUM): every rank then fits the same polynomials, those of the global batch.
+ * stats == max followed by windows on the same stream.
+ */
+int rexsc_sc_calib_max(const int16_t *d_pos, const int16_t *d_neg, int32_t bit_length, int64_t n_elem, void *d_stats,
+                       void *stream);
+int rexsc_sc_calib_windows(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos,
+                           const void *d_guide_neg, int32_t guide_dtype, int32_t bit_length, int32_t counts_via_half,
+                           int64_t n_elem, void *d_stats, void *stream);
 
 /*
  * FXP fixed-point conv with saturating accumulation.  Replaces conv2d_saturate_acc

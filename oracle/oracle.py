@@ -198,15 +198,18 @@ def counts_to_value(pos: torch.Tensor, neg: torch.Tensor, bit_length: int, dtype
     return vp, vn, vp - vn
 
 
-def calib_windows(a_bit: np.ndarray, a_act: np.ndarray):
+def calib_windows(a_bit: np.ndarray, a_act: np.ndarray, top=None):
     """Window statistics of compute_bias_std_coef (utils_functional.py:901-925) in numpy: for each start of
     ``linspace(0, max(a_bit), 30)`` the elements with ``start <= a_act < start + 0.1`` (scalar rounded to the
     tensor's fp32 as torch's comparison does), ``err = a_bit - a_act`` in fp32, its count, mean and unbiased
     standard deviation (accumulated in float64).  Returns ``(starts, count, mean, std)``; mean / std are NaN
-    where the reference skips the window (fewer than two elements)."""
+    where the reference skips the window (fewer than two elements).  ``top`` overrides ``max(a_bit)`` (a shard of a
+    batch whose maximum was found over all shards)."""
     a_bit = np.asarray(a_bit, dtype=np.float32).reshape(-1)
     a_act = np.asarray(a_act, dtype=np.float32).reshape(-1)
-    starts = np.linspace(0, float(a_bit.max()) if a_bit.size else 0.0, 30)
+    if top is None:
+        top = float(a_bit.max()) if a_bit.size else 0.0
+    starts = np.linspace(0, top, 30)
     count = np.zeros(30, dtype=np.int64)
     mean = np.full(30, np.nan)
     std = np.full(30, np.nan)
@@ -219,6 +222,21 @@ def calib_windows(a_bit: np.ndarray, a_act: np.ndarray):
             mean[i] = err.mean()
             std[i] = err.std(ddof=1)
     return starts, count, mean, std
+
+
+def calib_window_sums(a_bit: np.ndarray, a_act: np.ndarray, top=None) -> np.ndarray:
+    """``[30, 3]`` float64: element count, sum of err and sum of err^2 per window of calib_windows (the form in which
+    shards of a batch can be added up)."""
+    a_bit = np.asarray(a_bit, dtype=np.float32).reshape(-1)
+    a_act = np.asarray(a_act, dtype=np.float32).reshape(-1)
+    if top is None:
+        top = float(a_bit.max()) if a_bit.size else 0.0
+    out = np.zeros((30, 3))
+    err_all = (a_bit - a_act).astype(np.float32).astype(np.float64)
+    for i, start in enumerate(np.linspace(0, top, 30)):
+        sel = (a_act >= np.float32(start)) & (a_act < np.float32(start + 0.1))
+        out[i] = (sel.sum(), err_all[sel].sum(), (err_all[sel] ** 2).sum())
+    return out
 
 
 def compute_bias_std_coef(or_n: int, a_bit: torch.Tensor, a_act: torch.Tensor, order: int = 5):

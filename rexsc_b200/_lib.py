@@ -57,6 +57,8 @@ SYMBOLS = {
     "rexsc_orn_bias_std_bwd": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _i64, _i32, _vp]),
     "rexsc_sc_counts_to_value": (C.c_int, [_vp, _vp, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "rexsc_sc_calib_stats": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "rexsc_sc_calib_max": (C.c_int, [_vp, _vp, _i32, _i64, _vp, _vp]),
+    "rexsc_sc_calib_windows": (C.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp]),
     "rexsc_fxp_conv2d_workspace_size": (_sz, [C.POINTER(FxpConvDesc)]),
     "rexsc_fxp_conv2d_fwd": (C.c_int, [C.POINTER(FxpConvDesc), _vp, _vp, _vp, _vp, _sz, _vp]),
     "rexsc_alu_probe": (C.c_int, [_i32, _i32, _vp, _vp]),

@@ -420,27 +420,50 @@ extern "C" int rexsc_sc_counts_to_value(const int16_t *d_pos, const int16_t *d_n
     return REXSC_OK;
 }
 
-extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos,
-                                    const void *d_guide_neg, int32_t guide_dtype, int32_t bit_length,
-                                    int32_t counts_via_half, int64_t n_elem, void *d_stats, void *stream)
+static int calib_check(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos, const void *d_guide_neg,
+                       bool need_guides, int32_t guide_dtype, int32_t bit_length, int64_t n_elem, void *d_stats)
 {
     if (n_elem < 0 || !d_stats || (reinterpret_cast<uintptr_t>(d_stats) & 7)) return REXSC_E_BAD_ARG;
     // up to 4096 the fp32 estimate of an element's window is within one of the exact answer (the kernel relies on it)
     if (!pow2(bit_length) || bit_length > 4096) return REXSC_E_UNSUPPORTED;
-    if (n_elem > 0 && (!d_pos || !d_neg || !d_guide_pos || !d_guide_neg)) return REXSC_E_BAD_ARG;
-    if (guide_dtype != REXSC_F32 && guide_dtype != REXSC_F16) return REXSC_E_UNSUPPORTED;
+    if (n_elem > 0 && (!d_pos || !d_neg)) return REXSC_E_BAD_ARG;
+    if (need_guides) {
+        if (n_elem > 0 && (!d_guide_pos || !d_guide_neg)) return REXSC_E_BAD_ARG;
+        if (guide_dtype != REXSC_F32 && guide_dtype != REXSC_F16) return REXSC_E_UNSUPPORTED;
+    }
+    return REXSC_OK;
+}
+
+extern "C" int rexsc_sc_calib_max(const int16_t *d_pos, const int16_t *d_neg, int32_t bit_length, int64_t n_elem,
+                                  void *d_stats, void *stream)
+{
+    const int rc = calib_check(d_pos, d_neg, nullptr, nullptr, false, 0, bit_length, n_elem, d_stats);
+    if (rc != REXSC_OK) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     CalibStats *out = (CalibStats *)d_stats;
     REXSC_CUDA_CHECK(cudaMemsetAsync(out, 0, sizeof(CalibStats), st));
     if (n_elem == 0) return REXSC_OK;
     const int vec = aligned16(d_pos) && aligned16(d_neg);
-    const int gvec = aligned16(d_guide_pos) && aligned16(d_guide_neg);
-    const float inv_l = 1.f / (float)bit_length;
     // at least four groups per thread where the input allows, so that the unrolled loop of the kernel runs
     unsigned max_grid = grid_for((n_elem + 3) / 4, kThreads);
     if (max_grid > 148u * 8u) max_grid = 148u * 8u;
     max_count_kernel<<<max_grid, kThreads, 0, st>>>(d_pos, d_neg, n_elem, vec, out);
     REXSC_LAUNCH_CHECK("max_count_kernel");
+    return REXSC_OK;
+}
+
+extern "C" int rexsc_sc_calib_windows(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos,
+                                      const void *d_guide_neg, int32_t guide_dtype, int32_t bit_length,
+                                      int32_t counts_via_half, int64_t n_elem, void *d_stats, void *stream)
+{
+    const int rc = calib_check(d_pos, d_neg, d_guide_pos, d_guide_neg, true, guide_dtype, bit_length, n_elem, d_stats);
+    if (rc != REXSC_OK) return rc;
+    if (n_elem == 0) return REXSC_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    CalibStats *out = (CalibStats *)d_stats;
+    const int vec = aligned16(d_pos) && aligned16(d_neg);
+    const int gvec = aligned16(d_guide_pos) && aligned16(d_guide_neg);
+    const float inv_l = 1.f / (float)bit_length;
     // two CTAs fit an SM (94 KB of tables each): one persistent wave, one fold per CTA
     unsigned grid = grid_for(n_elem, kStatWarps * 32);
     if (grid > 148u * 2u) grid = 148u * 2u;
@@ -461,4 +484,16 @@ extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, 
 #undef REXSC_CALIB_LAUNCH
     REXSC_LAUNCH_CHECK("calib_bins_kernel");
     return REXSC_OK;
+}
+
+extern "C" int rexsc_sc_calib_stats(const int16_t *d_pos, const int16_t *d_neg, const void *d_guide_pos,
+                                    const void *d_guide_neg, int32_t guide_dtype, int32_t bit_length,
+                                    int32_t counts_via_half, int64_t n_elem, void *d_stats, void *stream)
+{
+    int rc = calib_check(d_pos, d_neg, d_guide_pos, d_guide_neg, true, guide_dtype, bit_length, n_elem, d_stats);
+    if (rc != REXSC_OK) return rc;
+    rc = rexsc_sc_calib_max(d_pos, d_neg, bit_length, n_elem, d_stats, stream);
+    if (rc != REXSC_OK) return rc;
+    return rexsc_sc_calib_windows(d_pos, d_neg, d_guide_pos, d_guide_neg, guide_dtype, bit_length, counts_via_half,
+                                  n_elem, d_stats, stream);
 }

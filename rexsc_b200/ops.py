@@ -478,46 +478,61 @@ def sc_counts_to_value(result_pos: torch.Tensor, result_neg: torch.Tensor, bit_l
 CALIB_BINS = 30
 
 
+def _calib_operands(result_pos, result_neg, value_pos, value_neg, what):
+    for t in (result_pos, result_neg, value_pos, value_neg):
+        _require_cuda(t, what)
+    if result_pos.dtype != torch.int16 or result_neg.dtype != torch.int16:
+        raise ValueError(f"{what}: counts must be int16")
+    if not (result_pos.shape == result_neg.shape == value_pos.shape == value_neg.shape):
+        raise ValueError(f"{what}: counts and values differ in shape")
+    p = _flat_dense(result_pos)
+    n = _match_layout(result_neg, p)
+    gdt = torch.float16 if value_pos.dtype == torch.float16 and value_neg.dtype == torch.float16 else torch.float32
+    gp = _match_layout(value_pos.detach().to(gdt), p)
+    gn = _match_layout(value_neg.detach().to(gdt), p)
+    return p, n, gp, gn, gdt
+
+
 def sc_calib_stats(result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos: torch.Tensor,
-                   value_neg: torch.Tensor, bit_length: int, counts_via_half: bool = False) -> torch.Tensor:
+                   value_neg: torch.Tensor, bit_length: int, counts_via_half: bool = False,
+                   between=None) -> torch.Tensor:
     """Per-window statistics of ``err = counts / bit_length - value`` for the calibration fit, computed on the
     device without a host synchronisation (replaces the masked passes of compute_bias_std_coef,
-    utils_functional.py:917-925).  Returns a float64 CUDA tensor ``[31, 3]``: rows 0..29 are
+    utils_functional.py:917-925).  Returns a float64 CUDA tensor of 91 entries: ``[:90].view(30, 3)`` are
     ``(count, sum err, sum err^2)`` of the windows ``[e_i, e_i + 0.1)``, ``e = linspace(0, max(counts)/L, 30)``;
-    row 30 holds the largest count in its first 4 bytes (read it with :func:`calib_max_count`)."""
-    for t in (result_pos, result_neg, value_pos, value_neg):
-        _require_cuda(t, "sc_calib_stats")
-    if result_pos.dtype != torch.int16 or result_neg.dtype != torch.int16:
-        raise ValueError("sc_calib_stats: counts must be int16")
-    if not (result_pos.shape == result_neg.shape == value_pos.shape == value_neg.shape):
-        raise ValueError("sc_calib_stats: counts and values differ in shape")
+    the first 4 bytes of entry 90 hold the largest count as int32.
+
+    ``between(stats)``, if given, runs after the maximum is known and before the windows are filled: a batch
+    sharded over several GPUs all-reduces the maximum there (``sharding.reduce_calib_max_``) so that all ranks use
+    the same windows."""
+    p, n, gp, gn, gdt = _calib_operands(result_pos, result_neg, value_pos, value_neg, "sc_calib_stats")
     lib = _lib.load()
-    dev = result_pos.device
+    dev = p.device
     with torch.cuda.device(dev):
-        p = _flat_dense(result_pos)
-        n = _match_layout(result_neg, p)
-        gdt = torch.float16 if value_pos.dtype == torch.float16 and value_neg.dtype == torch.float16 else torch.float32
-        gp = _match_layout(value_pos.detach().to(gdt), p)
-        gn = _match_layout(value_neg.detach().to(gdt), p)
         stats = torch.empty((CALIB_BINS * 3 + 1,), dtype=torch.float64, device=dev)
-        _lib.check(lib.rexsc_sc_calib_stats(_ptr(p), _ptr(n), _ptr(gp), _ptr(gn), _DTYPES[gdt], int(bit_length),
-                                            1 if counts_via_half else 0, p.numel(), _ptr(stats), _stream(dev)),
-                   "rexsc_sc_calib_stats")
+        if between is None:
+            _lib.check(lib.rexsc_sc_calib_stats(_ptr(p), _ptr(n), _ptr(gp), _ptr(gn), _DTYPES[gdt], int(bit_length),
+                                                1 if counts_via_half else 0, p.numel(), _ptr(stats), _stream(dev)),
+                       "rexsc_sc_calib_stats")
+        else:
+            _lib.check(lib.rexsc_sc_calib_max(_ptr(p), _ptr(n), int(bit_length), p.numel(), _ptr(stats),
+                                              _stream(dev)), "rexsc_sc_calib_max")
+            between(stats)
+            _lib.check(lib.rexsc_sc_calib_windows(_ptr(p), _ptr(n), _ptr(gp), _ptr(gn), _DTYPES[gdt],
+                                                  int(bit_length), 1 if counts_via_half else 0, p.numel(),
+                                                  _ptr(stats), _stream(dev)), "rexsc_sc_calib_windows")
     return stats
 
 
-def compute_bias_std_coef(or_n: int, result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos: torch.Tensor,
-                          value_neg: torch.Tensor, bit_length: int, order: int = 5,
-                          counts_via_half: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Calibration fit with the same result as compute_bias_std_coef (utils_functional.py:901-950) called on
-    ``cat(pos, neg) / bit_length`` and ``cat(value_pos, value_neg)``, taking the int16 counts and the guide values
-    directly.  The window statistics come from one device pass (:func:`sc_calib_stats`) and one 728-byte read-back;
-    windows with fewer than two elements are left out and the two least-squares fits run in torch, as there."""
+def fit_bias_std_coef(stats: torch.Tensor, bit_length: int, order: int = 5, counts_via_half: bool = False,
+                      device=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The host half of the calibration: window sums (the 91-entry block of :func:`sc_calib_stats`, on any device)
+    -> per-window mean / unbiased std of err -> least-squares polynomials over the window starts, with the rules of
+    compute_bias_std_coef (utils_functional.py:919-950): windows with fewer than two elements are left out, the
+    bias fit is skipped (zeros) when ``order >= valid_windows // 5``.  Needs no GPU."""
     import numpy as np
-    dev = result_pos.device
-    if or_n < 0:
-        return torch.zeros(order + 1, device=dev), torch.zeros(order + 1, device=dev)
-    raw = sc_calib_stats(result_pos, result_neg, value_pos, value_neg, bit_length, counts_via_half).cpu()
+    dev = torch.device(device) if device is not None else stats.device
+    raw = stats.detach().cpu().contiguous()
     max_count = int(raw[CALIB_BINS * 3:].view(torch.int32)[0])
     top = float(torch.tensor(max_count, dtype=torch.float16 if counts_via_half else torch.float32)) / bit_length
     sums = raw[:CALIB_BINS * 3].view(CALIB_BINS, 3).numpy()
@@ -530,13 +545,37 @@ def compute_bias_std_coef(or_n: int, result_pos: torch.Tensor, result_neg: torch
     std_bins = torch.tensor(np.sqrt(var), dtype=torch.float32, device=dev)
     output_range = output_range[valid]
     basis = torch.from_numpy(np.stack([output_range ** i for i in range(order + 1)], axis=1)).to(dev).float()
-    n_valid = int(valid.sum())
-    if order >= n_valid // 5:
+    if order >= int(valid.sum()) // 5:
         bias_coef = torch.zeros(order + 1, device=dev)
     else:
         bias_coef = torch.linalg.lstsq(basis, bias_bins)[0]
     std_coef = torch.linalg.lstsq(basis, std_bins)[0]
     return bias_coef, std_coef
+
+
+def compute_bias_std_coef(or_n: int, result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos: torch.Tensor,
+                          value_neg: torch.Tensor, bit_length: int, order: int = 5,
+                          counts_via_half: bool = False, across_ranks: bool = False
+                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Calibration fit with the same result as compute_bias_std_coef (utils_functional.py:901-950) called on
+    ``cat(pos, neg) / bit_length`` and ``cat(value_pos, value_neg)``, taking the int16 counts and the guide values
+    directly.  The window statistics come from one device pass (:func:`sc_calib_stats`) and one 728-byte read-back;
+    the two least-squares fits run in torch, as there (:func:`fit_bias_std_coef`).
+
+    ``across_ranks=True`` (inside an initialised torch.distributed job) calibrates on the global batch instead of
+    this rank's shard: the maximum count and then the window sums are all-reduced, 728 bytes in all, so every rank
+    fits identical coefficients and the replicas cannot drift apart."""
+    dev = result_pos.device
+    if or_n < 0:
+        return torch.zeros(order + 1, device=dev), torch.zeros(order + 1, device=dev)
+    if across_ranks:
+        from . import sharding
+        stats = sc_calib_stats(result_pos, result_neg, value_pos, value_neg, bit_length, counts_via_half,
+                               between=sharding.reduce_calib_max_)
+        sharding.reduce_calib_sums_(stats)
+    else:
+        stats = sc_calib_stats(result_pos, result_neg, value_pos, value_neg, bit_length, counts_via_half)
+    return fit_bias_std_coef(stats, bit_length, order, counts_via_half, dev)
 
 
 # ---- FXP conv -------------------------------------------------------------------------------------------

@@ -51,3 +51,25 @@ def sync_calibration_(tensors: Iterable[torch.Tensor]) -> None:
     for t in tensors:
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         t.div_(w)
+
+
+CALIB_SUMS = 90  # 30 windows x (count, sum err, sum err^2) in the 91-entry float64 block of ops.sc_calib_stats
+
+
+def reduce_calib_max_(stats: torch.Tensor) -> None:
+    """All-reduce (MAX), in place, the largest count held as int32 in the first 4 bytes of entry 90 of a calibration
+    block.  Called between the two stages of the statistics pass: the windows every rank then fills are those of
+    the global batch.  The only exchange of the calibration path besides :func:`reduce_calib_sums_`."""
+    if _world() == 1:
+        return
+    m = stats[CALIB_SUMS:].view(torch.int32)[:1]
+    dist.all_reduce(m, op=dist.ReduceOp.MAX)
+
+
+def reduce_calib_sums_(stats: torch.Tensor) -> None:
+    """All-reduce (SUM), in place, the 90 window sums of a calibration block.  Valid only if every rank filled the
+    same windows (see :func:`reduce_calib_max_`); afterwards every rank holds the statistics of the global batch and
+    fits identical coefficients."""
+    if _world() == 1:
+        return
+    dist.all_reduce(stats[:CALIB_SUMS], op=dist.ReduceOp.SUM)

@@ -156,3 +156,31 @@ def test_calib_stats_edge_cases(ops, oracle):
     # empty input
     e16, e32 = torch.zeros(0, dtype=torch.int16).cuda(), torch.zeros(0).cuda()
     assert not ops.sc_calib_stats(e16, e16, e32, e32, 32)[:90].any()
+
+
+def test_calib_two_stage_calls_equal_single_call(ops, oracle):
+    """rexsc_sc_calib_max + rexsc_sc_calib_windows == rexsc_sc_calib_stats; a maximum raised between the stages (what
+    an all-reduce over ranks does on a shard that does not hold the global maximum) moves the windows accordingly."""
+    pos, neg, vpos, vneg = _synthetic(50_000, 32, 2, 1.9, 0.05, 3)
+    args = (pos.cuda(), neg.cuda(), vpos.cuda(), vneg.cuda(), 32)
+    one = ops.sc_calib_stats(*args).cpu()
+    seen = []
+    two = ops.sc_calib_stats(*args, between=lambda st: seen.append(int(st[90:].view(torch.int32)[0]))).cpu()
+    assert seen == [int(max(pos.max(), neg.max()))]
+    # sums are folded with double atomics whose order varies from launch to launch: equal to rounding, counts exactly
+    assert torch.equal(one[90:], two[90:]) and torch.equal(one[:90].view(30, 3)[:, 0], two[:90].view(30, 3)[:, 0])
+    assert torch.allclose(one[:90], two[:90], rtol=1e-10, atol=1e-9)
+
+    def raise_max(st):
+        st[90:].view(torch.int32)[0] = 80
+    moved = ops.sc_calib_stats(*args, between=raise_max).cpu()
+    a_bit = np.concatenate([pos.numpy(), neg.numpy()]).astype(np.float32) / 32
+    a_act = np.concatenate([vpos.numpy(), vneg.numpy()])
+    ref = oracle.calib_window_sums(a_bit, a_act, top=80 / 32)
+    got = moved[:90].view(30, 3).numpy()
+    assert np.array_equal(got[:, 0], ref[:, 0])
+    assert np.allclose(got[:, 1:], ref[:, 1:], rtol=1e-5, atol=1e-4)
+    # single-process job: across_ranks is a no-op and gives the same fit
+    b0, s0 = ops.compute_bias_std_coef(2, *args, 5)
+    b1, s1 = ops.compute_bias_std_coef(2, *args, 5, across_ranks=True)
+    assert torch.allclose(b0, b1, rtol=1e-3, atol=1e-5) and torch.allclose(s0, s1, rtol=1e-3, atol=1e-5)
