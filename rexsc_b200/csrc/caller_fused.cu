@@ -251,11 +251,13 @@ calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ n
     const float inv_step = flat ? 0.f : 1.f / step;
     const float lo0 = e_lo[1], hi0 = e_hi[1];
 
-    // number of edges of a sentinel-padded table that are <= x, from an estimate that is off by at most one
+    // Number T of edges of a sentinel-padded table that are <= x.  q estimates x / spacing with an error far below
+    // one (stream lengths up to 4096), so floor(q) is T - 1 give or take one: edges below index floor(q) are <= x
+    // for certain, edges from floor(q) + 2 on are above it, and two exact comparisons decide the rest.  NaN and
+    // negative x give 0.
     auto edges_below = [&](const float *tbl, float q, float x) -> int {
-        int cand = q >= (float)(kBins - 1) ? kBins - 1 : (q > 0.f ? (int)q : 0);
-        const int c = cand - 1 + (tbl[cand] <= x) + (tbl[cand + 1] <= x) + (tbl[cand + 2] <= x);
-        return max(c, 0);
+        const int cand = q >= (float)(kBins - 1) ? kBins - 1 : (q > 0.f ? (int)q : 0);
+        return cand + (tbl[cand + 1] <= x) + (tbl[cand + 2] <= x);
     };
     auto cell_of = [&](float x) -> int {
         if (flat) return (x >= lo0 ? kBins : 0) + (x >= hi0 ? kBins : 0);

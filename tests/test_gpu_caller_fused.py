@@ -184,3 +184,23 @@ def test_calib_two_stage_calls_equal_single_call(ops, oracle):
     b0, s0 = ops.compute_bias_std_coef(2, *args, 5)
     b1, s1 = ops.compute_bias_std_coef(2, *args, 5, across_ranks=True)
     assert torch.allclose(b0, b1, rtol=1e-3, atol=1e-5) and torch.allclose(s0, s1, rtol=1e-3, atol=1e-5)
+
+
+@pytest.mark.parametrize("L,max_count", [(32, 64), (32, 37), (128, 1), (4096, 3), (64, 192)])
+def test_calib_guides_on_and_next_to_window_edges(ops, oracle, L, max_count):
+    """Guide values exactly on every window start and end, and one fp32 step below and above each: membership must
+    follow the exact fp32 comparisons of the reference, whatever the kernel's estimate of the window index says."""
+    top = max_count / L
+    starts = np.linspace(0, top, 30)
+    edges = np.concatenate([starts.astype(np.float32), (starts + 0.1).astype(np.float32)])
+    vals = np.concatenate([edges, np.nextafter(edges, np.float32(-np.inf)), np.nextafter(edges, np.float32(np.inf)),
+                           (edges[:-1] + edges[1:]) / 2]).astype(np.float32)
+    n = vals.size
+    g = torch.Generator().manual_seed(L + max_count)
+    pos = torch.randint(0, max_count + 1, (n,), generator=g, dtype=torch.int32).to(torch.int16)
+    neg = torch.randint(0, max_count + 1, (n,), generator=g, dtype=torch.int32).to(torch.int16)
+    pos[0] = max_count
+    vpos = torch.from_numpy(vals)
+    vneg = torch.from_numpy(vals[::-1].copy())
+    sums, got_max = _windows(ops, pos, neg, vpos, vneg, L)
+    _check_windows(oracle, sums, got_max, pos, neg, vpos, vneg, L, (L, max_count))
