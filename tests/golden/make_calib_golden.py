@@ -1,7 +1,7 @@
 """Generate tests/golden/calib_ref_py.npz by EXECUTING the reference's own compute_bias_std_coef
 (utils_functional.py:901-950) on CPU tensors.
 
-Run in a container that has the reference checkout (its path in REXSC_REFERENCE, default /root/reference):
+Run in a container that has the reference checkout (its path in REXSC_REFERENCE_ROOT, as for oracle/build_ref.py):
     python tests/golden/make_calib_golden.py
 
 The reference module imports its four extension modules at load time; the stand-in modules of
@@ -45,7 +45,7 @@ def main():
     import rexsc_b200
 
     rexsc_b200.install_dropin()
-    sys.path.insert(0, os.environ.get("REXSC_REFERENCE", "/root/reference"))
+    sys.path.insert(0, os.environ.get("REXSC_REFERENCE_ROOT", "/root/reference"))
     import utils_functional as uf
 
     real_lstsq = torch.linalg.lstsq
