@@ -212,6 +212,7 @@ __device__ __forceinline__ void window_edges(int i, double top, float &lo, float
 // end edges at or below its guide value lies in the windows ch <= b < cl and in cell cl + ch.  The kernel adds
 // every element to exactly one cell and turns cells into windows once per CTA at the end.
 constexpr int kCells = 2 * kBins + 1;
+constexpr int kBuckets = 512;
 
 template <typename G, bool HALF>
 __global__ void __launch_bounds__(kStatWarps * 32)
@@ -251,6 +252,35 @@ calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ n
     const float inv_step = flat ? 0.f : 1.f / step;
     const float lo0 = e_lo[1], hi0 = e_hi[1];
 
+    // Bucket table: the axis from 0 to beyond the last window end in buckets half a window spacing wide.  A bucket
+    // stores how many of the 60 edges lie a quarter bucket or more below it (x = base) and the at most two edges
+    // (one start, one end: same-kind edges are a full spacing apart) from there to a quarter bucket above it
+    // (y, z; NaN if absent), so an element's cell is base + (y <= x) + (z <= x): one 128-bit load and two exact
+    // comparisons.  The quarter-bucket overlap absorbs the rounding of the bucket index.  Used when the table fits
+    // (maximum count / L of about 0.02 and more); otherwise the per-table estimates below decide.
+    __shared__ float4 bucket[kBuckets];
+    const float bw = 0.5f * step;
+    const float inv_bw = flat ? 0.f : 1.f / bw;
+    const float n_need = flat ? 0.f : ((float)top + 0.1f) * inv_bw + 3.f;
+    const bool use_buckets = !flat && n_need < (float)kBuckets;
+    const int n_buckets = use_buckets ? (int)n_need : 0;
+    for (int t = threadIdx.x; t < n_buckets; t += blockDim.x) {
+        const float lower = ((float)t - 0.25f) * bw, upper = ((float)t + 1.25f) * bw;
+        int base = 0;
+        float y = NAN, z = NAN;
+        // starts and ends are each ascending, so the first edge of a kind above `lower` is the only candidate of it
+        float cs = NAN, ce = NAN;
+        for (int j = kBins; j >= 1; j--) {
+            if (e_lo[j] <= lower) base++; else cs = e_lo[j];
+            if (e_hi[j] <= lower) base++; else ce = e_hi[j];
+        }
+        if (!(cs <= upper)) cs = NAN;
+        if (!(ce <= upper)) ce = NAN;
+        y = cs; z = ce;
+        bucket[t] = make_float4(__int_as_float(base), y, z, 0.f);
+    }
+    __syncthreads();
+
     // Number T of edges of a sentinel-padded table that are <= x.  q estimates x / spacing with an error far below
     // one (stream lengths up to 4096), so floor(q) is T - 1 give or take one: edges below index floor(q) are <= x
     // for certain, edges from floor(q) + 2 on are above it, and two exact comparisons decide the rest.  NaN and
@@ -261,6 +291,11 @@ calib_bins_kernel(const int16_t *__restrict__ pos, const int16_t *__restrict__ n
     };
     auto cell_of = [&](float x) -> int {
         if (flat) return (x >= lo0 ? kBins : 0) + (x >= hi0 ? kBins : 0);
+        if (use_buckets) {
+            const float q = fminf(fmaxf(x * inv_bw, 0.f), (float)(n_buckets - 1)); // NaN -> bucket 0, cell 0
+            const float4 b = bucket[(int)q];
+            return __float_as_int(b.x) + (b.y <= x) + (b.z <= x);
+        }
         return edges_below(e_lo, x * inv_step, x) + edges_below(e_hi, (x - 0.1f) * inv_step, x);
     };
 

@@ -186,7 +186,7 @@ def test_calib_two_stage_calls_equal_single_call(ops, oracle):
     assert torch.allclose(b0, b1, rtol=1e-3, atol=1e-5) and torch.allclose(s0, s1, rtol=1e-3, atol=1e-5)
 
 
-@pytest.mark.parametrize("L,max_count", [(32, 64), (32, 37), (128, 1), (4096, 3), (64, 192)])
+@pytest.mark.parametrize("L,max_count", [(32, 64), (32, 37), (128, 1), (128, 2), (128, 4), (4096, 3), (64, 192)])
 def test_calib_guides_on_and_next_to_window_edges(ops, oracle, L, max_count):
     """Guide values exactly on every window start and end, and one fp32 step below and above each: membership must
     follow the exact fp32 comparisons of the reference, whatever the kernel's estimate of the window index says."""
