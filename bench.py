@@ -372,6 +372,26 @@ def run_ours(args, rank, world, local_rank):
     }
 
 
+def run_train(args, rank, world, local_rank):
+    """Training-step throughput (the first half of the headline metric): the reference's own models and training loop
+    on the drop-in ops, synthetic ImageNet-shaped batches, per `sync` mode; with several GPUs the weight gradients
+    are all-reduced over NCCL inside the timed region.  Every rank takes part; the numbers are whole-job."""
+    from rexsc_b200 import ops
+
+    ops.release_workspaces()
+    torch.cuda.empty_cache()
+    try:
+        from rexsc_b200 import frontend
+        from rexsc_b200.frontend import train as fe_train
+
+        fe = frontend.load()
+    except ImportError as exc:
+        return {"unavailable": str(exc).splitlines()[0]}
+    ops.manual_seed(0, rank)
+    return fe_train.train_block(args.train_workload, warmup=max(10, args.train_warmup), steps=args.train_steps,
+                                device=torch.device("cuda", local_rank), rank=rank, world=world, fe=fe)
+
+
 # ------------------------------------------------------------------------------------------------------
 def load_reference_cpu():
     """The reference's own CPU extension from oracle/_ref (built by oracle/build_ref.py); None if it cannot run
@@ -470,6 +490,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-train", action="store_true", help="skip the training-step block")
+    ap.add_argument("--train-steps", type=int, default=30)
+    ap.add_argument("--train-warmup", type=int, default=10)
+    ap.add_argument("--train-workload", default="resnet18_or2_L32")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -493,6 +517,9 @@ def main():
     r = run_ours(args, rank, world, local_rank)
     if world > 1:
         torch.distributed.barrier()
+    train = None
+    if not args.no_train:
+        train = run_train(args, rank, world, local_rank)
     if rank == 0:
         imgs = BATCH * world * args.steps
         value = imgs / (r["ms"] * 1e-3)
@@ -569,6 +596,8 @@ def main():
         ]
         if secondary is not roof_expand:
             line["roofline_expand"] = roof_expand
+        if train is not None:
+            line["train"] = train
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_block()
         print(json.dumps(line), flush=True)

@@ -36,3 +36,37 @@ def checksum(a: np.ndarray) -> int:
     a = a.astype(np.int64).reshape(-1)
     idx = (np.arange(a.size, dtype=np.int64) % 65521) + 1
     return int((a * idx).sum())
+
+
+def reference_gpu_modules():
+    """(sc_extension_cuda_ref, fixed_extension_cuda_ref) built by oracle/build_ref.py --gpu, or None."""
+    import build_ref
+
+    try:
+        return build_ref.load_gpu()
+    except Exception:  # built for another torch / CUDA runtime
+        return None
+
+
+class ops_of:
+    """Context manager: inside it the reference's utils_functional calls ``mods`` (e.g. the reference's own GPU
+    extensions) instead of the drop-in modules it imported.  Only the two module-level names of
+    utils_functional.py:18,20 are rebound; nothing of the front end's code changes."""
+
+    def __init__(self, fe, mods):
+        self.uf, self.mods = fe.utils_functional, mods
+
+    def __enter__(self):
+        self.saved = (self.uf.sc_extension_cuda, self.uf.fixed_extension_cuda)
+        self.uf.sc_extension_cuda, self.uf.fixed_extension_cuda = self.mods
+        return self
+
+    def __exit__(self, *exc):
+        self.uf.sc_extension_cuda, self.uf.fixed_extension_cuda = self.saved
+        return False
+
+
+def rel_err(a, b):
+    """max |a - b| / max |b| over two tensors (the relative measure used for gradients)."""
+    a, b = a.detach().double(), b.detach().double()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))

@@ -60,6 +60,39 @@ def test_sc_conv_matches_reference_gpu_kernels(ops, ref_gpu, case, xnor):
     assert torch.equal(p, rp) and torch.equal(n, rn), f"{case} xnor={xnor}"
 
 
+# The layer shapes of the two ImageNet configurations at their full batch: (N, Cin, H, Cout, K, stride, pad, L, or_n).
+# ResNet-18, batch 256, 32-bit streams, OR-2: the six distinct SC conv shapes; ResNet-34, batch 192, 64-bit, OR-3.
+FULL_SIZE_CASES = [
+    (256, 64, 56, 64, 3, 1, 1, 32, 2), (256, 64, 56, 128, 3, 2, 1, 32, 2), (256, 128, 28, 128, 3, 1, 1, 32, 2),
+    (256, 256, 14, 256, 3, 1, 1, 32, 2), (256, 512, 7, 512, 3, 1, 1, 32, 2), (256, 64, 56, 128, 1, 2, 0, 32, 2),
+    (256, 128, 28, 256, 3, 2, 1, 32, 2), (256, 256, 14, 512, 3, 2, 1, 32, 2), (256, 256, 14, 512, 1, 2, 0, 32, 2),
+    (192, 64, 56, 64, 3, 1, 1, 64, 3), (192, 128, 28, 256, 3, 2, 1, 64, 3), (192, 512, 7, 512, 3, 1, 1, 64, 3),
+]
+
+
+@pytest.mark.parametrize("case", FULL_SIZE_CASES)
+def test_sc_conv_full_size_matches_reference_gpu_kernels(ops, ref_gpu, case):
+    """Channels_last, XNOR generator (the front end's setting), full batch: every output count of the persistent
+    tensor-core path (many tiles per CTA, slot-split sums at 7x7) against the reference's kernels, bit for bit."""
+    N, C, H, Co, K, s, p, L, or_n = case
+    g = torch.Generator(device="cuda").manual_seed(sum(case))
+    x = torch.rand(N, C, H + 2 * p, H + 2 * p, device="cuda", generator=g)
+    x = ((x * 128).round() / 128).contiguous(memory_format=torch.channels_last)
+    if p:
+        x[:, :, :p], x[:, :, -p:], x[:, :, :, :p], x[:, :, :, -p:] = 0, 0, 0, 0    # the zero border F.pad leaves
+    w = (torch.randn(Co, C, K, K, device="cuda", generator=g) * 0.1).clamp(-1, 1)
+    w = ((w * 128).round() / 128).contiguous(memory_format=torch.channels_last)
+    args = (L, -1, 16, (0, 0), (s, s), PROG, or_n - 1, 1, True, False)
+    rp, rn = ref_gpu[0].conv2d_generic_general_split_acc(x, w, *args)
+    torch.cuda.synchronize()
+    pos, neg = ops.conv2d_generic_general_split_acc(x, w, *args)
+    assert ops.workspace_status() == 0
+    assert pos.stride() == rp.stride()
+    assert torch.equal(pos, rp) and torch.equal(neg, rn), case
+    del rp, rn, pos, neg, x, w
+    torch.cuda.empty_cache()
+
+
 # The reference's GPU *linear* op is not executed here: its translation unit keeps its own copy of the scratch
 # pointers but shares the "already allocated" flag with the conv unit (sc_device.cuh:711-714, sc_device.cu:3,
 # sc_cuda_matmul.cu:634-644), so calling it after a conv in the same process dereferences unallocated buffers.
