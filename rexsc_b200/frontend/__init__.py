@@ -10,13 +10,17 @@ The front end of nanocad-lab/rex-sc (``utils_functional.py``, ``utils_class.py``
   and data-loading code touches, resolve to the import stand-ins under ``stubs/`` when the real packages are absent;
 * the reference's own modules come from a checkout (``reference_root`` argument or ``REXSC_REFERENCE_ROOT``) or,
   on a machine without a checkout, from the byte-compiled copy that ``python -m rexsc_b200.frontend.build`` writes
-  (``baseline/_ref/frontend/*.pyc``).  TorchScript needs source text, so for the byte-compiled copy
+  (``baseline/_ref/frontend/<module>.pycode``: a code object per module, imported through a small finder because
+  snapshot tools commonly drop ``*.pyc``).  TorchScript needs source text, so for the byte-compiled copy
   ``torch.jit.script`` is switched off while the modules are imported: the 27 small scripted helpers of
   utils_functional.py:286-459 then run as the plain Python functions they decorate (same ATen calls).
 """
 from __future__ import annotations
 
 import importlib
+import importlib.abc
+import importlib.util
+import marshal
 import os
 import sys
 import types
@@ -30,7 +34,37 @@ COMPILED = os.path.join(REPO, "baseline", "_ref", "frontend")
 # modules of the reference that the SC path uses, in import order
 MODULES = ("config", "utils_functional", "utils_class", "network", "utils", "utils_own", "resnet_sc")
 
+COMPILED_EXT = ".pycode"      # py_compile output (16-byte header + marshalled code object) under another extension
+
 _loaded: Optional[types.SimpleNamespace] = None
+
+
+class _CompiledFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    """Imports the reference's top-level modules from their byte-compiled copies under ``COMPILED``."""
+
+    def find_spec(self, name, path=None, target=None):
+        if path is not None or name not in MODULES:
+            return None
+        f = os.path.join(COMPILED, name + COMPILED_EXT)
+        if not os.path.exists(f):
+            return None
+        return importlib.util.spec_from_loader(name, self, origin=f)
+
+    def create_module(self, spec):
+        return None
+
+    def exec_module(self, module):
+        with open(module.__spec__.origin, "rb") as fh:
+            data = fh.read()
+        if data[:4] != importlib.util.MAGIC_NUMBER:
+            raise ImportError(f"{module.__spec__.origin} was compiled by another Python version; rebuild it with "
+                              "`python -m rexsc_b200.frontend.build --force`")
+        module.__file__ = module.__spec__.origin
+        exec(marshal.loads(data[16:]), module.__dict__)
+
+
+def have_compiled() -> bool:
+    return all(os.path.exists(os.path.join(COMPILED, m + COMPILED_EXT)) for m in MODULES)
 
 
 def reference_root(explicit: Optional[str] = None) -> Optional[str]:
@@ -88,12 +122,14 @@ def load(reference_root_dir: Optional[str] = None) -> types.SimpleNamespace:
     root = None if forced else reference_root(reference_root_dir)
     sourceless = False
     if root is None:
-        if not os.path.exists(os.path.join(COMPILED, "utils_functional.pyc")):
+        if not have_compiled():
             raise ImportError(
                 "the reference front end is not available: set REXSC_REFERENCE_ROOT to a checkout of "
                 "nanocad-lab/rex-sc, or run `python -m rexsc_b200.frontend.build` where one is present")
         root, sourceless = COMPILED, True
-    if root not in sys.path:
+        if not any(isinstance(f, _CompiledFinder) for f in sys.meta_path):
+            sys.meta_path.insert(0, _CompiledFinder())
+    elif root not in sys.path:
         sys.path.insert(0, root)
     jit_was_on = bool(torch.jit._state._enabled)
     if sourceless and jit_was_on:

@@ -3,7 +3,8 @@
     python -m rexsc_b200.frontend.build [reference_root] [--force]
 
 Like the reference's C++/CUDA extensions that the test-suite compiles into ``oracle/_ref``, this is a BUILD OUTPUT
-of the unchanged reference sources, compiled from where they lie: one ``<module>.pyc`` per module under
+of the unchanged reference sources, compiled from where they lie: one ``<module>.pycode`` per module (the
+``py_compile`` output under another extension, because snapshot tools commonly drop ``*.pyc``) under
 ``baseline/_ref/frontend/`` (a git-ignored directory; no source text is copied anywhere).  ``frontend.load()``
 imports from there when no checkout is reachable.  Does nothing when the checkout is absent.
 """
@@ -13,7 +14,7 @@ import os
 import py_compile
 import sys
 
-from . import COMPILED, MODULES, reference_root
+from . import COMPILED, COMPILED_EXT, MODULES, reference_root
 
 
 def build(root: str | None = None, force: bool = False) -> bool:
@@ -22,7 +23,7 @@ def build(root: str | None = None, force: bool = False) -> bool:
     os.makedirs(COMPILED, exist_ok=True)
     ok = True
     for name in MODULES:
-        out = os.path.join(COMPILED, name + ".pyc")
+        out = os.path.join(COMPILED, name + COMPILED_EXT)
         if src_root is None:
             ok = ok and os.path.exists(out)
             continue

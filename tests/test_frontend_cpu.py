@@ -18,8 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _have_frontend():
     from rexsc_b200 import frontend
 
-    return frontend.reference_root() is not None or os.path.exists(os.path.join(frontend.COMPILED,
-                                                                                 "utils_functional.pyc"))
+    return frontend.reference_root() is not None or frontend.have_compiled()
 
 
 needs_frontend = pytest.mark.skipif(not _have_frontend(), reason="reference front end not available")
