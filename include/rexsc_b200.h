@@ -7,9 +7,14 @@
  *   - every pointer named d_* is a DEVICE pointer on the current CUDA device;
  *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises;
  *   - functions return REXSC_OK (0) or a negative REXSC_E_* code and never throw;
- *   - no global mutable state, no allocation: scratch is a caller-owned workspace whose size the
- *     matching *_workspace_size() function reports (the reference keeps ~1.3 GiB of process-lifetime
- *     scratch instead: torch_c/sc-extension/sc_cuda_kernel.cu:622-632, sc_device.cuh:711-714);
+ *   - no allocation and no numeric state kept between calls: scratch is a caller-owned workspace whose size
+ *     the matching *_workspace_size() function reports (the reference keeps ~1.3 GiB of process-lifetime
+ *     scratch instead: torch_c/sc-extension/sc_cuda_kernel.cu:622-632, sc_device.cuh:711-714).  The only
+ *     library-owned device memory is the fixed array behind rexsc_sc_conv2d_fwd_static; the only host-side
+ *     state is a per-thread cache of derived launch plans (pure functions of the descriptors) and the text
+ *     of the last CUDA error;
+ *   - int16 outputs of the SC conv must be at least 4-byte aligned (16-byte aligned outputs take the
+ *     vectorised store path); tensors from an allocator always are, offset views may not be;
  *   - each entry point cites the reference interface it replaces (paths inside nanocad-lab/rex-sc).
  */
 #ifndef REXSC_B200_H
@@ -100,14 +105,18 @@ int rexsc_sc_conv2d_fwd(const rexsc_sc_conv_desc *desc, const void *d_act, const
  * device.  Same arguments and bit-identical results as rexsc_sc_conv2d_fwd, with the scratch taken from a
  * fixed 32 MiB array inside the library (rexsc_sc_conv2d_static_scratch_bytes), which every GPU that loads
  * the library holds until the process ends.  Returns REXSC_E_STATIC_SCRATCH, launching nothing, when
- * rexsc_sc_conv2d_workspace_size(desc) is larger than that.  The first call on a device resolves the array's
- * device address: make it before any stream capture starts.  All calls share the array (each call rewrites
+ * rexsc_sc_conv2d_workspace_size(desc) is larger than that.  Every call asks the runtime for the array's device
+ * address (no allocation; still valid after a device reset); the first call on a device may load the library's
+ * module there: make it before any stream capture starts.  All calls share the array (each call rewrites
  * what it reads and clears its status word), so calls that overlap on the GPU race: serialise them.
- * rexsc_workspace_status does not apply; the status word is internal.
+ * rexsc_sc_conv2d_static_status(stream) is the twin of rexsc_workspace_status for this array: it synchronises the
+ * stream and returns REXSC_OK, or REXSC_E_DEVICE_TIMEOUT when a bounded device-side wait of the last call gave up
+ * (its outputs are then incomplete).  It allocates nothing either.
  */
 size_t rexsc_sc_conv2d_static_scratch_bytes(void);
 int rexsc_sc_conv2d_fwd_static(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                                int16_t *d_out_pos, int16_t *d_out_neg, void *stream);
+int rexsc_sc_conv2d_static_status(void *stream);
 
 /*
  * The two stages of rexsc_sc_conv2d_fwd as separate calls (same descriptor, same workspace):

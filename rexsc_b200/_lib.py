@@ -43,6 +43,7 @@ SYMBOLS = {
     "rexsc_sc_conv2d_fwd": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_conv2d_static_scratch_bytes": (_sz, []),
     "rexsc_sc_conv2d_fwd_static": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _vp, _vp]),
+    "rexsc_sc_conv2d_static_status": (C.c_int, [_vp]),
     "rexsc_sc_conv2d_expand": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_conv2d_accumulate": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_linear_workspace_size": (_sz, [_i32] * 6),

@@ -44,6 +44,8 @@ struct ConvPlan {
     int l;         // LFSR length in bits
     int period;    // 2^l - 1
     int nvals;     // 2^l
+    int scale;     // quantisation scale of activations and weights: 2^l when the caller gives the LFSR length,
+                   // else bit_length (sc_cuda.cpp:76-77,90-91; differs from 2^l only for bit_length 2 and 4)
     int slots;     // bit_length * gen_config
     int words;     // ceil(slots / 32)
     int n_or;      // OR-n limit (bin_config + 1)

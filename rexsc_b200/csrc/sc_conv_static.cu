@@ -12,14 +12,13 @@
 //     exits, whether or not this entry point is ever called;
 //   * a call whose scratch need (rexsc_sc_conv2d_workspace_size) exceeds that size is rejected with
 //     REXSC_E_STATIC_SCRATCH and nothing is launched;
-//   * the first call on each device looks the array's device address up (cudaGetSymbolAddress, with that
-//     device current).  Make that first call during set-up, before any stream capture begins;
+//   * every call asks the runtime for the array's address on the current device (cudaGetSymbolAddress: no
+//     allocation, valid again after a device reset).  The FIRST call on a device may load the library's module
+//     there; make that first call during set-up, before any stream capture begins;
 //   * all calls share the one array and it keeps whatever the previous call left in it.  Each call rewrites
 //     every region it later reads (stream tables, activation words, weight words, sign words) and clears the
 //     status word first, so stale contents never reach a result -- but two calls that overlap on the GPU
 //     (different streams, or different host threads without ordering) race on it.  Serialise them.
-#include <mutex>
-
 #include "common.cuh"
 
 #define REXSC_STATIC_SCRATCH_BYTES (32u << 20)
@@ -30,24 +29,15 @@ static __device__ __align__(256) unsigned char g_static_scratch[REXSC_STATIC_SCR
 
 namespace {
 
-constexpr int kMaxDevices = 64;
-void *g_scratch_addr[kMaxDevices] = {nullptr};
-std::mutex g_scratch_mutex;
-
-// Device address of the static scratch on the current device; looked up once per device.
+// Device address of the static scratch on the CURRENT device.  Asked of the runtime on every call instead of being
+// cached: the lookup allocates nothing and costs about a microsecond once the module is loaded, and an address kept
+// across a cudaDeviceReset (or any other re-creation of the context) would be stale.
 int static_scratch_address(void **out)
 {
-    int dev = -1;
-    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) return REXSC_E_UNSUPPORTED;
-    std::lock_guard<std::mutex> lock(g_scratch_mutex);
-    if (g_scratch_addr[dev] == nullptr) {
-        void *ptr = nullptr;
-        REXSC_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
-        if (ptr == nullptr) return REXSC_E_CUDA;
-        g_scratch_addr[dev] = ptr;
-    }
-    *out = g_scratch_addr[dev];
+    void *ptr = nullptr;
+    REXSC_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) return REXSC_E_CUDA;
+    *out = ptr;
     return REXSC_OK;
 }
 
@@ -71,4 +61,15 @@ extern "C" int rexsc_sc_conv2d_fwd_static(const rexsc_sc_conv_desc *desc, const 
     if (rc != REXSC_OK) return rc;
     return rexsc::conv_forward(desc, d_act, d_weight, d_out_pos, d_out_neg, scratch, REXSC_STATIC_SCRATCH_BYTES,
                                (cudaStream_t)stream);
+}
+
+// Device status of the calls made through rexsc_sc_conv2d_fwd_static on the current device: synchronises `stream`
+// and reads the status word at the head of the built-in scratch, exactly as rexsc_workspace_status does for a
+// caller-owned workspace.  Allocates nothing.
+extern "C" int rexsc_sc_conv2d_static_status(void *stream)
+{
+    void *scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != REXSC_OK) return rc;
+    return rexsc_workspace_status(scratch, stream);
 }

@@ -60,6 +60,7 @@ struct TcArgs {
     long long total_o; // candidates = N * Ho * Wo
     int tiles_x;       // candidate tiles = ceil(total_o / kTcM); a CTA walks tiles blockIdx.x, + gridDim.x, ... of the
     int total_tiles;   // tiles_x * (64-channel output chunks) * split; tile index = (part * chunks + chunk) * tiles_x + x
+    int out_vec;       // both output pointers are 16-byte aligned: rows may be stored as 128-bit vectors
     int split;         // 1, or 2: a tile covers half of the time slots and adds its sums into zeroed outputs with
                        // packed 16-bit atomics -- fills the last wave when there are few tiles per SM
     int slots_part;    // slots / split
@@ -181,8 +182,10 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     //   empty[b]  the MMAs that read operand buffer b have completed  (one commit per issuing warp); after the last
     //             chunk of a slot this also says that the slot's counts are complete in their accumulator buffer
     //   tfree[t]  accumulator buffer t has been folded                (one arrival per expanding warp)
-    uint64_t *bar_full = bars, *bar_empty = bars + 2, *bar_tfree = bars + 4;
+    //   drain     every MMA of an issuing warp has completed          (one commit per issuing warp, at its exit)
+    uint64_t *bar_full = bars, *bar_empty = bars + 2, *bar_tfree = bars + 4, *bar_drain = bars + 6;
     if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar_drain)), "r"(kTcM / kTcSub) : "memory");
         for (int b = 0; b < 2; b++) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_full[b])), "r"(kTcWorkers / 32) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(&bar_empty[b])), "r"(kTcM / kTcSub) : "memory");
@@ -191,7 +194,11 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        // two accumulator buffers of 2 row blocks x 128 columns: the whole tensor memory of the SM
+        // two accumulator buffers of 2 row blocks x 128 columns: the whole tensor memory of the SM.  The allocation
+        // blocks until all 512 columns are free, so this kernel assumes it is the only user of tensor memory on its
+        // SM: its > 113 KB of dynamic shared memory keeps a second CTA of itself away, but a kernel of ANOTHER stream
+        // that holds tensor memory (the FXP conv of this library, a vendor GEMM) would make the allocation wait for
+        // that kernel's CTA to finish.  Callers that overlap streams must serialise this kernel with such kernels.
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(tmem_slot)),
                      "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -437,7 +444,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                         unsigned int *row32 = reinterpret_cast<unsigned int *>(row);
 #pragma unroll
                         for (int j = 0; j < 32; j++) atomicAdd(row32 + j, acc[j]);
-                    } else if ((a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
+                    } else if (a.out_vec && (a.Co & 7) == 0 && co0 + kTcCout <= a.Co) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
                             *reinterpret_cast<uint4 *>(row + 2 * j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
@@ -468,6 +475,11 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             issue_mmas(step, s, ck);
             if (++ck == a.CK) { ck = 0; s++; }
         }
+        // Whatever way the loop ended: arrive on the drain barrier once all MMAs this warp has issued are complete,
+        // so that tensor memory is not released under an MMA still in flight after a timed-out wait.
+        asm volatile("{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+                     "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(saddr(bar_drain))
+                     : "memory");
     } else {
         // ---- expanding / folding warps ----
         load_tile(0);
@@ -509,8 +521,12 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0)
+    if (warp == 0) {
+        // bounded like every other wait; in a run without time-outs the MMAs are long complete and this returns at once
+        if (!wait_on(bar_drain, 0) && lane == 0) atomicExch(status, 4);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
 }
 
 // Tensor-pipe issue-rate probe: back-to-back int8 MMAs (M128 x N x K32) on fixed shared-memory operands.
@@ -693,7 +709,9 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     {
         const long long tiles = (long long)a.tiles_x * NC;
         const double whole = (double)((tiles + sms - 1) / sms), halves = (double)((2 * tiles + sms - 1) / sms) / 2.0;
-        const bool rows_ok = d.out_channels_last && (p.Co % kTcCout) == 0;
+        // packed 32-bit atomic adds need 4-byte aligned rows: an int16 view at an odd element offset takes whole tiles
+        const bool aligned4 = ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 3u) == 0;
+        const bool rows_ok = d.out_channels_last && (p.Co % kTcCout) == 0 && aligned4;
         // (measured: tiles of strided layers -- several patch rows per thread, 32-channel steps -- lose more at the extra
         // tile switches than the fuller wave gains)
         const bool long_tiles = g.rows_a <= kTcWorkers && (slots / 2) * g.CK >= 32;
@@ -710,6 +728,8 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
         REXSC_CUDA_CHECK(cudaMemsetAsync(d_neg, 0, out_bytes, st));
     }
     a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
+    if ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 1u) return REXSC_E_BAD_ARG;
+    a.out_vec = ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 15u) == 0 ? 1 : 0;
     {
         const long long cap = p.n_or < p.Kdot ? p.n_or : p.Kdot;
         a.descale_each = (((long long)slots * cap) << kTcScaleLog2) > 65535 ? 1 : 0;

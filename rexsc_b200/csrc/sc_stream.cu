@@ -170,6 +170,8 @@ static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
     if (l < 1 || l > 7) return REXSC_E_UNSUPPORTED;
     p->l = l;
     p->nvals = 1 << l;
+    p->scale = d->lfsr_length > 0 ? (1 << l) : d->bit_length;
+    if (p->scale > p->nvals) return REXSC_E_UNSUPPORTED;
     p->period = p->nvals - 1;
     p->slots = d->bit_length * d->gen_config;
     if (p->slots > 1024) return REXSC_E_TOO_LONG;
@@ -377,7 +379,7 @@ int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void
     a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
     a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
-    a.scale = (float)p.nvals;
+    a.scale = (float)p.scale;
     bool nhwc = d.act_channels_last != 0;
     switch (d.act_dtype) {
     case REXSC_F32: return expand_act_dispatch<float>(a, nhwc, d_act, d_lut, d_A, st);
@@ -524,7 +526,7 @@ int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
     a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
-    a.scale = (float)p.nvals;
+    a.scale = (float)p.scale;
     const int CW = (p.C + 31) / 32;
     const long long items = ((p.NHWp + 31) / 32) * CW;
     const size_t lut_bytes = (size_t)p.period * p.nvals * p.words * sizeof(uint32_t);
@@ -612,7 +614,7 @@ int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const v
     ExpandWArgs a;
     a.C = p.C; a.Co = p.Co; a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.NT = p.NT;
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
-    a.ohwi = d.w_channels_last; a.w_plane_words = p.w_plane_words; a.scale = (float)p.nvals;
+    a.ohwi = d.w_channels_last; a.w_plane_words = p.w_plane_words; a.scale = (float)p.scale;
     long long total_threads = (long long)p.NT * p.CCH * p.KHW * 8 * 32;
     unsigned blocks = (unsigned)((total_threads + 255) / 256);
     switch (d.w_dtype) {
@@ -709,7 +711,7 @@ int launch_expand_weight_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, co
     a.C = p.C; a.Co = p.Co; a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW;
     a.CW = (p.C + 31) / 32; a.NC = (p.Co + 63) / 64;
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
-    a.ohwi = d.w_channels_last; a.scale = (float)p.nvals;
+    a.ohwi = d.w_channels_last; a.scale = (float)p.scale;
     const long long items = (long long)a.NC * 64 * a.KHW * a.CW;
     const long long blocks = (items + 7) / 8;
     if (blocks > 0x7fffffffLL) return REXSC_E_TOO_LONG;

@@ -44,6 +44,7 @@ class Workload:
     generator: str = "lfsr"
     inputs: str = "imagenet"         # imagenet: clip(N(0,1),-3,3) normalised; cifar: U[0,1)
     optimizer: str = "sgd"
+    acc_limit: int = 128             # samples accumulated before an optimizer step (the reference's default)
     extra: Dict = field(default_factory=dict)
 
 
@@ -178,10 +179,10 @@ class Trainer:
         loader = TimedLoader((x, y), warmup, steps, self.device, barrier=barrier)
         self.model.sync = sync
         # calibrate=False: the loop then leaves model.sync alone (it would alternate 2 / 3 by iteration index);
-        # acc_limit=128 as the reference's default, i.e. one optimizer step per iteration at these batch sizes
+        # acc_limit: 128 by default as in the reference, i.e. one optimizer step per iteration at these batch sizes
         self.fe.utils_own.train(loader, self.model, self.criterion, 0, self.optimizer, scaler=self.scaler,
-                                dtype=wl.dtype, scheduler=None, acc_limit=128, channels_last=wl.channels_last,
-                                calibrate=False)
+                                dtype=wl.dtype, scheduler=None, acc_limit=wl.acc_limit,
+                                channels_last=wl.channels_last, calibrate=False)
         if sync == 2:
             self.sync_calibration()
         return {"ms": loader.elapsed_ms, "images": batch * steps, "steps": steps, "batch": batch}

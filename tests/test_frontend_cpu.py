@@ -163,7 +163,7 @@ def _train_worker(rank, world, port, out):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         fe = frontend.load()
-        wl = train.Workload("tiny_or2", "tinyconv", "or_2", [5, 5, 5, 7], 4, 32, 10, "fp32", False, inputs="cifar")
+        wl = train.Workload("tiny_or2", "tinyconv", "or_2", [5, 5, 5, 7], 4, 32, 10, "fp32", False, inputs="cifar", acc_limit=4)
         tr = train.Trainer(fe, wl, "cpu", seed=3, rank=rank, lr=1e-2)
         res = {s: tr.run(s, 1, 2, barrier=True) for s in (3, 2, 1)}
         params = torch.cat([p.detach().reshape(-1) for p in tr.model.parameters()])

@@ -159,6 +159,21 @@ def test_generator_options(ops, oracle):
                 assert_same(ours, ref, f"gen={gen} prog={prog} lfsr={lfsr} {kernel} xnor={xnor}")
 
 
+def test_short_streams_scale_by_the_stream_length(ops, oracle):
+    """bit_length 2 and 4 with a derived LFSR length: the LFSR has 3 bits (sc_cuda_kernel.cu:594-619 falls through)
+    but values are scaled by bit_length itself, not by 2^3 (sc_cuda.cpp:76-77,90-91)."""
+    x, w = conv_inputs(2, 40, 7, 7, 9, 3, seed=21, wscale=0.6)
+    for L in (2, 4):
+        for xnor in (False, True):
+            ref = oracle.conv2d_generic_general_split(x, w, L, -1, 16, (1, 1), (1, 1), PROG, 1, 1, xnor, False)
+            assert L == 2 or int(ref[0].sum()) > 0
+            for kernel in ("direct", "tiled", "tensor"):
+                assert_same(run_ours(ops, x, w, L, 1, 1, 2, xnor, kernel), ref, f"L={L} {kernel} xnor={xnor}")
+        # with the LFSR length given, the scale is 2^lfsr_length instead
+        ref = oracle.conv2d_generic_general_split(x, w, L, 3, 16, (1, 1), (1, 1), PROG, 1, 1, True, False)
+        assert_same(run_ours(ops, x, w, L, 1, 1, 2, True, "auto", lfsr=3), ref, f"L={L} lfsr=3")
+
+
 def test_asymmetric_padding_and_stride(ops, oracle):
     x, w = conv_inputs(2, 8, 9, 11, 6, 3, seed=9)
     ref = oracle.conv2d_generic_general_split(x, w, 32, -1, 16, (2, 1), (2, 1), PROG, 1, 1, True, False)
@@ -439,3 +454,21 @@ def test_prepared_conv_reuses_weight_streams(ops, kernel):
             conv(xs[0][:, :, :11])   # another shape needs another object
     finally:
         ops.set_conv_kernel("auto")
+
+
+def test_device_timeout_status_is_decoded(ops):
+    """A non-zero status word at the head of a workspace (what a bounded device-side wait leaves when it gives up)
+    is reported as REXSC_E_DEVICE_TIMEOUT.  The word is written from the host; no kernel runs."""
+    import ctypes as C
+
+    from rexsc_b200 import _lib
+
+    lib = _lib.load()
+    ws = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.rexsc_workspace_status(C.c_void_p(ws.data_ptr()), st) == 0
+    ws[:4] = torch.tensor([4, 0, 0, 0], dtype=torch.uint8, device="cuda")
+    assert lib.rexsc_workspace_status(C.c_void_p(ws.data_ptr()), st) == -6
+    with pytest.raises(RuntimeError, match="REXSC_E_DEVICE_TIMEOUT"):
+        _lib.check(-6, "status")
+    assert lib.rexsc_workspace_status(None, st) == -1

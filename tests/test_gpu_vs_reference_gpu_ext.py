@@ -39,6 +39,7 @@ CONV_CASES = [
     (2, 64, 10, 10, 64, 3, 1, 1, 64, 3, True),
     (2, 70, 9, 9, 40, 3, 1, 1, 32, 2, False),
     (2, 64, 4, 4, 10, 4, 0, 1, 128, 1, False),
+    (2, 40, 7, 7, 9, 3, 1, 1, 4, 2, False),         # 4-bit streams: 3-bit LFSR, values scaled by 4
 ]
 
 

@@ -1,5 +1,5 @@
 """CPU tests of the oracle: it must reproduce every golden vector produced by the reference's own CPU
-extensions, the survey's known-answer sums, and the algebraic properties of the LFSR generator."""
+extensions, known-answer sums of the first configuration, and the algebraic properties of the LFSR generator."""
 import os
 
 import numpy as np
@@ -93,10 +93,12 @@ def test_stream_density_equals_value(oracle):
             assert int(bo.sum()) == max(value - 1, 0)
 
 
-def test_or_n_definition_against_torch(oracle):
-    """sum_t min(count_t, n) restated with torch.conv2d on explicit bit planes."""
+@pytest.mark.parametrize("L,l", [(32, 5), (4, 3)])
+def test_or_n_definition_against_torch(oracle, L, l):
+    """sum_t min(count_t, n) restated with torch.conv2d on explicit bit planes.  The 4-bit case has a 3-bit LFSR
+    (period 7) while values are scaled by the stream length 4 (sc_cuda.cpp:76-77, sc_cuda_kernel.cu:594-619)."""
     x, w = conv_inputs(2, 6, 7, 7, 5, 3, prec=5, seed=3)
-    L, l, or_n, xnor = 32, 5, 2, True
+    or_n, xnor = 2, True
     xp = torch.nn.functional.pad(x, (1, 1, 1, 1))
     aq = oracle.quantize_act(xp, L)
     wp, wn = oracle.quantize_weight(w, L)
@@ -107,7 +109,7 @@ def test_or_n_definition_against_torch(oracle):
         flat = q.reshape(-1, C * H * W)
         for b in range(flat.shape[0]):
             for i in range(C * H * W):
-                seed = (offset + i) % (L - 1) + 1 - int(xnor)
+                seed = (offset + i) % ((1 << l) - 1) + 1 - int(xnor)
                 out.reshape(L, -1, C * H * W)[:, b, i] = oracle.stream_bits(int(flat[b, i]), seed, l, xnor, L)
         return torch.from_numpy(out)
 

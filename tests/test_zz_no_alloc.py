@@ -47,6 +47,7 @@ def _run_both(lib_mod, lib, case, seed):
     rc = lib.rexsc_sc_conv2d_fwd_static(C.byref(d), vp(x), vp(w), vp(outs[2]), vp(outs[3]), st)
     assert rc == 0, rc
     torch.cuda.synchronize()
+    assert lib.rexsc_sc_conv2d_static_status(st) == 0    # no bounded device wait gave up in the static call
     assert int(outs[0].min()) >= 0                       # the sentinel was overwritten everywhere
     assert torch.equal(outs[2], outs[0]), f"{case}: pos differs from the workspace entry point"
     assert torch.equal(outs[3], outs[1]), f"{case}: neg differs from the workspace entry point"
