@@ -332,19 +332,30 @@ def run_sc(args, wl, rank, world, local_rank):
     din, dout = torch.empty_like(big_in, device=dev), torch.empty_like(big_out, device=dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-    def both_ways():
+    def both_ways(reps=3):
+        """GB/s of each direction, measured on its own stream while the other direction is busy too."""
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        torch.cuda.synchronize()
         with torch.cuda.stream(s_in):
-            din.copy_(big_in, non_blocking=True)
+            ev[0].record(s_in)
+            for _ in range(reps):
+                din.copy_(big_in, non_blocking=True)
+            ev[1].record(s_in)
         with torch.cuda.stream(s_out):
-            big_out.copy_(dout, non_blocking=True)
-        torch.cuda.current_stream(dev).wait_stream(s_in)
-        torch.cuda.current_stream(dev).wait_stream(s_out)
+            ev[2].record(s_out)
+            for _ in range(2 * reps):
+                big_out.copy_(dout, non_blocking=True)
+            ev[3].record(s_out)
+        torch.cuda.synchronize()
+        return (reps * big_in.numel() * 4 / ev[0].elapsed_time(ev[1]) / 1e6,
+                2 * reps * big_out.numel() * 2 / ev[2].elapsed_time(ev[3]) / 1e6)
 
     if world > 1:
         torch.distributed.barrier()
-    t_copy = _event_ms(both_ways, reps=3, warm=1)
-    link = {"h2d_gbs": -sharding.max_over_ranks(-big_in.numel() * 4 / t_copy / 1e6, device=dev),    # slowest rank
-            "d2h_gbs": -sharding.max_over_ranks(-big_out.numel() * 2 / t_copy / 1e6, device=dev)}
+    both_ways(1)
+    h2d_gbs, d2h_gbs = both_ways()
+    link = {"h2d_gbs": -sharding.max_over_ranks(-h2d_gbs, device=dev),    # slowest rank
+            "d2h_gbs": -sharding.max_over_ranks(-d2h_gbs, device=dev)}
     del din, dout
 
     # ---- accumulate kernels timed alone per layer with CUDA events (same stream, after the layer's expand stage) ----

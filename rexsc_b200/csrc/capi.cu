@@ -65,11 +65,18 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
     int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
     if (rc != REXSC_OK) return rc;
     if (allow_partial ? (!d_act && !d_weight) : (!d_act || !d_weight)) return REXSC_E_BAD_ARG;
-    REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
     const int k = resolve_kernel(desc, p);
     if (k < 0) return k;
     // The linear generators always use the XOR LFSR (torch_c/sc-extension/sc_cuda_matmul.cu:27-57).
     const int xnor = desc->linear_seeds ? 0 : (desc->xnor ? 1 : 0);
+    if (k == REXSC_KERNEL_TENSOR && d_act && d_weight) {
+        // one launch for the whole stage (it also clears the status block) where the shape qualifies
+        rc = launch_expand_all_bits(p, *desc, d_act, d_weight, xnor, static_cast<uint32_t *>(b.tc),
+                                    reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p)),
+                                    b.status, st);
+        if (rc != REXSC_E_UNSUPPORTED) return rc;
+    }
+    REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
     rc = launch_build_lut_pair(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
                                desc->prog_load_width, desc->prog_load_wait, b.lut_a, b.lut_w, st);
     if (rc != REXSC_OK) return rc;

@@ -129,6 +129,10 @@ int launch_build_lut_pair(int l, int bit_length, int gen_config, int xnor, int t
 int launch_expand_weight_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_w, const uint32_t *d_lut,
                               uint32_t *d_Wb, cudaStream_t st);
 size_t conv_tc_weight_offset(const ConvPlan &p);
+// stream tables + weight bit planes + activation bit planes + status clear in one launch (sc_stream.cu);
+// REXSC_E_UNSUPPORTED when the shape does not qualify and the separate launches have to be used
+int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const void *d_w, int xnor,
+                           uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, cudaStream_t st);
 int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,
                    int *d_status, cudaStream_t st);
 

@@ -517,6 +517,730 @@ __global__ void __launch_bounds__(256, 3) expand_act_bits_kernel(ExpandActArgs a
     }
 }
 
+// ---- the same expansion for stream tables that fit shared memory twice over (stream lengths up to 64) -------------
+// What the kernel above spends per element -- a byte load, the seed phase with its wrap-around, the table index, a
+// select for zero values, 32-bit loads of single activations -- is cut down here so that the stage runs at memory speed:
+//   * the table is kept in shared memory with its rows repeated once (phase rows 0 .. 2*period-2), so the phase of an
+//     element, (channel part + pixel part), needs no modulo: index = pixel base + channel base + value * words + word,
+//     one three-input add (plus one multiply-add when there is more than one word per stream);
+//   * row `value 0` of the table is all zero (0 > state never holds), so padding, channels beyond C and zero activations
+//     need no special case;
+//   * channels_last inputs are read as 16-byte vectors (4 floats or 8 halves of one pixel per lane) and quantised
+//     without a float-to-int conversion: clamp, add 2^23 rounding towards +inf, keep the low byte;
+//   * the first two steps of the 32 x 32 bit transpose move whole bytes and are single byte-permute instructions;
+//   * CTAs are persistent (the table is loaded once per CTA) and a warp handles all channel words of its 32 pixels, so
+//     the pixel decode (three integer divisions) is paid once per 32 x C elements.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ void transpose32_regs_prmt(uint32_t (&v)[32])
+{
+#pragma unroll
+    for (int k = 0; k < 16; k++) { // distance 16: half-words
+        const uint32_t a = v[k], b = v[k + 16];
+        v[k] = prmt(a, b, 0x5410u);
+        v[k + 16] = prmt(a, b, 0x7632u);
+    }
+#pragma unroll
+    for (int k = 0; k < 32; k++) { // distance 8: bytes
+        if ((k & 8) == 0) {
+            const uint32_t a = v[k], b = v[k + 8];
+            v[k] = prmt(a, b, 0x6240u);
+            v[k + 8] = prmt(a, b, 0x7351u);
+        }
+    }
+#pragma unroll
+    for (int j = 4; j >= 1; j >>= 1) {
+        const uint32_t m = j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
+#pragma unroll
+        for (int k = 0; k < 32; k++) {
+            if ((k & j) == 0) {
+                const uint32_t a = v[k], b = v[k + j];
+                v[k] = (a & m) | ((b << j) & ~m);
+                v[k + j] = ((a >> j) & m) | (b & ~m);
+            }
+        }
+    }
+}
+
+// ceil(clamp(x * scale, 0, scale - 1)) as the low byte of a float: exact, because 0 <= v < 2^23 after the clamp and the
+// addition rounds towards +infinity.  NaN inputs quantise to 0 like the comparison-based clamp of quant_ceil_unipolar.
+__device__ __forceinline__ uint32_t quant_ceil_bits(float x, float scale, float top)
+{
+    const float v = fminf(fmaxf(x * scale, 0.f), top);
+    return __float_as_uint(__fadd_ru(v, 8388608.0f));
+}
+
+template <typename T> struct ActVec;
+template <> struct ActVec<float> {
+    static constexpr int kElems = 4;
+    static __device__ __forceinline__ uint32_t load_quant(const float *p, float scale, float top)
+    {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        const uint32_t lo = prmt(quant_ceil_bits(t.x, scale, top), quant_ceil_bits(t.y, scale, top), 0x0040u);
+        const uint32_t hi = prmt(quant_ceil_bits(t.z, scale, top), quant_ceil_bits(t.w, scale, top), 0x0040u);
+        return prmt(lo, hi, 0x5410u);
+    }
+};
+template <> struct ActVec<__half> {
+    static constexpr int kElems = 8;
+    static __device__ __forceinline__ uint2 load_quant(const __half *p, float scale, float top)
+    {
+        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        uint32_t b[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+            b[k] = prmt(quant_ceil_bits(f.x, scale, top), quant_ceil_bits(f.y, scale, top), 0x0040u);
+        }
+        return make_uint2(prmt(b[0], b[1], 0x5410u), prmt(b[2], b[3], 0x5410u));
+    }
+};
+template <> struct ActVec<__nv_bfloat16> {
+    static constexpr int kElems = 8;
+    static __device__ __forceinline__ uint2 load_quant(const __nv_bfloat16 *p, float scale, float top)
+    {
+        const uint4 t = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        uint32_t b[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            b[k] = prmt(quant_ceil_bits(__uint_as_float(w[k] << 16), scale, top),
+                        quant_ceil_bits(__uint_as_float(w[k] & 0xffff0000u), scale, top), 0x0040u);
+        return make_uint2(prmt(b[0], b[1], 0x5410u), prmt(b[2], b[3], 0x5410u));
+    }
+};
+
+__device__ __forceinline__ void store_bytes(uint32_t *dst, uint32_t v) { dst[0] = v; }
+__device__ __forceinline__ void store_bytes(uint32_t *dst, uint2 v) { dst[0] = v.x; dst[1] = v.y; }
+
+constexpr int kFastWarps = 8;
+// VEC: channels_last input whose pixels' channel runs are 16-byte aligned (C a multiple of the vector width)
+template <typename T, bool NHWC, bool VEC, int WORDS>
+__global__ void __launch_bounds__(kFastWarps * 32, 2)
+expand_act_bits_fast_kernel(ExpandActArgs a, const T *__restrict__ x, const uint32_t *__restrict__ lut_g,
+                            uint32_t *__restrict__ Ab, int CW, long long n_groups)
+{
+    __shared__ __align__(16) uint8_t q_s[kFastWarps][32][44]; // [warp][pixel][channel]; the odd 11-word pitch puts the
+                                                              // 32 lanes' rows into 32 different banks
+    __shared__ long long xb_s[kFastWarps][32];                // [warp][pixel] input offset of the pixel's channel 0
+    __shared__ uint32_t u_s[kFastWarps][32];                  // [warp][channel of the word] channel part of the index
+    extern __shared__ __align__(16) uint32_t lut_s[];         // [2 * period - 1][nvals * words + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t period = (uint32_t)a.period;
+    // one word of padding per row: the bank of an entry then depends on its phase as well, so the many lanes whose
+    // activation is zero (same column of different rows) do not pile up on one bank
+    const uint32_t row_src = (uint32_t)a.nvals * (uint32_t)WORDS, row_words = row_src + 1u;
+    {
+        const int rows = 2 * a.period - 1, all = rows * (int)row_src;
+        for (int i = threadIdx.x; i < all; i += blockDim.x) {
+            const int r = i / (int)row_src, col = i - r * (int)row_src;
+            lut_s[r * (int)row_words + col] = __ldg(lut_g + (r < a.period ? r : r - a.period) * (int)row_src + col);
+        }
+        __syncthreads();
+    }
+    const float top = a.scale - 1.f;
+    const size_t slot_stride = (size_t)CW * a.NHWp;
+    for (long long grp = (long long)blockIdx.x * kFastWarps + warp; grp < n_groups; grp += (long long)gridDim.x * kFastWarps) {
+        // lane = pixel: where it sits in the input
+        const long long P0 = grp * 32, P = P0 + lane;
+        int n = 0, h = 0, w = 0;
+        const bool live = P < a.NHW && decode_pixel(a, P, n, h, w);
+        const int hi = h - a.ph, wi = w - a.pw;
+        const bool inside = live && hi >= 0 && hi < a.H && wi >= 0 && wi < a.W;
+        const uint32_t pix_mod = a.linear_seeds ? 0u : ((uint32_t)h * (uint32_t)a.Wp + (uint32_t)w) % period;
+        const uint32_t pix_base = pix_mod * row_words;
+        const long long xbase = NHWC ? (((long long)n * a.H + hi) * a.W + wi) * a.C
+                                     : (((long long)n * a.C) * a.H + hi) * a.W + wi;
+        const bool store_ok = P < a.NHWp;
+        if (NHWC) xb_s[warp][lane] = inside ? xbase : -1;
+        for (int cw = 0; cw < CW; cw++) {
+            const int c0 = cw * 32;
+            __syncwarp(); // the previous word's tile has been consumed; xb_s is visible
+            // ---- quantise the 32 pixels x 32 channels of this word into the byte tile ----
+            if (NHWC && VEC) {
+                constexpr int E = ActVec<T>::kElems, LPP = 32 / E, PPI = 32 / LPP; // lanes per pixel, pixels per pass
+                const int ch = (lane % LPP) * E, pp = lane / LPP;
+#pragma unroll
+                for (int p0 = 0; p0 < 32; p0 += PPI) {
+                    const long long xb = xb_s[warp][p0 + pp];
+                    uint8_t *dst = &q_s[warp][p0 + pp][ch];
+                    uint32_t *dst32 = reinterpret_cast<uint32_t *>(dst);
+                    if (xb >= 0 && c0 + ch < a.C) {
+                        store_bytes(dst32, ActVec<T>::load_quant(x + xb + c0 + ch, a.scale, top));
+                    } else {
+                        dst32[0] = 0u;
+                        if (E == 8) dst32[1] = 0u;
+                    }
+                }
+            } else if (NHWC) {
+                const int c = c0 + lane;
+                for (int p0 = 0; p0 < 32; p0++) {
+                    const long long xb = xb_s[warp][p0];
+                    const float val = (xb >= 0 && c < a.C) ? load_as_float<T>(x, xb + c) : 0.f;
+                    q_s[warp][p0][lane] = (uint8_t)quant_ceil_bits(val, a.scale, top);
+                }
+            } else {
+                const long long plane = (long long)a.H * a.W;
+                constexpr int kBatch = 16;
+#pragma unroll
+                for (int cc0 = 0; cc0 < 32; cc0 += kBatch) {
+                    float val[kBatch];
+#pragma unroll
+                    for (int i = 0; i < kBatch; i++) {
+                        const int c = c0 + cc0 + i;
+                        val[i] = (inside && c < a.C) ? load_as_float<T>(x, xbase + c * plane) : 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < kBatch; i += 4) {
+                        const uint32_t lo = prmt(quant_ceil_bits(val[i], a.scale, top), quant_ceil_bits(val[i + 1], a.scale, top), 0x0040u);
+                        const uint32_t hi2 = prmt(quant_ceil_bits(val[i + 2], a.scale, top), quant_ceil_bits(val[i + 3], a.scale, top), 0x0040u);
+                        *reinterpret_cast<uint32_t *>(&q_s[warp][lane][cc0 + i]) = prmt(lo, hi2, 0x5410u);
+                    }
+                }
+            }
+            // channel part of the table index for the 32 channels of this word (the same for every pixel)
+            {
+                const uint32_t c = (uint32_t)(c0 + lane);
+                const uint32_t cph = a.linear_seeds ? c % period : (uint32_t)(((unsigned long long)c * a.plane_mod) % period);
+                u_s[warp][lane] = cph * row_words;
+            }
+            __syncwarp();
+            // ---- lane = pixel: look the 32 channels' stream words up, transpose, store 32 slot words ----
+#pragma unroll
+            for (int wd = 0; wd < WORDS; wd++) {
+                uint32_t v[32];
+#pragma unroll
+                for (int c4 = 0; c4 < 32; c4 += 4) {
+                    const uint32_t q4 = *reinterpret_cast<const uint32_t *>(&q_s[warp][lane][c4]);
+                    const uint4 u4 = *reinterpret_cast<const uint4 *>(&u_s[warp][c4]);
+                    const uint32_t uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const uint32_t q = (q4 >> (8 * k)) & 0xffu;
+                        v[c4 + k] = lut_s[pix_base + uu[k] + (uint32_t)wd + q * (uint32_t)WORDS];
+                    }
+                }
+                transpose32_regs_prmt(v);
+                if (store_ok) {
+                    uint32_t *dst = Ab + ((size_t)(wd * 32) * CW + cw) * a.NHWp + P;
+#pragma unroll
+                    for (int t = 0; t < 32; t++) {
+                        __stcs(dst, v[t]);
+                        dst += slot_stride;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+// ---- channels_last inputs with 16-byte aligned channel runs: the raw tile of the NEXT (pixel group, channel word) is
+// fetched with cp.async into a per-warp staging buffer while the current one is quantised, looked up and transposed, so
+// every warp keeps one tile of loads (4 KB of fp32) in flight all the time.  Without that the kernel above is latency-
+// bound: its 16 warps per SM alternate between waiting for their loads and computing (ncu: issue slots 34 % busy,
+// long_scoreboard the only stall that matters, DRAM 17 %).
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src, bool valid)
+{
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0; // 0: the 16 destination bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+template <typename T> struct RawVec;
+template <> struct RawVec<float> {
+    static __device__ __forceinline__ uint32_t quant(const void *p, float scale, float top)
+    {
+        const float4 t = *reinterpret_cast<const float4 *>(p);
+        const uint32_t lo = prmt(quant_ceil_bits(t.x, scale, top), quant_ceil_bits(t.y, scale, top), 0x0040u);
+        const uint32_t hi = prmt(quant_ceil_bits(t.z, scale, top), quant_ceil_bits(t.w, scale, top), 0x0040u);
+        return prmt(lo, hi, 0x5410u);
+    }
+};
+template <> struct RawVec<__half> {
+    static __device__ __forceinline__ uint2 quant(const void *p, float scale, float top)
+    {
+        const uint4 t = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        uint32_t b[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+            b[k] = prmt(quant_ceil_bits(f.x, scale, top), quant_ceil_bits(f.y, scale, top), 0x0040u);
+        }
+        return make_uint2(prmt(b[0], b[1], 0x5410u), prmt(b[2], b[3], 0x5410u));
+    }
+};
+template <> struct RawVec<__nv_bfloat16> {
+    static __device__ __forceinline__ uint2 quant(const void *p, float scale, float top)
+    {
+        const uint4 t = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        uint32_t b[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            b[k] = prmt(quant_ceil_bits(__uint_as_float(w[k] << 16), scale, top),
+                        quant_ceil_bits(__uint_as_float(w[k] & 0xffff0000u), scale, top), 0x0040u);
+        return make_uint2(prmt(b[0], b[1], 0x5410u), prmt(b[2], b[3], 0x5410u));
+    }
+};
+
+// Shared-memory scratch of the pipelined expansion, one set per warp
+struct ActAsyncShared {
+    uint8_t q[kFastWarps][32][44];     // [warp][pixel][channel] quantised values; odd 11-word pitch: 32 rows, 32 banks
+    long long xb[kFastWarps][2][32];   // [warp][group buffer][pixel] input offset of the pixel's channel 0 (-1: padding)
+    uint32_t u[kFastWarps][32];        // [warp][channel of the word] channel part of the table index
+};
+
+// The pipelined expansion of all groups of this CTA.  lut_s: the doubled, padded table, already in shared memory;
+// raw_all: per warp (raw_stride bytes apart) two staging tiles of 32 pixels x 32 channels.
+template <typename T, int WORDS>
+__device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, const T *__restrict__ x,
+                                                      const uint32_t *lut_s, uint8_t *raw_all, int raw_stride,
+                                                      ActAsyncShared &sh, uint32_t *__restrict__ Ab, int CW,
+                                                      long long n_groups)
+{
+    constexpr int E = 16 / (int)sizeof(T), LPP = 32 / E, PPI = 32 / LPP; // elements per lane, lanes per pixel, pixels per pass
+    constexpr int kRowBytes = 32 * (int)sizeof(T), kTileBytes = 32 * kRowBytes;
+    auto &q_s = sh.q;
+    auto &xb_s = sh.xb;
+    auto &u_s = sh.u;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint8_t *raw_s = raw_all + (size_t)warp * raw_stride; // this warp's two staging tiles
+    const uint32_t period = (uint32_t)a.period;
+    const uint32_t row_src = (uint32_t)a.nvals * (uint32_t)WORDS, row_words = row_src + 1u;
+    const float top = a.scale - 1.f;
+    const size_t slot_stride = (size_t)CW * a.NHWp;
+    const long long stride = (long long)gridDim.x * kFastWarps;
+    const int ch = (lane % LPP) * E, pp = lane / LPP;
+
+    struct Pix { long long P; uint32_t pix_base; bool store_ok; };
+    // lane = pixel of group `grp`: input offset of its channel 0 into xb_s[warp][buf], seed phase and store position
+    auto decode = [&](long long grp, int buf) {
+        Pix r;
+        r.P = grp * 32 + lane;
+        int n = 0, h = 0, w = 0;
+        const bool live = r.P < a.NHW && decode_pixel(a, r.P, n, h, w);
+        const int hi = h - a.ph, wi = w - a.pw;
+        const bool inside = live && hi >= 0 && hi < a.H && wi >= 0 && wi < a.W;
+        const uint32_t pix_mod = a.linear_seeds ? 0u : ((uint32_t)h * (uint32_t)a.Wp + (uint32_t)w) % period;
+        r.pix_base = pix_mod * row_words;
+        r.store_ok = r.P < a.NHWp;
+        xb_s[warp][buf][lane] = inside ? (((long long)n * a.H + hi) * a.W + wi) * a.C : -1;
+        return r;
+    };
+    // start the copies of tile (group in xb_s[buf], channel word cw) into staging buffer `stage`
+    auto issue = [&](int buf, int cw, int stage) {
+        uint8_t *dst = raw_s + stage * kTileBytes;
+        const int c = cw * 32 + ch;
+#pragma unroll
+        for (int p0 = 0; p0 < 32; p0 += PPI) {
+            const long long xb = xb_s[warp][buf][p0 + pp];
+            const bool ok = xb >= 0 && c < a.C;
+            cp_async16(dst + (p0 + pp) * kRowBytes + ch * (int)sizeof(T), ok ? (const void *)(x + xb + c) : (const void *)x, ok);
+        }
+        cp_async_commit();
+    };
+
+    long long grp = (long long)blockIdx.x * kFastWarps + warp;
+    if (grp >= n_groups) return; // warp-uniform; no block-wide barrier follows
+    Pix cur = decode(grp, 0), nxt = cur;
+    __syncwarp();
+    issue(0, 0, 0);
+    int buf = 0, stage = 0;
+    for (;;) {
+        const long long grp_next = grp + stride;
+        const bool has_next = grp_next < n_groups;
+        if (has_next) nxt = decode(grp_next, buf ^ 1);
+        __syncwarp();
+        for (int cw = 0; cw < CW; cw++) {
+            // keep the next tile's loads in flight while this one is processed
+            if (cw + 1 < CW) issue(buf, cw + 1, stage ^ 1);
+            else if (has_next) issue(buf ^ 1, 0, stage ^ 1);
+            else cp_async_commit(); // an empty group keeps the wait below uniform
+            cp_async_wait_all_but_one();
+            __syncwarp();
+            // ---- quantise the staged 32 pixels x 32 channels into the byte tile ----
+            {
+                const uint8_t *src = raw_s + stage * kTileBytes;
+#pragma unroll
+                for (int p0 = 0; p0 < 32; p0 += PPI)
+                    store_bytes(reinterpret_cast<uint32_t *>(&q_s[warp][p0 + pp][ch]),
+                                RawVec<T>::quant(src + (p0 + pp) * kRowBytes + ch * (int)sizeof(T), a.scale, top));
+                const uint32_t c = (uint32_t)(cw * 32 + lane);
+                const uint32_t cph = a.linear_seeds ? c % period : (uint32_t)(((unsigned long long)c * a.plane_mod) % period);
+                u_s[warp][lane] = cph * row_words;
+            }
+            __syncwarp();
+            // ---- lane = pixel: look the 32 channels' stream words up, transpose, store 32 slot words ----
+#pragma unroll
+            for (int wd = 0; wd < WORDS; wd++) {
+                uint32_t v[32];
+#pragma unroll
+                for (int c4 = 0; c4 < 32; c4 += 4) {
+                    const uint32_t q4 = *reinterpret_cast<const uint32_t *>(&q_s[warp][lane][c4]);
+                    const uint4 u4 = *reinterpret_cast<const uint4 *>(&u_s[warp][c4]);
+                    const uint32_t uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const uint32_t q = (q4 >> (8 * k)) & 0xffu;
+                        v[c4 + k] = lut_s[cur.pix_base + uu[k] + (uint32_t)wd + q * (uint32_t)WORDS];
+                    }
+                }
+                transpose32_regs_prmt(v);
+                if (cur.store_ok) {
+                    uint32_t *dst = Ab + ((size_t)(wd * 32) * CW + cw) * a.NHWp + cur.P;
+#pragma unroll
+                    for (int t = 0; t < 32; t++) {
+                        __stcs(dst, v[t]);
+                        dst += slot_stride;
+                    }
+                }
+            }
+            __syncwarp(); // the byte tile, the index table and this staging buffer may be rewritten
+            stage ^= 1;
+        }
+        if (!has_next) break;
+        grp = grp_next;
+        cur = nxt;
+        buf ^= 1;
+    }
+}
+
+
+// copy the global table into shared memory: rows repeated once, one word of padding per row
+template <int WORDS>
+__device__ __forceinline__ void load_doubled_table(const ExpandActArgs &a, const uint32_t *__restrict__ lut_g, uint32_t *lut_s)
+{
+    const int row_src = a.nvals * WORDS, row_words = row_src + 1;
+    const int rows = 2 * a.period - 1, all = rows * row_src;
+    for (int i = threadIdx.x; i < all; i += blockDim.x) {
+        const int r = i / row_src, col = i - r * row_src;
+        lut_s[r * row_words + col] = __ldg(lut_g + (r < a.period ? r : r - a.period) * row_src + col);
+    }
+}
+
+template <typename T, int WORDS>
+__global__ void __launch_bounds__(kFastWarps * 32, 2)
+expand_act_bits_async_kernel(ExpandActArgs a, const T *__restrict__ x, const uint32_t *__restrict__ lut_g,
+                             uint32_t *__restrict__ Ab, int CW, long long n_groups, int lut_smem_bytes)
+{
+    __shared__ __align__(16) ActAsyncShared sh;
+    extern __shared__ __align__(16) uint32_t lut_s[]; // [2 * period - 1][nvals * words + 1], then the staging buffers
+    load_doubled_table<WORDS>(a, lut_g, lut_s);
+    __syncthreads();
+    expand_act_async_body<T, WORDS>(a, x, lut_s, reinterpret_cast<uint8_t *>(lut_s) + lut_smem_bytes,
+                                    2 * 32 * 32 * (int)sizeof(T), sh, Ab, CW, n_groups);
+}
+
+// helpers of the weight bit-plane expansion (used by the merged kernel below and by expand_weight_bits_kernel)
+__device__ __forceinline__ uint32_t transpose32_warp(uint32_t x, int lane)
+{
+    // recursive block swap across lanes: after the step with distance j, 2j x 2j blocks are transposed
+#pragma unroll
+    for (int j = 16; j >= 1; j >>= 1) {
+        const uint32_t low = j == 16 ? 0x0000ffffu : j == 8 ? 0x00ff00ffu : j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
+        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
+        x = (lane & j) ? ((x & ~low) | ((y & ~low) >> j)) : ((x & low) | ((y & low) << j));
+    }
+    return x;
+}
+
+__device__ __forceinline__ uint32_t reverse_nibbles(uint32_t v)
+{
+    v = __byte_perm(__brev(v), 0, 0x0123); // all 32 bits reversed, bytes back in order: every byte bit-reversed
+    return ((v & 0x0f0f0f0fu) << 4) | ((v >> 4) & 0x0f0f0f0fu); // nibbles of a byte back in order
+}
+
+struct ExpandWBitsArgs {
+    int C, Co, KH, KW, KHW, CW, NC;
+    int period, nvals, words, linear_seeds, ohwi;
+    float scale;
+};
+
+// ---- the whole expand stage of a tensor-core conv call in ONE launch ------------------------------------------------
+// Stream tables, weight bit planes and activation bit planes used to be three dependent launches (plus the clearing of
+// the status word); for the smaller layers their launch latencies, not their work, made up most of the stage.  Here
+// every CTA builds both tables in its own shared memory straight from the LFSR (a few thousand short generator runs
+// per CTA, nothing read from global memory), takes its share of the weight items, then runs the pipelined activation
+// expansion.
+// Table of stream words of every (seed phase, value), built in shared memory without running the generator per entry.
+// Valid for gen_config 1 with progressive loading inactive (the front end's settings), where the activation and the
+// weight table coincide.  The LFSR visits its states in one cycle c_0, c_1, ...; the generator seeded with state s emits
+// at step t the comparison value > c_{pos(s) + t + 1}, so the word of (phase, value) has bit t set iff that threshold is
+// below the value.  Per phase one thread scatters bit t into the entry `threshold + 1` of its (thread-private) row and
+// then ORs the row's entries cumulatively: entry v ends up holding every bit whose threshold is < v.  Rows are written
+// twice (phase and phase + period) with one word of padding, the layout the expansion kernels index without a modulo.
+template <int WORDS>
+__device__ __forceinline__ void build_doubled_table(const LutParams &lp, int period, int nvals, uint32_t *lut_s,
+                                                    uint8_t *cyc_s, uint8_t *pos_s)
+{
+    const int row_words = nvals * WORDS + 1;
+    if (threadIdx.x == 0) {
+        int st = 1 - (lp.xnor ? 1 : 0);
+        for (int k = 0; k < period; k++) {
+            cyc_s[k] = (uint8_t)st;
+            pos_s[st] = (uint8_t)k;
+            st = lfsr_next(st, lp.l, lp.xnor);
+        }
+    }
+    __syncthreads();
+    for (int phase = threadIdx.x; phase < period; phase += blockDim.x) {
+        uint32_t *row = lut_s + phase * row_words;
+        for (int i = 0; i < nvals * WORDS; i++) row[i] = 0u;
+        int k = pos_s[phase + 1 - (lp.xnor ? 1 : 0)];
+        for (int t = 0; t < lp.bit_length; t++) {
+            if (++k == period) k = 0;
+            const int thr = cyc_s[k];
+            if (thr + 1 < nvals) row[(thr + 1) * WORDS + (t >> 5)] |= 1u << (t & 31);
+        }
+        for (int v = 1; v < nvals; v++)
+#pragma unroll
+            for (int j = 0; j < WORDS; j++) row[v * WORDS + j] |= row[(v - 1) * WORDS + j];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < (period - 1) * row_words; i += blockDim.x) lut_s[period * row_words + i] = lut_s[i];
+    __syncthreads();
+}
+
+struct ExpandAllArgs {
+    ExpandActArgs act;
+    ExpandWBitsArgs w;
+    LutParams lut;
+    int w_dtype;
+    int w_coarse;      // weight items are blocks of 32 output channels (else single output channels)
+    long long w_items;
+};
+
+__device__ __forceinline__ float load_weight_any(const void *w, int dtype, long long i)
+{
+    if (dtype == REXSC_F32) return static_cast<const float *>(w)[i];
+    if (dtype == REXSC_F16) return __half2float(static_cast<const __half *>(w)[i]);
+    return __bfloat162float(static_cast<const __nv_bfloat16 *>(w)[i]);
+}
+
+template <typename T, int WORDS>
+__global__ void __launch_bounds__(kFastWarps * 32, 2)
+expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restrict__ wt, uint32_t *__restrict__ Ab,
+                  uint32_t *__restrict__ Wb, int *__restrict__ status, int CW, long long n_groups, int lut_smem_bytes)
+{
+    __shared__ __align__(16) ActAsyncShared sh;
+    extern __shared__ __align__(16) uint32_t lut_s[];
+    __shared__ uint8_t cyc_s[128], pos_s[128]; // the LFSR cycle and the position of every state in it
+    const ExpandActArgs &a = g.act;
+    if (blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0; // the device status block of the workspace
+    build_doubled_table<WORDS>(g.lut, a.period, a.nvals, lut_s, cyc_s, pos_s);
+    // ---- weights: one warp per (block of 32 output channels, tap, channel word); lane = input channel of the word ----
+    // For every output channel of the block the warp looks the 32 channels' stream words up and transposes them across
+    // its lanes (lane = time slot afterwards); the 32 x 32 slot words of the block go through a swizzled tile in the
+    // warp's staging area so that each slot's words leave as one 128-byte run over the output channels.
+    {
+        const ExpandWBitsArgs &wa = g.w;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const int slots = WORDS * 32;
+        const size_t row_words_w = (size_t)wa.KHW * wa.CW;
+        const int row_words = wa.nvals * WORDS + 1;
+        uint32_t *tile = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(lut_s) + lut_smem_bytes) + warp * 2048; // [2][32][32]
+        // Small filters: one output channel per item (more items than warps matter more than coalesced stores)
+        for (long long item = (long long)blockIdx.x * kFastWarps + warp; !g.w_coarse && item < g.w_items;
+             item += (long long)gridDim.x * kFastWarps) {
+            const int cw = (int)(item % wa.CW);
+            long long t = item / wa.CW;
+            const int tap = (int)(t % wa.KHW);
+            const int co = (int)(t / wa.KHW); // 0 .. NC*64: rows past Co stay zero
+            const int kh = tap / wa.KW, kw = tap - kh * wa.KW;
+            const int ci = cw * 32 + lane;
+            int mag = 0;
+            bool neg = false;
+            if (ci < wa.C && co < wa.Co) {
+                const long long wi = wa.ohwi ? (((long long)co * wa.KH + kh) * wa.KW + kw) * wa.C + ci
+                                             : (((long long)co * wa.C + ci) * wa.KH + kh) * wa.KW + kw;
+                const float v = load_weight_any(wt, g.w_dtype, wi) * wa.scale;
+                const int qp = (int)ceilf(fminf(fmaxf(v, 0.f), wa.scale - 1.f));
+                const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - wa.scale), 0.f));
+                if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
+            }
+            const long long seed_ind = wa.linear_seeds ? (long long)ci : ((long long)ci * wa.KH + kh) * wa.KW + kw;
+            const int row_off = (int)((13 + seed_ind) % wa.period) * row_words;
+            const int nchunk = co >> 6, col = co & 63;
+#pragma unroll
+            for (int wd = 0; wd < WORDS; wd++) {
+                const uint32_t v = lut_s[row_off + mag * WORDS + wd];
+                uint32_t *dst = Wb + (((size_t)nchunk * slots + wd * 32 + lane) * row_words_w + (size_t)tap * wa.CW + cw) * 128 + col;
+                dst[0] = reverse_nibbles(transpose32_warp(neg ? 0u : v, lane));
+                dst[64] = reverse_nibbles(transpose32_warp(neg ? v : 0u, lane));
+            }
+        }
+        // Large filters: 32 output channels per item, stores coalesced through the tile
+        for (long long item = (long long)blockIdx.x * kFastWarps + warp; g.w_coarse && item < g.w_items;
+             item += (long long)gridDim.x * kFastWarps) {
+            const int cw = (int)(item % wa.CW);
+            long long t = item / wa.CW;
+            const int tap = (int)(t % wa.KHW);
+            const int cb = (int)(t / wa.KHW); // block of 32 output channels, 0 .. 2*NC: rows past Co stay zero
+            const int kh = tap / wa.KW, kw = tap - kh * wa.KW;
+            const int ci = cw * 32 + lane;
+            // seed index c*KH*KW + kh*KW + kw, offset 13 for both signs (sc_cuda_conv.cu:45,55-56); linear: c only
+            const long long seed_ind = wa.linear_seeds ? (long long)ci : ((long long)ci * wa.KH + kh) * wa.KW + kw;
+            const int row_off = (int)((13 + seed_ind) % wa.period) * row_words;
+            const int nchunk = cb >> 1, col0 = (cb & 1) * 32;
+#pragma unroll 1
+            for (int wd = 0; wd < WORDS; wd++) {
+#pragma unroll 4
+                for (int cl = 0; cl < 32; cl++) {
+                    const int co = cb * 32 + cl;
+                    int mag = 0;
+                    bool neg = false;
+                    if (ci < wa.C && co < wa.Co) {
+                        const long long wi = wa.ohwi ? (((long long)co * wa.KH + kh) * wa.KW + kw) * wa.C + ci
+                                                     : (((long long)co * wa.C + ci) * wa.KH + kh) * wa.KW + kw;
+                        const float v = load_weight_any(wt, g.w_dtype, wi) * wa.scale;
+                        // w_pos = ceil(clamp(v, 0, L-1)); w_neg = ceil(-clamp(v, 1-L, 0))  (sc_cuda.cpp:92-93)
+                        const int qp = (int)ceilf(fminf(fmaxf(v, 0.f), wa.scale - 1.f));
+                        const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - wa.scale), 0.f));
+                        if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
+                    }
+                    const uint32_t v = lut_s[row_off + mag * WORDS + wd]; // row `value 0` is zero
+                    tile[cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? 0u : v, lane));
+                    tile[1024 + cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? v : 0u, lane));
+                }
+                __syncwarp();
+                uint32_t *dst = Wb + (((size_t)nchunk * slots + wd * 32) * row_words_w + (size_t)tap * wa.CW + cw) * 128 + col0 + lane;
+#pragma unroll 4
+                for (int sl = 0; sl < 32; sl++) {
+                    dst[0] = tile[lane * 32 + (sl ^ lane)];
+                    dst[64] = tile[1024 + lane * 32 + (sl ^ lane)];
+                    dst += row_words_w * 128;
+                }
+                __syncwarp();
+            }
+        }
+    }
+    // (each warp goes on as soon as its own weight items are done: its staging area is its own)
+    expand_act_async_body<T, WORDS>(a, x, lut_s, reinterpret_cast<uint8_t *>(lut_s) + lut_smem_bytes, 8192, sh, Ab, CW, n_groups);
+}
+
+template <typename T, int WORDS>
+static int launch_expand_all_t(const ExpandAllArgs &g, const void *d_act, const void *d_w, uint32_t *d_Ab, uint32_t *d_Wb,
+                               int *d_status, int CW, size_t lut_bytes, cudaStream_t st)
+{
+    const long long n_groups = (g.act.NHWp + 31) / 32;
+    int dev = 0, sms = 0;
+    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
+    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    long long blocks = (n_groups + kFastWarps - 1) / kFastWarps;
+    const long long wblocks = (g.w_items + kFastWarps - 1) / kFastWarps;
+    if (blocks < wblocks) blocks = wblocks;
+    if (blocks > 2LL * sms) blocks = 2LL * sms; // persistent: two CTAs per SM
+    const size_t lut_al = (lut_bytes + 15) / 16 * 16;
+    // per warp: two activation tiles of 32 pixels x 32 channels, and at least the two 4 KB weight tiles
+    const size_t staging = (size_t)kFastWarps * 8192;
+    static_assert(2 * 32 * 32 * sizeof(T) <= 8192, "activation staging exceeds the per-warp area");
+    auto kernel = expand_all_kernel<T, WORDS>;
+    REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(lut_al + staging)));
+    kernel<<<(unsigned)blocks, kFastWarps * 32, lut_al + staging, st>>>(g, (const T *)d_act, d_w, d_Ab, d_Wb, d_status, CW,
+                                                                       n_groups, (int)lut_al);
+    REXSC_LAUNCH_CHECK("expand_all_kernel");
+    return REXSC_OK;
+}
+
+// The expand stage of the tensor-core path in one launch; REXSC_E_UNSUPPORTED when the shape does not qualify (the
+// caller then uses the separate launches): channels_last activations with 16-byte aligned channel runs, at most two
+// words per stream, tables that fit shared memory.
+int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const void *d_w, int xnor,
+                           uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, cudaStream_t st)
+{
+    if (!d.act_channels_last || (p.words != 1 && p.words != 2) || p.NHWp >= (1LL << 31)) return REXSC_E_UNSUPPORTED;
+    const int esz = d.act_dtype == REXSC_F32 ? 4 : 2;
+    if ((p.C % (16 / esz)) != 0 || (reinterpret_cast<uintptr_t>(d_act) & 15u) != 0) return REXSC_E_UNSUPPORTED;
+    const size_t lut_bytes = (size_t)(2 * p.period - 1) * (p.nvals * p.words + 1) * sizeof(uint32_t);
+    if (lut_bytes > 72 * 1024) return REXSC_E_UNSUPPORTED;
+    // the in-kernel table builder covers the front end's generator settings: no AND-n replication, progressive loading
+    // inactive (every value bit loaded from the first step on: load width - 1 >= total width)
+    if (d.gen_config != 1 || d.prog_load_width - 1 < d.prog_total_width || p.l > 7) return REXSC_E_UNSUPPORTED;
+    ExpandAllArgs g;
+    ExpandActArgs &a = g.act;
+    a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
+    a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
+    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
+    a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
+    a.scale = (float)p.scale;
+    ExpandWBitsArgs &w = g.w;
+    w.C = p.C; w.Co = p.Co; w.KH = p.KH; w.KW = p.KW; w.KHW = p.KHW;
+    w.CW = (p.C + 31) / 32; w.NC = (p.Co + 63) / 64;
+    w.period = p.period; w.nvals = p.nvals; w.words = p.words; w.linear_seeds = d.linear_seeds;
+    w.ohwi = d.w_channels_last; w.scale = (float)p.scale;
+    g.lut = LutParams{p.l, d.bit_length, d.gen_config, xnor, d.prog_total_width, d.prog_load_width, d.prog_load_wait, p.words};
+    g.w_dtype = d.w_dtype;
+    g.w_items = (long long)w.NC * 2 * w.KHW * w.CW; // blocks of 32 output channels x taps x channel words
+    g.w_coarse = g.w_items >= 2048 ? 1 : 0;           // enough of them to occupy the grid's warps
+    if (!g.w_coarse) g.w_items *= 32;                 // single output channels
+    const int CW = w.CW;
+#define REXSC_ALL(T) (p.words == 1 ? launch_expand_all_t<T, 1>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)   \
+                                   : launch_expand_all_t<T, 2>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st))
+    switch (d.act_dtype) {
+    case REXSC_F32: return REXSC_ALL(float);
+    case REXSC_F16: return REXSC_ALL(__half);
+    case REXSC_BF16: return REXSC_ALL(__nv_bfloat16);
+    default: return REXSC_E_BAD_ARG;
+    }
+#undef REXSC_ALL
+}
+
+template <typename T, int WORDS>
+static int launch_fast_t(const ExpandActArgs &a, bool nhwc, const void *d_act, const uint32_t *d_lut, uint32_t *d_Ab,
+                         int CW, size_t lut_bytes, cudaStream_t st)
+{
+    const long long n_groups = (a.NHWp + 31) / 32;
+    int dev = 0, sms = 0;
+    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
+    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    long long blocks = (n_groups + kFastWarps - 1) / kFastWarps;
+    if (blocks > 2LL * sms) blocks = 2LL * sms; // persistent: two CTAs per SM, each loads the table once
+    constexpr int E = 16 / (int)sizeof(T);
+    const bool vec = nhwc && (a.C % E) == 0 && (reinterpret_cast<uintptr_t>(d_act) & 15u) == 0;
+    auto run = [&](auto kernel) -> int {
+        REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lut_bytes));
+        kernel<<<(unsigned)blocks, kFastWarps * 32, lut_bytes, st>>>(a, (const T *)d_act, d_lut, d_Ab, CW, n_groups);
+        REXSC_LAUNCH_CHECK("expand_act_bits_fast_kernel");
+        return REXSC_OK;
+    };
+    if (!nhwc) return run(expand_act_bits_fast_kernel<T, false, false, WORDS>);
+    if (vec) {
+        // staging: two tiles of 32 pixels x 32 channels per warp behind the table
+        const size_t lut_al = (lut_bytes + 15) / 16 * 16;
+        const size_t smem = lut_al + (size_t)kFastWarps * 2 * 32 * 32 * sizeof(T);
+        auto kernel = expand_act_bits_async_kernel<T, WORDS>;
+        REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kernel<<<(unsigned)blocks, kFastWarps * 32, smem, st>>>(a, (const T *)d_act, d_lut, d_Ab, CW, n_groups, (int)lut_al);
+        REXSC_LAUNCH_CHECK("expand_act_bits_async_kernel");
+        return REXSC_OK;
+    }
+    return run(expand_act_bits_fast_kernel<T, true, false, WORDS>);
+}
+
+static int launch_expand_act_bits_fast(const ExpandActArgs &a, const rexsc_sc_conv_desc &d, bool nhwc, const void *d_act,
+                                       const uint32_t *d_lut, uint32_t *d_Ab, int CW, size_t lut_bytes, cudaStream_t st)
+{
+#define REXSC_FAST(T) (a.words == 1 ? launch_fast_t<T, 1>(a, nhwc, d_act, d_lut, d_Ab, CW, lut_bytes, st)             \
+                                    : launch_fast_t<T, 2>(a, nhwc, d_act, d_lut, d_Ab, CW, lut_bytes, st))
+    switch (d.act_dtype) {
+    case REXSC_F32: return REXSC_FAST(float);
+    case REXSC_F16: return REXSC_FAST(__half);
+    case REXSC_BF16: return REXSC_FAST(__nv_bfloat16);
+    default: return REXSC_E_BAD_ARG;
+    }
+#undef REXSC_FAST
+}
+
 int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const uint32_t *d_lut,
                            uint32_t *d_Ab, cudaStream_t st)
 {
@@ -535,6 +1259,9 @@ int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     const long long blocks = (items + 8 * per_warp - 1) / (8 * per_warp);
     if (blocks > 0x7fffffffLL) return REXSC_E_TOO_LONG;
     const bool nhwc = d.act_channels_last != 0;
+    const size_t fast_lut_bytes = (size_t)(2 * p.period - 1) * (p.nvals * p.words + 1) * sizeof(uint32_t);
+    if ((p.words == 1 || p.words == 2) && fast_lut_bytes <= 72 * 1024 && p.NHWp < (1LL << 31))
+        return launch_expand_act_bits_fast(a, d, nhwc, d_act, d_lut, d_Ab, CW, fast_lut_bytes, st);
 #define REXSC_ACT_BITS2(T, NHWC_, SM_)                                                                                  \
     expand_act_bits_kernel<T, NHWC_, SM_><<<(unsigned)blocks, 256, SM_ ? lut_bytes : 0, st>>>((a), (const T *)d_act, d_lut, d_Ab, CW, items)
 #define REXSC_ACT_BITS(T)                                                                                              \
@@ -637,30 +1364,6 @@ int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const v
 // Wb[nchunk][slot][tap*CW + cw][row], row = sign*64 + local output channel, nibbles bit-reversed (the kernel's operand
 // scaling).  One warp per (output channel, tap, channel word): lane = input channel; the 32 x 32 bit matrix
 // (channel x slot) of each sign is transposed across the warp so that lane t holds slot t's channel-packed word.
-__device__ __forceinline__ uint32_t transpose32_warp(uint32_t x, int lane)
-{
-    // recursive block swap across lanes: after the step with distance j, 2j x 2j blocks are transposed
-#pragma unroll
-    for (int j = 16; j >= 1; j >>= 1) {
-        const uint32_t low = j == 16 ? 0x0000ffffu : j == 8 ? 0x00ff00ffu : j == 4 ? 0x0f0f0f0fu : j == 2 ? 0x33333333u : 0x55555555u;
-        const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
-        x = (lane & j) ? ((x & ~low) | ((y & ~low) >> j)) : ((x & low) | ((y & low) << j));
-    }
-    return x;
-}
-
-__device__ __forceinline__ uint32_t reverse_nibbles(uint32_t v)
-{
-    v = __byte_perm(__brev(v), 0, 0x0123); // all 32 bits reversed, bytes back in order: every byte bit-reversed
-    return ((v & 0x0f0f0f0fu) << 4) | ((v >> 4) & 0x0f0f0f0fu); // nibbles of a byte back in order
-}
-
-struct ExpandWBitsArgs {
-    int C, Co, KH, KW, KHW, CW, NC;
-    int period, nvals, words, linear_seeds, ohwi;
-    float scale;
-};
-
 template <typename T>
 __global__ void __launch_bounds__(256) expand_weight_bits_kernel(ExpandWBitsArgs a, const T *__restrict__ wt,
                                                                  const uint32_t *__restrict__ lut, uint32_t *__restrict__ Wb,

@@ -196,3 +196,36 @@ def test_reference_training_loop_runs_on_the_drop_in(fe):
     layers = train.sc_layers(fe, tr.model)
     assert len(layers) == 19
     assert sum(float(m.std_coef.abs().sum()) > 0 for m in layers) >= 15
+
+
+@pytest.mark.parametrize("channels_last", [False, True])
+def test_guide_conv_pair_matches_the_two_convolutions(ops, channels_last):
+    """The opt-in single guide convolution against the reference's two (utils_functional.py:1199-1211): same values,
+    same gradients with respect to activation and weight (1e-3 relative)."""
+    from rexsc_b200.frontend.guide import guide_conv_pair
+
+    torch.manual_seed(3)
+    x = torch.rand(8, 64, 16, 16, device="cuda")
+    w = (torch.randn(96, 64, 3, 3, device="cuda") * 0.1).clamp(-1, 1)
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
+        w = w.contiguous(memory_format=torch.channels_last)
+    cot = torch.randn(8, 96, 8, 8, device="cuda")
+    res = []
+    for fused in (False, True):
+        xi, wi = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        if fused:
+            p, n = guide_conv_pair(xi, wi, (2, 2), (1, 1))
+        else:
+            p = torch.nn.functional.conv2d(xi, wi.clamp(0, 100), padding=(1, 1), stride=(2, 2))
+            n = torch.nn.functional.conv2d(xi, -(wi.clamp(-100, 0)), padding=(1, 1), stride=(2, 2))
+        (p * cot - 0.5 * n * cot).sum().backward()
+        res.append((p.detach(), n.detach(), xi.grad, wi.grad))
+    for a, b in zip(res[0], res[1]):
+        assert rel_err(b, a) < 1e-3
+    # and the halves feed the fused point-wise op like two separate tensors do
+    bias = torch.tensor([0.01, -0.05, 0.02, 0.003, -0.001, 0.0002], device="cuda")
+    zero = torch.zeros(6, device="cuda")
+    a = ops.or_approx_n_forward_bias_std_both_acc(res[0][0], res[0][1], bias, zero, 2)
+    b = ops.or_approx_n_forward_bias_std_both_acc(res[1][0], res[1][1], bias, zero, 2)
+    assert rel_err(b, a) < 1e-3
