@@ -229,6 +229,10 @@ int rexsc_sc_counts_to_value(const int16_t *d_pos, const int16_t *d_neg, int32_t
  *   int32  reserved
  * d_stats: REXSC_CALIB_STATS_BYTES of device memory, 8-byte aligned.  guide_dtype REXSC_F32 or REXSC_F16.
  * counts_via_half != 0 rounds each count to fp16 first, as `.to(float16)` under autocast does (exact up to 2048).
+ * REXSC_F16 guide values are widened to fp32 before the comparisons and the subtraction, i.e. the result equals
+ * compute_bias_std_coef(a_bit, a_act.float()); torch itself would round the window edges and err to fp16 for a half
+ * a_act.  The reference's front end never has a half a_act (its guide values are the fp32 outputs of
+ * or_approx_n_forward_acc, utils_functional.py:474,1234-1235); REXSC_F32 with counts_via_half is its autocast case.
  */
 #define REXSC_CALIB_BINS 30
 #define REXSC_CALIB_STATS_BYTES (REXSC_CALIB_BINS * 3 * 8 + 8)

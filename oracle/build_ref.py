@@ -24,6 +24,21 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
+
+def default_reference_root() -> str:
+    """Where the reference checkout lies: REXSC_REFERENCE_ROOT, else the ``reference_path`` entry of the BASELINE.json
+    next to this directory, else nothing (an empty string: no sources, nothing is built)."""
+    env = os.environ.get("REXSC_REFERENCE_ROOT")
+    if env:
+        return env
+    try:
+        import json
+
+        with open(os.path.join(os.path.dirname(HERE), "BASELINE.json")) as fh:
+            return json.load(fh).get("reference_path") or ""
+    except Exception:
+        return ""
+
 MODULES = {
     "sc_extension_ref": ["sc.cpp", "sc_conv.cpp", "sc_matmul.cpp"],
     "fixed_extension_ref": ["fixed.cpp"],
@@ -40,7 +55,7 @@ def _cxx() -> str:
 
 def build(reference_root: str | None = None, force: bool = False) -> bool:
     """Return True when both modules exist under oracle/_ref after the call."""
-    root = reference_root or os.environ.get("REXSC_REFERENCE_ROOT", "/root/reference")
+    root = reference_root or default_reference_root()
     src_dir = os.path.join(root, "torch_c", "sc-extension")
     have_src = os.path.isdir(src_dir)
     os.makedirs(OUT, exist_ok=True)
@@ -94,7 +109,7 @@ GPU_MODULES = {
 def build_gpu(reference_root: str | None = None, force: bool = False) -> bool:
     """Cross-compile the reference's GPU extensions (no GPU needed) into oracle/_ref; used on a GPU box as a
     second parity anchor (the reference's own kernels, XNOR generator included) and as the kernel to beat."""
-    root = reference_root or os.environ.get("REXSC_REFERENCE_ROOT", "/root/reference")
+    root = reference_root or default_reference_root()
     src_dir = os.path.join(root, "torch_c", "sc-extension")
     have_src = os.path.isdir(src_dir)
     os.makedirs(OUT, exist_ok=True)

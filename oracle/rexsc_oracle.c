@@ -5,17 +5,17 @@
  * the thing shipped or measured: only tests/, __graft_entry__.smoke() and the
  * cpu_baseline / reference legs of bench.py may build, load or call it.
  *
- * Parity status: PINNED for the integer paths.  The restatement is checked
- * bit-for-bit against the reference's own CPU extensions compiled unchanged
- * (oracle/build_ref.py) and against golden vectors produced by them
- * (tests/golden/).  The reference CPU code implements the XOR-feedback LFSR only,
- * so the XNOR generator (the GPU reference's production setting) is pinned through
- * the shared code path (same seeds, same accumulation) plus the LFSR period /
- * state-space properties tested in tests/test_oracle.py, not by an executed
- * reference.  The floating-point point-wise functions are "parity unpinned": the
- * reference holds no test vectors for them and its GPU kernels cannot run where
- * the fixtures are made; they are checked against the closed-form formulas in
- * double precision.
+ * Parity status: PINNED.  The restatement is checked bit-for-bit against the
+ * reference's own CPU extensions compiled unchanged (oracle/build_ref.py) and
+ * against golden vectors produced by them (tests/golden/).  The reference CPU code
+ * implements the XOR-feedback LFSR only; the XNOR generator (the GPU reference's
+ * production setting) is pinned through the shared code path plus the LFSR period /
+ * state-space properties of tests/test_oracle.py and, where a GPU is available,
+ * against the reference's own GPU extensions executed unchanged
+ * (tests/test_gpu_vs_reference_gpu_ext.py: the library's kernels equal both this
+ * oracle and the reference's kernels, bit for bit).  The floating-point point-wise
+ * functions are checked against the closed-form formulas in double precision here
+ * and bit-for-bit against the reference's GPU kernels in the same GPU test file.
  *
  * Every function cites the reference file:line (paths inside nanocad-lab/rex-sc)
  * whose behaviour it restates.  The algorithms are written differently on purpose

@@ -139,6 +139,9 @@ static void linear_desc(rexsc_sc_conv_desc *d, int32_t batch, int32_t c_in, int3
     d->c_out = c_out; d->kh = 1; d->kw = 1;
     d->stride_h = 1; d->stride_w = 1;
     d->act_dtype = act_dtype; d->w_dtype = w_dtype;
+    // with 1x1 maps and filters NCHW and NHWC are the same memory; channels_last selects the vectorised expansion and
+    // lets short grids split their time slots over more CTAs
+    d->act_channels_last = 1; d->w_channels_last = 1; d->out_channels_last = 1;
     d->bit_length = bit_length; d->lfsr_length = lfsr_length; d->bin_config = bin_config;
     d->gen_config = gen_config; d->xnor = 0;
     d->prog_total_width = tw; d->prog_load_width = lw; d->prog_load_wait = lwait;

@@ -714,11 +714,16 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
         const bool rows_ok = d.out_channels_last && (p.Co % kTcCout) == 0 && aligned4;
         // (measured: tiles of strided layers -- several patch rows per thread, 32-channel steps -- lose more at the extra
         // tile switches than the fuller wave gains)
-        const bool long_tiles = g.rows_a <= kTcWorkers && (slots / 2) * g.CK >= 32;
+        auto long_tiles = [&](int parts) { return g.rows_a <= kTcWorkers && (slots / parts) * g.CK >= 32; };
         // and the atomic adds cost about as much as they save once the outputs are tens of MB (measured at 28x28)
         const bool small_out = (size_t)p.M * p.Co * sizeof(int16_t) <= (size_t)16 << 20;
-        if (rows_ok && long_tiles && small_out && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL)
+        if (rows_ok && long_tiles(2) && small_out && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL)
             a.split = 2;
+        // Grids that leave most SMs idle even then (a linear layer: a handful of tiles, long streams): keep halving the
+        // share of the time slots per tile while every tile still finds an SM of its own
+        if (rows_ok && small_out)
+            while (a.split < 16 && slots % (2 * a.split) == 0 && long_tiles(2 * a.split) && tiles * 2 * a.split <= sms)
+                a.split *= 2;
     }
     a.slots_part = slots / a.split;
     a.total_tiles = a.tiles_x * NC * a.split;

@@ -19,7 +19,7 @@ from . import _lib
 _DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 _DEBUG = os.environ.get("REXSC_B200_DEBUG", "0") == "1"
 
-# conv kernel selection for tests / benchmarks: "auto" | "direct" | "tiled"
+# conv kernel selection for tests / benchmarks: "auto" | "direct" | "tiled" | "tensor"
 _kernel_choice = threading.local()
 
 
@@ -159,7 +159,8 @@ class PreparedConv:
                                 stride, prog_load, bin_config, gen_config, xnor)
         pos, neg = conv(input)          # as often as needed; build a new object after the weights change
 
-    The object owns its workspace (activation + weight streams of that layer)."""
+    The object owns its workspace (activation + weight streams of that layer): about the size of the layer's activation
+    bit planes -- 220 MB for the largest ResNet-18 layer at batch 256, roughly 1 GB for all 19 layers of that model."""
 
     def __init__(self, weight: torch.Tensor, input_shape, input_dtype, channels_last: bool, bit_length: int,
                  lfsr_length: int, padding: Sequence[int], stride: Sequence[int], prog_load: Sequence[int],
@@ -501,6 +502,9 @@ def sc_calib_stats(result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos
     utils_functional.py:917-925).  Returns a float64 CUDA tensor of 91 entries: ``[:90].view(30, 3)`` are
     ``(count, sum err, sum err^2)`` of the windows ``[e_i, e_i + 0.1)``, ``e = linspace(0, max(counts)/L, 30)``;
     the first 4 bytes of entry 90 hold the largest count as int32.
+
+    Half-precision guide values are widened to float32 before the window comparisons and the subtraction (the result
+    equals the reference function on ``a_act.float()``); the reference's front end always passes float32 guides.
 
     ``between(stats)``, if given, runs after the maximum is known and before the windows are filled: a batch
     sharded over several GPUs all-reduces the maximum there (``sharding.reduce_calib_max_``) so that all ranks use

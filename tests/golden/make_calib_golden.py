@@ -42,11 +42,12 @@ def inputs(n, L, or_n, hi, noise, seed):
 
 
 def main():
-    import rexsc_b200
+    from rexsc_b200 import frontend
 
-    rexsc_b200.install_dropin()
-    sys.path.insert(0, os.environ.get("REXSC_REFERENCE_ROOT", "/root/reference"))
-    import utils_functional as uf
+    # the reference's utils_functional from its checkout (REXSC_REFERENCE_ROOT or BASELINE.json's reference_path)
+    if frontend.reference_root() is None:
+        raise SystemExit("make_calib_golden: no reference checkout reachable (set REXSC_REFERENCE_ROOT)")
+    uf = frontend.load().utils_functional
 
     real_lstsq = torch.linalg.lstsq
     out = {}
