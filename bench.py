@@ -265,10 +265,16 @@ def run_sc(args, wl, rank, world, local_rank):
         l["x_pin16"] = l["x_host"].half().contiguous(memory_format=fmt).pin_memory()
         l["x_pin32"] = l["x_host"].pin_memory()
     launches = {"n": 0}
-    KERNELS_PER_CONV = 4   # stream tables, activation expansion, weight expansion, accumulate
+    for l in layers:
+        # kernels per conv call: expand + accumulate where the single-launch expand stage applies (tensor-core path,
+        # streams of at most 64 bits, fp32 NCHW or channels_last with 16-byte aligned channel runs); else stream
+        # tables, activation expansion, weight expansion, accumulate
+        d = _sc_desc(_lib, l, wl, l["x"], l["w"])
+        tensor = lib.rexsc_sc_conv2d_kernel_choice(C.byref(d)) == 3
+        l["kernels"] = 2 if (tensor and l["L"] <= 64 and (not wl["channels_last"] or l["shape"][0] % 8 == 0)) else 4
 
     def conv(l, x):
-        launches["n"] += KERNELS_PER_CONV
+        launches["n"] += l["kernels"]
         return ops.conv2d_generic_general_split_acc(x, l["w"], l["L"], -1, 16, (0, 0), (l["stride"],) * 2, PROG,
                                                     or_n - 1, 1, True, False)
 

@@ -751,6 +751,12 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src,
     const int bytes = valid ? 16 : 0; // 0: the 16 destination bytes are zero-filled, nothing is read
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src, bool valid)
+{
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gmem_src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
@@ -801,7 +807,8 @@ struct ActAsyncShared {
 
 // The pipelined expansion of all groups of this CTA.  lut_s: the doubled, padded table, already in shared memory;
 // raw_all: per warp (raw_stride bytes apart) two staging tiles of 32 pixels x 32 channels.
-template <typename T, int WORDS>
+// NCHW (fp32 only): the staged tile is [channel][pixel], fetched with 4-byte copies (one per channel and lane = pixel).
+template <typename T, int WORDS, bool NCHW = false>
 __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, const T *__restrict__ x,
                                                       const uint32_t *lut_s, uint8_t *raw_all, int raw_stride,
                                                       ActAsyncShared &sh, uint32_t *__restrict__ Ab, int CW,
@@ -833,12 +840,24 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
         const uint32_t pix_mod = a.linear_seeds ? 0u : ((uint32_t)h * (uint32_t)a.Wp + (uint32_t)w) % period;
         r.pix_base = pix_mod * row_words;
         r.store_ok = r.P < a.NHWp;
-        xb_s[warp][buf][lane] = inside ? (((long long)n * a.H + hi) * a.W + wi) * a.C : -1;
+        xb_s[warp][buf][lane] = !inside ? -1
+                                : NCHW  ? (((long long)n * a.C) * a.H + hi) * a.W + wi
+                                        : (((long long)n * a.H + hi) * a.W + wi) * a.C;
         return r;
     };
     // start the copies of tile (group in xb_s[buf], channel word cw) into staging buffer `stage`
     auto issue = [&](int buf, int cw, int stage) {
         uint8_t *dst = raw_s + stage * kTileBytes;
+        if (NCHW) {
+            const long long xb = xb_s[warp][buf][lane], plane = (long long)a.H * a.W;
+#pragma unroll 8
+            for (int cc = 0; cc < 32; cc++) {
+                const bool ok = xb >= 0 && cw * 32 + cc < a.C;
+                cp_async4(dst + cc * kRowBytes + lane * 4, ok ? (const void *)(x + xb + (cw * 32 + cc) * plane) : (const void *)x, ok);
+            }
+            cp_async_commit();
+            return;
+        }
         const int c = cw * 32 + ch;
 #pragma unroll
         for (int p0 = 0; p0 < 32; p0 += PPI) {
@@ -870,10 +889,21 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
             // ---- quantise the staged 32 pixels x 32 channels into the byte tile ----
             {
                 const uint8_t *src = raw_s + stage * kTileBytes;
+                if (NCHW) {
+                    // lane = pixel reads its column of the [channel][pixel] tile and packs four channels per store
+                    const float *col = reinterpret_cast<const float *>(src) + lane;
 #pragma unroll
-                for (int p0 = 0; p0 < 32; p0 += PPI)
-                    store_bytes(reinterpret_cast<uint32_t *>(&q_s[warp][p0 + pp][ch]),
-                                RawVec<T>::quant(src + (p0 + pp) * kRowBytes + ch * (int)sizeof(T), a.scale, top));
+                    for (int c4 = 0; c4 < 32; c4 += 4) {
+                        const uint32_t lo = prmt(quant_ceil_bits(col[c4 * 32], a.scale, top), quant_ceil_bits(col[(c4 + 1) * 32], a.scale, top), 0x0040u);
+                        const uint32_t hi2 = prmt(quant_ceil_bits(col[(c4 + 2) * 32], a.scale, top), quant_ceil_bits(col[(c4 + 3) * 32], a.scale, top), 0x0040u);
+                        *reinterpret_cast<uint32_t *>(&q_s[warp][lane][c4]) = prmt(lo, hi2, 0x5410u);
+                    }
+                } else {
+#pragma unroll
+                    for (int p0 = 0; p0 < 32; p0 += PPI)
+                        store_bytes(reinterpret_cast<uint32_t *>(&q_s[warp][p0 + pp][ch]),
+                                    RawVec<T>::quant(src + (p0 + pp) * kRowBytes + ch * (int)sizeof(T), a.scale, top));
+                }
                 const uint32_t c = (uint32_t)(cw * 32 + lane);
                 const uint32_t cph = a.linear_seeds ? c % period : (uint32_t)(((unsigned long long)c * a.plane_mod) % period);
                 u_s[warp][lane] = cph * row_words;
@@ -1026,7 +1056,7 @@ __device__ __forceinline__ float load_weight_any(const void *w, int dtype, long 
     return __bfloat162float(static_cast<const __nv_bfloat16 *>(w)[i]);
 }
 
-template <typename T, int WORDS>
+template <typename T, int WORDS, bool NCHW>
 __global__ void __launch_bounds__(kFastWarps * 32, 2)
 expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restrict__ wt, uint32_t *__restrict__ Ab,
                   uint32_t *__restrict__ Wb, int *__restrict__ status, int CW, long long n_groups, int lut_smem_bytes)
@@ -1124,10 +1154,10 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
         }
     }
     // (each warp goes on as soon as its own weight items are done: its staging area is its own)
-    expand_act_async_body<T, WORDS>(a, x, lut_s, reinterpret_cast<uint8_t *>(lut_s) + lut_smem_bytes, 8192, sh, Ab, CW, n_groups);
+    expand_act_async_body<T, WORDS, NCHW>(a, x, lut_s, reinterpret_cast<uint8_t *>(lut_s) + lut_smem_bytes, 8192, sh, Ab, CW, n_groups);
 }
 
-template <typename T, int WORDS>
+template <typename T, int WORDS, bool NCHW>
 static int launch_expand_all_t(const ExpandAllArgs &g, const void *d_act, const void *d_w, uint32_t *d_Ab, uint32_t *d_Wb,
                                int *d_status, int CW, size_t lut_bytes, cudaStream_t st)
 {
@@ -1143,7 +1173,7 @@ static int launch_expand_all_t(const ExpandAllArgs &g, const void *d_act, const 
     // per warp: two activation tiles of 32 pixels x 32 channels, and at least the two 4 KB weight tiles
     const size_t staging = (size_t)kFastWarps * 8192;
     static_assert(2 * 32 * 32 * sizeof(T) <= 8192, "activation staging exceeds the per-warp area");
-    auto kernel = expand_all_kernel<T, WORDS>;
+    auto kernel = expand_all_kernel<T, WORDS, NCHW>;
     REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(lut_al + staging)));
     kernel<<<(unsigned)blocks, kFastWarps * 32, lut_al + staging, st>>>(g, (const T *)d_act, d_w, d_Ab, d_Wb, d_status, CW,
                                                                        n_groups, (int)lut_al);
@@ -1157,9 +1187,15 @@ static int launch_expand_all_t(const ExpandAllArgs &g, const void *d_act, const 
 int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const void *d_w, int xnor,
                            uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, cudaStream_t st)
 {
-    if (!d.act_channels_last || (p.words != 1 && p.words != 2) || p.NHWp >= (1LL << 31)) return REXSC_E_UNSUPPORTED;
+    if ((p.words != 1 && p.words != 2) || p.NHWp >= (1LL << 31)) return REXSC_E_UNSUPPORTED;
     const int esz = d.act_dtype == REXSC_F32 ? 4 : 2;
-    if ((p.C % (16 / esz)) != 0 || (reinterpret_cast<uintptr_t>(d_act) & 15u) != 0) return REXSC_E_UNSUPPORTED;
+    const bool nchw = !d.act_channels_last;
+    if (nchw) {
+        // channel-planar inputs are staged with 4-byte copies: fp32 only
+        if (d.act_dtype != REXSC_F32 || (reinterpret_cast<uintptr_t>(d_act) & 3u) != 0) return REXSC_E_UNSUPPORTED;
+    } else if ((p.C % (16 / esz)) != 0 || (reinterpret_cast<uintptr_t>(d_act) & 15u) != 0) {
+        return REXSC_E_UNSUPPORTED;
+    }
     const size_t lut_bytes = (size_t)(2 * p.period - 1) * (p.nvals * p.words + 1) * sizeof(uint32_t);
     if (lut_bytes > 72 * 1024) return REXSC_E_UNSUPPORTED;
     // the in-kernel table builder covers the front end's generator settings: no AND-n replication, progressive loading
@@ -1184,8 +1220,11 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     g.w_coarse = g.w_items >= 2048 ? 1 : 0;           // enough of them to occupy the grid's warps
     if (!g.w_coarse) g.w_items *= 32;                 // single output channels
     const int CW = w.CW;
-#define REXSC_ALL(T) (p.words == 1 ? launch_expand_all_t<T, 1>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)   \
-                                   : launch_expand_all_t<T, 2>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st))
+#define REXSC_ALL(T) (p.words == 1 ? launch_expand_all_t<T, 1, false>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)   \
+                                   : launch_expand_all_t<T, 2, false>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st))
+    if (nchw)
+        return p.words == 1 ? launch_expand_all_t<float, 1, true>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)
+                            : launch_expand_all_t<float, 2, true>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st);
     switch (d.act_dtype) {
     case REXSC_F32: return REXSC_ALL(float);
     case REXSC_F16: return REXSC_ALL(__half);

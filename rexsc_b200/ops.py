@@ -18,6 +18,24 @@ from . import _lib
 
 _DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}
 _DEBUG = os.environ.get("REXSC_B200_DEBUG", "0") == "1"
+_NVTX = os.environ.get("REXSC_B200_NVTX", "0") == "1"
+
+
+def _traced(fn):
+    """With REXSC_B200_NVTX=1 every op call is an NVTX range named after the op (shows up in Nsight timelines between
+    the front end's own torch ranges); otherwise the function is returned untouched."""
+    if not _NVTX:
+        return fn
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        torch.cuda.nvtx.range_push("rexsc_b200." + fn.__name__)
+        try:
+            return fn(*args, **kwargs)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    return wrapper
 
 # conv kernel selection for tests / benchmarks: "auto" | "direct" | "tiled" | "tensor"
 _kernel_choice = threading.local()
@@ -93,6 +111,7 @@ def _flat_dense(t: torch.Tensor) -> torch.Tensor:
 
 
 # ---- SC conv2d / linear -------------------------------------------------------------------------------
+@_traced
 def conv2d_generic_general_split_acc(input: torch.Tensor, weight: torch.Tensor, bit_length: int, lfsr_length: int,
                                      z_units: int, padding: Sequence[int], stride: Sequence[int],
                                      prog_load: Sequence[int], bin_config: int, gen_config: int, xnor: bool,
@@ -222,6 +241,7 @@ class PreparedConv:
         return [pos, neg]
 
 
+@_traced
 def conv2d_generic_general_acc(input, weight, bit_length, lfsr_length, z_units, padding, stride, prog_load,
                                bin_config, gen_config, xnor, mux) -> torch.Tensor:
     """SC conv2d forward, returns pos - neg as int16 (sc_cuda.cpp:73-85)."""
@@ -241,6 +261,7 @@ def workspace_status(device=None) -> int:
         return _lib.load().rexsc_workspace_status(_ptr(buf), _stream(dev))
 
 
+@_traced
 def linear_generic_general_acc(input: torch.Tensor, weight: torch.Tensor, prog_load: Sequence[int], bit_length: int,
                                lfsr_length: int, bin_config: int, gen_config: int, xnor: bool,
                                mux: bool) -> List[torch.Tensor]:
@@ -326,6 +347,7 @@ def _match_layout(t: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@_traced
 def or_approx_n_forward_acc(input: torch.Tensor, or_n: int) -> torch.Tensor:
     """f_n(input) as float32, same strides as the input (sc_cuda_pw.cu:708-746)."""
     _require_cuda(input, "or_approx_n_forward_acc")
@@ -346,6 +368,7 @@ def _require_f32_grad(grad: torch.Tensor, what: str) -> None:
         raise RuntimeError(f"{what}: expected scalar type Float for grad_output but found {grad.dtype}")
 
 
+@_traced
 def or_approx_n_backward_acc(grad_output: torch.Tensor, input: torch.Tensor, or_n: int) -> torch.Tensor:
     """grad_output * f_n'(fp16(input)) as float32 (sc_cuda_pw.cu:767-811)."""
     _require_cuda(grad_output, "or_approx_n_backward_acc")
@@ -362,6 +385,7 @@ def or_approx_n_backward_acc(grad_output: torch.Tensor, input: torch.Tensor, or_
     return out
 
 
+@_traced
 def or_approx_n_forward_bias_std_both_acc(input_pos: torch.Tensor, input_neg: torch.Tensor, bias_coef: torch.Tensor,
                                           std_coef: torch.Tensor, or_n: int) -> torch.Tensor:
     """y(f_n(pos)) - y(f_n(neg)) with bias polynomial and Gaussian error injection, float32
@@ -383,6 +407,7 @@ def or_approx_n_forward_bias_std_both_acc(input_pos: torch.Tensor, input_neg: to
     return out
 
 
+@_traced
 def or_approx_n_backward_bias_std_both_acc(grad_output: torch.Tensor, input_pos: torch.Tensor,
                                            input_neg: torch.Tensor, bias_coef: torch.Tensor,
                                            or_n: int) -> List[torch.Tensor]:
@@ -405,6 +430,7 @@ def or_approx_n_backward_bias_std_both_acc(grad_output: torch.Tensor, input_pos:
     return [gp, gn]
 
 
+@_traced
 def or_approx_n_forward_bias_std_acc(input: torch.Tensor, bias_coef: torch.Tensor, std_coef: torch.Tensor,
                                      or_n: int) -> torch.Tensor:
     """Single-sided y(f_n(fp16(input))) returned as float16 (sc_cuda_pw.cu:834-861)."""
@@ -423,6 +449,7 @@ def or_approx_n_forward_bias_std_acc(input: torch.Tensor, bias_coef: torch.Tenso
     return out
 
 
+@_traced
 def or_approx_n_backward_bias_std_acc(grad_output: torch.Tensor, input: torch.Tensor, bias_coef: torch.Tensor,
                                       or_n: int) -> torch.Tensor:
     """Single-sided backward, float32 (sc_cuda_pw.cu:929-950)."""
@@ -442,6 +469,7 @@ def or_approx_n_backward_bias_std_acc(grad_output: torch.Tensor, input: torch.Te
 
 
 # ---- caller arithmetic on the SC counts (one pass each) ------------------------------------------------------
+@_traced
 def sc_counts_to_value(result_pos: torch.Tensor, result_neg: torch.Tensor, bit_length: int,
                        dtype: torch.dtype = torch.float32, split: bool = True, diff: bool = False):
     """``result.to(dtype) / bit_length`` for both signs and, with ``diff``, their difference, in one pass over the
@@ -494,6 +522,7 @@ def _calib_operands(result_pos, result_neg, value_pos, value_neg, what):
     return p, n, gp, gn, gdt
 
 
+@_traced
 def sc_calib_stats(result_pos: torch.Tensor, result_neg: torch.Tensor, value_pos: torch.Tensor,
                    value_neg: torch.Tensor, bit_length: int, counts_via_half: bool = False,
                    between=None) -> torch.Tensor:
@@ -583,6 +612,7 @@ def compute_bias_std_coef(or_n: int, result_pos: torch.Tensor, result_neg: torch
 
 
 # ---- FXP conv -------------------------------------------------------------------------------------------
+@_traced
 def conv2d_saturate_acc(input: torch.Tensor, weight: torch.Tensor, add_config: int, precision_in: int,
                         precision_out: int, padding: Sequence[int], stride: Sequence[int]) -> torch.Tensor:
     """FXP saturating conv forward, int32 NCHW (fixed_cuda.cpp:24-34)."""
