@@ -278,13 +278,13 @@ int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void *d_act, con
 
 /*
  * Register-only LOP3 issue-rate probe used by the benchmark to measure the integer-ALU roofline the
- * SC conv kernels are judged against.  Launches `blocks` x 256 threads doing `iters` x 64 dependent-free
+ * SC conv kernels are measured against.  Launches `blocks` x 256 threads doing `iters` x 64 dependent-free
  * LOP3 per thread; d_sink receives one word per thread.  Total lane-ops = blocks*256*iters*64.
  */
 int rexsc_alu_probe(int32_t blocks, int32_t iters, uint32_t *d_sink, void *stream);
 
 /*
- * Tensor-pipe probe used by the benchmark to measure the int8 tcgen05 rate the tensor-core SC conv kernel is judged
+ * Tensor-pipe probe used by the benchmark to measure the int8 tcgen05 rate the tensor-core SC conv kernel is measured
  * against: `blocks` CTAs (two fit an SM) each issue iters x 16 int8 MMAs of shape M128 x n_cols x K32 (n_cols 128
  * or 256) on fixed shared-memory operands.  Total multiply-accumulates = blocks*iters*16*128*n_cols*32.
  * d_sink receives blocks*128 words.
