@@ -54,13 +54,28 @@ static int conv_buffers(const rexsc_sc_conv_desc *desc, void *d_workspace, size_
     return REXSC_OK;
 }
 
+// Activation grid of the tensor-core path for a plan (see make_compact_plan in common.cuh):
+//   kGridStandard     every padded pixel is stored;
+//   kGridCompact      the compact grid, valid by construction: the descriptor itself pads by at least one pixel;
+//   kGridSpeculative  the layer qualifies but the border is the caller's data (a caller that pads before the call, as
+//                     the reference's front end does): the expand stage checks the border on the device and leaves
+//                     its verdict in word 1 of the status block (0: compact planes, 1: standard planes), and the
+//                     accumulate stage launches one kernel for either outcome, of which the verdict lets one run.
+enum { kGridStandard = 0, kGridCompact = 1, kGridSpeculative = 2 };
+
+static int grid_mode(const rexsc_sc_conv_desc *desc, const ConvPlan &p, int kernel, ConvPlan *pc)
+{
+    if (kernel != REXSC_KERNEL_TENSOR || desc->linear_seeds || !make_compact_plan(p, pc)) return kGridStandard;
+    return (p.ph >= 1 && p.pw >= 1) ? kGridCompact : kGridSpeculative;
+}
+
 // stage 1: stream generation (LUTs, activation words, weight words + signs) into the workspace.
 // allow_partial: a null operand is skipped and what an earlier expand with the same descriptor and workspace wrote
 // for it stays in place (a caller whose weights do not change between calls expands them once).
 static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, void *d_workspace,
                        size_t workspace_bytes, cudaStream_t st, bool allow_partial)
 {
-    ConvPlan p;
+    ConvPlan p, pc;
     ConvBuffers b;
     int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
     if (rc != REXSC_OK) return rc;
@@ -69,26 +84,45 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
     if (k < 0) return k;
     // The linear generators always use the XOR LFSR (torch_c/sc-extension/sc_cuda_matmul.cu:27-57).
     const int xnor = desc->linear_seeds ? 0 : (desc->xnor ? 1 : 0);
-    if (k == REXSC_KERNEL_TENSOR && d_act && d_weight) {
+    const int mode = grid_mode(desc, p, k, &pc);
+    const ConvPlan &pa = mode == kGridCompact ? pc : p; // the grid the separate activation launches below write
+    uint32_t *Ab = static_cast<uint32_t *>(b.tc);
+    // the weight planes sit behind the largest (the standard) activation planes, whichever grid is in use
+    uint32_t *Wb = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p));
+    if (k == REXSC_KERNEL_TENSOR && d_act) {
         // one launch for the whole stage (it also clears the status block) where the shape qualifies
-        rc = launch_expand_all_bits(p, *desc, d_act, d_weight, xnor, static_cast<uint32_t *>(b.tc),
-                                    reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p)),
-                                    b.status, st);
+        const bool no_w = d_weight == nullptr;
+        if (mode == kGridSpeculative) {
+            REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
+            rc = launch_expand_all_bits(pc, *desc, d_act, d_weight, xnor, Ab, Wb, b.status,
+                                        ExpandAllOptions{true, false, no_w}, st);
+            if (rc == REXSC_OK) // the standard planes, if the border turned out not to be zero
+                rc = launch_expand_all_bits(p, *desc, d_act, d_weight, xnor, Ab, Wb, b.status,
+                                            ExpandAllOptions{false, true, true}, st);
+        } else {
+            rc = launch_expand_all_bits(pa, *desc, d_act, d_weight, xnor, Ab, Wb, b.status,
+                                        ExpandAllOptions{false, false, no_w}, st);
+        }
         if (rc != REXSC_E_UNSUPPORTED) return rc;
     }
-    REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
+    if (mode == kGridSpeculative) {
+        // Separate launches write the standard planes.  Word 1 says so to the accumulate stage; a weights-only call
+        // leaves it as the last activation expand set it.
+        REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, sizeof(int), st));
+        if (d_act) REXSC_CUDA_CHECK(cudaMemsetAsync(reinterpret_cast<char *>(b.status + 1), 1, 1, st));
+    } else {
+        REXSC_CUDA_CHECK(cudaMemsetAsync(b.status, 0, 256, st));
+    }
     rc = launch_build_lut_pair(p.l, desc->bit_length, desc->gen_config, xnor, desc->prog_total_width,
                                desc->prog_load_width, desc->prog_load_wait, b.lut_a, b.lut_w, st);
     if (rc != REXSC_OK) return rc;
     if (k == REXSC_KERNEL_TENSOR) {
         // the tensor-core kernel reads channel-packed bit planes: Ab, then Wb, in the tensor region of the workspace
         if (d_act) {
-            rc = launch_expand_act_bits(p, *desc, d_act, b.lut_a, static_cast<uint32_t *>(b.tc), st);
+            rc = launch_expand_act_bits(pa, *desc, d_act, b.lut_a, Ab, st);
             if (rc != REXSC_OK) return rc;
         }
-        if (d_weight)
-            rc = launch_expand_weight_bits(p, *desc, d_weight, b.lut_w,
-                                           reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(b.tc) + conv_tc_weight_offset(p)), st);
+        if (d_weight) rc = launch_expand_weight_bits(p, *desc, d_weight, b.lut_w, Wb, st);
         return rc;
     }
     // the ALU kernels read time-packed stream words
@@ -104,14 +138,28 @@ static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const 
 static int conv_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, int16_t *d_out_neg,
                            void *d_workspace, size_t workspace_bytes, cudaStream_t st)
 {
-    ConvPlan p;
+    ConvPlan p, pc;
     ConvBuffers b;
     int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
     if (rc != REXSC_OK) return rc;
     if (!d_out_pos || !d_out_neg) return REXSC_E_BAD_ARG;
     const int k = resolve_kernel(desc, p);
     if (k < 0) return k;
-    if (k == REXSC_KERNEL_TENSOR) return launch_conv_tc(p, *desc, b.tc, d_out_pos, d_out_neg, b.status, st);
+    if (k == REXSC_KERNEL_TENSOR) {
+        const size_t w_off = conv_tc_weight_offset(p);
+        const int mode = grid_mode(desc, p, k, &pc);
+        if (mode == kGridStandard) return launch_conv_tc(p, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, 0, true, st);
+        if (mode == kGridCompact) return launch_conv_tc(pc, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, 0, true, st);
+        // one launch per possible verdict of the expand stage; the outputs are cleared once if either adds into them
+        if (conv_tc_splits(pc, *desc, d_out_pos, d_out_neg) || conv_tc_splits(p, *desc, d_out_pos, d_out_neg)) {
+            const size_t out_bytes = (size_t)p.M * p.Co * sizeof(int16_t);
+            REXSC_CUDA_CHECK(cudaMemsetAsync(d_out_pos, 0, out_bytes, st));
+            REXSC_CUDA_CHECK(cudaMemsetAsync(d_out_neg, 0, out_bytes, st));
+        }
+        rc = launch_conv_tc(pc, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, +1, false, st);
+        if (rc != REXSC_OK) return rc;
+        return launch_conv_tc(p, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, -1, false, st);
+    }
     if (k == REXSC_KERNEL_TILED)
         return launch_conv_tiled(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, b.status, st);
     return launch_conv_direct(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, st);

@@ -62,6 +62,8 @@ struct ConvPlan {
     //   col'  = (w % sw) * Wq + w / sw       kept iff w % sw < nrw = min(sw, KW),  Wq = ceil(Wp / sw)
     //   P     = (n * Hrows + row') * Wrow + col',   Hrows = ceil(Hp / sh) * nrh,  Wrow = Wq * nrw
     int nrh, nrw, Wq, Hrows, Wrow;
+    int origin;           // 0: stored pixel (row', col') as above.  1: compact grid of 3x3 stride-1 layers whose border
+                          // pixels are zero (see make_compact_plan): stored pixel (r, c) = padded pixel (r + 1, c + 1)
     int max_tap;          // largest tap offset (see tap_offset)
     long long NHW;        // N * Hrows * Wrow
     long long NHWp;       // plane stride of the activation words (multiple of 4)
@@ -78,6 +80,17 @@ struct ConvPlan {
 };
 
 int make_conv_plan(const rexsc_sc_conv_desc *d, ConvPlan *p);
+
+// Compact activation grid for the tensor-core path of 3x3 stride-1 layers whose zero border is one pixel wide (what
+// padding 1 produces).  The standard grid stores every padded pixel, Hp x Wp per image, and the tensor-core kernel
+// computes one candidate row per stored pixel; (Hp*Wp - OH*OW) / (Hp*Wp) of them are no output pixel (40 % on 7x7
+// maps).  If all four border rows / columns are zero, one zero column can serve as the right border of a row AND the
+// left border of the next row, and one zero row as the bottom border of an image AND the top border of the next:
+// per image (OH + 1) x (OW + 1) stored pixels and candidates, stored pixel (r, c) = padded pixel (r + 1, c + 1), output
+// (i, j) centred on stored pixel (i, j), tap (kh, kw) at flat offset (kh - 1) * (OW + 1) + (kw - 1).  Zero pixels have
+// all-zero streams whatever their seed, so sharing them changes no count.  Returns false when the layer does not
+// qualify; *pc is then untouched.
+bool make_compact_plan(const ConvPlan &p, ConvPlan *pc);
 
 // Word offset of filter tap (kh, kw) relative to the word of tap (0, 0) of the same output pixel.
 __host__ __device__ __forceinline__ int tap_offset(int kh, int kw, int sh, int sw, int nrh, int Wrow, int Wq)
@@ -131,10 +144,20 @@ int launch_expand_weight_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, co
 size_t conv_tc_weight_offset(const ConvPlan &p);
 // stream tables + weight bit planes + activation bit planes + status clear in one launch (sc_stream.cu);
 // REXSC_E_UNSUPPORTED when the shape does not qualify and the separate launches have to be used
+// opt.verify_border: check that every border pixel of the padded activation quantises to zero and set d_status[1]
+//   otherwise (the caller clears the status block before the launch; the kernel then leaves it alone);
+// opt.gate: run only if d_status[1] != 0 (the fallback launch after a failed verification);
+// opt.skip_weights: activations only.
+struct ExpandAllOptions { bool verify_border, gate, skip_weights; };
 int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const void *d_w, int xnor,
-                           uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, cudaStream_t st);
-int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,
-                   int *d_status, cudaStream_t st);
+                           uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, const ExpandAllOptions &opt, cudaStream_t st);
+// gate: 0 = run always; +1 = run only if d_status[1] == 0 (compact planes valid); -1 = only if d_status[1] != 0.
+// weight_offset: byte offset of the weight bit planes in d_tc_ws (that of the standard plan, whatever grid p has).
+// zero_outputs: clear the outputs when the tiles add into them (false when the caller already did).
+int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, size_t weight_offset, int16_t *d_pos,
+                   int16_t *d_neg, int *d_status, int gate, bool zero_outputs, cudaStream_t st);
+// true when the kernel would add partial sums into zeroed outputs for this plan
+bool conv_tc_splits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const int16_t *d_pos, const int16_t *d_neg);
 
 // ---- device helpers -----------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float load_as_float(const T *p, long long i);

@@ -54,6 +54,8 @@ struct TcArgs {
     int CK;          // pipeline steps per slot = ceil(CW / KWc)
     int nrh, nrw, Wq, Hrows, Wrow; // stored pixel grid (see tap_offset in common.cuh)
     int Ho, Wo;      // origin grid of one image
+    int shift;       // candidates by which the patch starts BEFORE the tile's first candidate: 0, or Wo + 1 on the
+                     // compact grid (ConvPlan::origin), whose candidates are the CENTRE taps of their output pixels
     int Mh;          // patch rows per residue plane: kTcM + largest in-plane tap shift, rounded up to 8
     int rows_a;      // patch rows of all planes
     int slots, n_or;
@@ -150,9 +152,13 @@ __device__ __forceinline__ void spread32(uint32_t h, uint4 &lo16, uint4 &hi16)
 template <int KHW_T, int KWC, int RA, bool SPLIT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__restrict__ Wb,
-                  int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status)
+                  int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status, int gate)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    // One of a pair of launches, of which the expand stage's verdict on the activation borders (status word 1: 0 =
+    // the compact planes are valid) picks one: +1 runs on valid compact planes only, -1 on the standard planes that
+    // replaced them.  The whole grid takes the same branch, before any barrier or tensor memory exists.
+    if (gate != 0 && (gate > 0) == (status[1] != 0)) return;
     uint8_t *smem = smem_raw + ((128u - (saddr(smem_raw) & 127u)) & 127u);
     const int KHW = KHW_T ? KHW_T : a.KHW;
     const uint32_t a_bytes = 2u * (uint32_t)KWC * (uint32_t)a.rows_a * 16u; // [2*KWc columns][rows_a][16]
@@ -256,7 +262,9 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             a_off[r] = ~0u;
             if (g < a.rows_a) {
                 const int plane = g / a.Mh, q = g - plane * a.Mh;
-                const uint32_t o = (uint32_t)o0 + (uint32_t)q; // candidate indices fit 31 bits (checked on the host)
+                // candidate indices fit 31 bits (checked on the host); rows before the first stored pixel wrap around
+                // to large values and are zero like the rows behind the last one
+                const uint32_t o = (uint32_t)o0 + (uint32_t)q - (uint32_t)a.shift;
                 if (o < (uint32_t)a.total_o) {
                     const uint32_t t = o / (uint32_t)a.Wo, j = o - t * (uint32_t)a.Wo;
                     const uint32_t n = t / (uint32_t)a.Ho, i = t - n * (uint32_t)a.Ho;
@@ -682,32 +690,19 @@ size_t conv_tc_weight_offset(const ConvPlan &p)
     return align_up((size_t)p.words * 32 * CW * p.NHWp * 4, 256);
 }
 
-int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, int16_t *d_pos, int16_t *d_neg,
-                   int *d_status, cudaStream_t st)
+// share of the time slots per tile (TcArgs::split) for a plan on a device with `sms` SMs
+static int tc_split(const ConvPlan &p, const rexsc_sc_conv_desc &d, const TcGeom &g, const int16_t *d_pos,
+                    const int16_t *d_neg, int sms)
 {
-    if (!conv_tc_supported(p)) return REXSC_E_UNSUPPORTED;
-    const TcGeom g = tc_geometry(p);
-    const int CW = g.CW, NC = (p.Co + kTcCout - 1) / kTcCout;
+    const int NC = (p.Co + kTcCout - 1) / kTcCout;
     const int slots = p.words * 32;
-    const uint32_t *Ab = static_cast<const uint32_t *>(d_tc_ws);
-    const uint32_t *Wb = reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(d_tc_ws) +
-                                                            align_up((size_t)slots * CW * p.NHWp * 4, 256));
-    TcArgs a;
-    a.OH = p.OH; a.OW = p.OW; a.KHW = p.KHW; a.Co = p.Co;
-    a.CW = CW; a.KWc = g.KWc; a.CK = g.CK;
-    a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
-    a.Ho = g.Ho; a.Wo = g.Wo; a.Mh = g.Mh; a.rows_a = g.rows_a;
-    a.slots = slots;
-    a.total_o = (long long)p.N * g.Ho * g.Wo;
-    a.tiles_x = (int)((a.total_o + kTcM - 1) / kTcM);
-    int dev = 0, sms = 0;
-    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
-    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const long long total_o = (long long)p.N * g.Ho * g.Wo;
+    const int tiles_x = (int)((total_o + kTcM - 1) / kTcM);
     // Few tiles per SM: the last wave of whole tiles leaves SMs idle.  Half-length tiles (each half of the time slots,
     // summed with atomics) waste less when that saves more than the extra prologues cost.
-    a.split = 1;
+    int split = 1;
     {
-        const long long tiles = (long long)a.tiles_x * NC;
+        const long long tiles = (long long)tiles_x * NC;
         const double whole = (double)((tiles + sms - 1) / sms), halves = (double)((2 * tiles + sms - 1) / sms) / 2.0;
         // packed 32-bit atomic adds need 4-byte aligned rows: an int16 view at an odd element offset takes whole tiles
         const bool aligned4 = ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 3u) == 0;
@@ -718,16 +713,55 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
         // and the atomic adds cost about as much as they save once the outputs are tens of MB (measured at 28x28)
         const bool small_out = (size_t)p.M * p.Co * sizeof(int16_t) <= (size_t)16 << 20;
         if (rows_ok && long_tiles(2) && small_out && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL)
-            a.split = 2;
+            split = 2;
         // Grids that leave most SMs idle even then (a linear layer: a handful of tiles, long streams): keep halving the
         // share of the time slots per tile while every tile still finds an SM of its own
         if (rows_ok && small_out)
-            while (a.split < 16 && slots % (2 * a.split) == 0 && long_tiles(2 * a.split) && tiles * 2 * a.split <= sms)
-                a.split *= 2;
+            while (split < 16 && slots % (2 * split) == 0 && long_tiles(2 * split) && tiles * 2 * split <= sms)
+                split *= 2;
     }
+    return split;
+}
+
+static int device_sms(int *sms)
+{
+    int dev = 0;
+    REXSC_CUDA_CHECK(cudaGetDevice(&dev));
+    REXSC_CUDA_CHECK(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+    return REXSC_OK;
+}
+
+bool conv_tc_splits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const int16_t *d_pos, const int16_t *d_neg)
+{
+    int sms = 0;
+    if (!conv_tc_supported(p) || device_sms(&sms) != REXSC_OK) return false;
+    return tc_split(p, d, tc_geometry(p), d_pos, d_neg, sms) > 1;
+}
+
+int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, size_t weight_offset, int16_t *d_pos,
+                   int16_t *d_neg, int *d_status, int gate, bool zero_outputs, cudaStream_t st)
+{
+    if (!conv_tc_supported(p)) return REXSC_E_UNSUPPORTED;
+    const TcGeom g = tc_geometry(p);
+    const int CW = g.CW, NC = (p.Co + kTcCout - 1) / kTcCout;
+    const int slots = p.words * 32;
+    const uint32_t *Ab = static_cast<const uint32_t *>(d_tc_ws);
+    const uint32_t *Wb = reinterpret_cast<const uint32_t *>(static_cast<const uint8_t *>(d_tc_ws) + weight_offset);
+    TcArgs a;
+    a.OH = p.OH; a.OW = p.OW; a.KHW = p.KHW; a.Co = p.Co;
+    a.CW = CW; a.KWc = g.KWc; a.CK = g.CK;
+    a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.Ho = g.Ho; a.Wo = g.Wo; a.Mh = g.Mh; a.rows_a = g.rows_a;
+    a.shift = p.origin ? g.Wo + 1 : 0;
+    a.slots = slots;
+    a.total_o = (long long)p.N * g.Ho * g.Wo;
+    a.tiles_x = (int)((a.total_o + kTcM - 1) / kTcM);
+    int sms = 0;
+    if (int rc = device_sms(&sms)) return rc;
+    a.split = tc_split(p, d, g, d_pos, d_neg, sms);
     a.slots_part = slots / a.split;
     a.total_tiles = a.tiles_x * NC * a.split;
-    if (a.split > 1) {
+    if (a.split > 1 && zero_outputs) {
         const size_t out_bytes = (size_t)p.M * p.Co * sizeof(int16_t);
         REXSC_CUDA_CHECK(cudaMemsetAsync(d_pos, 0, out_bytes, st));
         REXSC_CUDA_CHECK(cudaMemsetAsync(d_neg, 0, out_bytes, st));
@@ -754,7 +788,7 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     auto kernel = p.KHW == 9 ? pick(std::integral_constant<int, 9>{})
                 : p.KHW == 1 ? pick(std::integral_constant<int, 1>{}) : pick(std::integral_constant<int, 0>{});
     REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
-    kernel<<<grid, kTcThreads, g.smem, st>>>(a, Ab, Wb, d_pos, d_neg, d_status);
+    kernel<<<grid, kTcThreads, g.smem, st>>>(a, Ab, Wb, d_pos, d_neg, d_status, gate);
     REXSC_LAUNCH_CHECK("sc_conv_tc_kernel");
     return REXSC_OK;
 }

@@ -185,6 +185,7 @@ static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
     if (p->Hp < p->KH || p->Wp < p->KW) return REXSC_E_BAD_ARG;
     p->OH = (p->Hp - p->KH) / p->sh + 1;
     p->OW = (p->Wp - p->KW) / p->sw + 1;
+    p->origin = 0;
     p->nrh = p->sh < p->KH ? p->sh : p->KH;
     p->nrw = p->sw < p->KW ? p->sw : p->KW;
     p->Wq = (p->Wp + p->sw - 1) / p->sw;
@@ -270,12 +271,33 @@ static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
     return REXSC_OK;
 }
 
+bool make_compact_plan(const ConvPlan &p, ConvPlan *pc)
+{
+    if (!p.tc_ok || p.sh != 1 || p.sw != 1 || p.KH != 3 || p.KW != 3 || p.OH < 1 || p.OW < 1) return false;
+    // the comparator works on int8: with 8-bit registers states above 127 read as negative and a zero VALUE still
+    // produces ones, so a zero pixel's stream depends on its seed
+    if (p.l > 7) return false;
+    ConvPlan c = p;
+    c.origin = 1;
+    c.Hrows = p.OH + 1;
+    c.Wq = p.OW + 1;
+    c.Wrow = c.Wq; // no pitch padding: the flat stored index is the candidate index
+    c.NHW = (long long)p.N * c.Hrows * c.Wrow;
+    c.NHWp = (c.NHW + 3) / 4 * 4;
+    c.a_plane_words = (long long)c.Cpad * c.NHWp;
+    c.tc_ok = conv_tc_supported(c);
+    if (!c.tc_ok || c.NHWp > p.NHWp) return false; // its planes live in the standard plan's region
+    *pc = c;
+    return true;
+}
+
 // ---- activation expansion -------------------------------------------------------------------
 // Seed index of an activation element: c*Hp*Wp + h*Wp + w on the PADDED tensor, offset 0
 // (torch_c/sc-extension/sc_cuda_conv.cu:133,139); linear: c only (sc_cuda_matmul.cu:177).
 struct ExpandActArgs {
     int N, C, H, W, Hp, Wp, ph, pw, Cpad;
     int sh, sw, nrh, nrw, Wq, Hrows, Wrow;
+    int origin;         // stored pixel (row', col') is padded pixel (h + origin, w + origin) of the mapping below
     uint32_t plane_mod; // (Hp * Wp) mod period
     long long NHW, NHWp, a_plane_words;
     int period, nvals, words, linear_seeds;
@@ -290,8 +312,8 @@ __device__ __forceinline__ bool decode_pixel(const ExpandActArgs &a, long long P
     const uint32_t t = P / (uint32_t)a.Wrow;
     const int row = (int)(t % (uint32_t)a.Hrows);
     n = (int)(t / (uint32_t)a.Hrows);
-    h = (row / a.nrh) * a.sh + row % a.nrh;
-    w = (col % a.Wq) * a.sw + col / a.Wq;
+    h = (row / a.nrh) * a.sh + row % a.nrh + a.origin;
+    w = (col % a.Wq) * a.sw + col / a.Wq + a.origin;
     return col < a.Wq * a.nrw && h < a.Hp && w < a.Wp; // pitch padding holds no pixel
 }
 
@@ -376,7 +398,7 @@ int launch_expand_act(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void
     ExpandActArgs a;
     a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
     a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
-    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow; a.origin = p.origin;
     a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.scale = (float)p.scale;
@@ -1046,7 +1068,10 @@ struct ExpandAllArgs {
     LutParams lut;
     int w_dtype;
     int w_coarse;      // weight items are blocks of 32 output channels (else single output channels)
-    long long w_items;
+    long long w_items; // 0: activations only
+    int verify_border; // check that the border pixels of the padded activation quantise to zero; status[1] = 1 otherwise
+    int gate;          // run only if status[1] != 0
+    int verify_vec;    // the border check may use 16-byte loads and 32-bit indices
 };
 
 __device__ __forceinline__ float load_weight_any(const void *w, int dtype, long long i)
@@ -1065,7 +1090,56 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
     extern __shared__ __align__(16) uint32_t lut_s[];
     __shared__ uint8_t cyc_s[128], pos_s[128]; // the LFSR cycle and the position of every state in it
     const ExpandActArgs &a = g.act;
-    if (blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0; // the device status block of the workspace
+    if (g.gate && status[1] == 0) return; // fallback launch: the compact planes were valid, nothing to redo
+    // the device status block of the workspace (when borders are verified the caller has cleared it: word 1 is being set)
+    if (!g.verify_border && !g.gate && blockIdx.x == 0 && threadIdx.x < 64) status[threadIdx.x] = 0;
+    if (g.verify_border) {
+        // Every border pixel of the padded tensor (rows 0 and Hp-1, columns 0 and Wp-1) must quantise to zero, i.e. be
+        // <= 0 (or NaN): the compact grid shares one zero row / column between neighbouring rows / images.
+        const uint32_t per_img = 2u * (uint32_t)a.Wp + 2u * (uint32_t)(a.Hp - 2);
+        auto border_pixel = [&](uint32_t b, int &hi, int &wi) { // b-th border pixel of an image -> input coordinates
+            int h, w;
+            if (b < (uint32_t)a.Wp) { h = 0; w = (int)b; }
+            else if (b < 2u * (uint32_t)a.Wp) { h = a.Hp - 1; w = (int)b - a.Wp; }
+            else { const int k = (int)b - 2 * a.Wp; h = 1 + (k >> 1); w = (k & 1) ? a.Wp - 1 : 0; }
+            hi = h - a.ph; wi = w - a.pw;
+            return hi >= 0 && hi < a.H && wi >= 0 && wi < a.W;
+        };
+        bool bad = false;
+        constexpr int E = 16 / (int)sizeof(T);
+        if (!NCHW && g.verify_vec) {
+            // channels_last: 16 bytes of one pixel per load (32-bit index arithmetic, checked on the host)
+            const uint32_t vecs = (uint32_t)a.C / E, total = (uint32_t)a.N * per_img * vecs;
+#pragma unroll 4
+            for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+                const uint32_t t = idx / vecs, v = idx - t * vecs, n = t / per_img, b = t - n * per_img;
+                int hi, wi;
+                if (border_pixel(b, hi, wi)) {
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(
+                        x + (((size_t)n * a.H + hi) * a.W + wi) * a.C + (size_t)v * E));
+                    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+                    for (int i = 0; i < E; i++) bad |= load_as_float<T>(e, i) > 0.f;
+                }
+            }
+        } else {
+            const long long total = (long long)a.N * per_img * a.C;
+            for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+                 idx += (long long)gridDim.x * blockDim.x) {
+                // channel-planar: consecutive threads walk the border pixels of one channel
+                const uint32_t b = (uint32_t)(idx % per_img);
+                const long long t = idx / per_img;
+                const int c = (int)(t % a.C), n = (int)(t / a.C);
+                int hi, wi;
+                if (border_pixel(b, hi, wi)) {
+                    const long long xi = NCHW ? (((long long)n * a.C + c) * a.H + hi) * a.W + wi
+                                              : (((long long)n * a.H + hi) * a.W + wi) * a.C + c;
+                    bad |= load_as_float<T>(x, xi) > 0.f;
+                }
+            }
+        }
+        if (bad) atomicExch(status + 1, 1);
+    }
     build_doubled_table<WORDS>(g.lut, a.period, a.nvals, lut_s, cyc_s, pos_s);
     // ---- weights: one warp per (block of 32 output channels, tap, channel word); lane = input channel of the word ----
     // For every output channel of the block the warp looks the 32 channels' stream words up and transposes them across
@@ -1185,7 +1259,7 @@ static int launch_expand_all_t(const ExpandAllArgs &g, const void *d_act, const 
 // caller then uses the separate launches): channels_last activations with 16-byte aligned channel runs, at most two
 // words per stream, tables that fit shared memory.
 int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const void *d_act, const void *d_w, int xnor,
-                           uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, cudaStream_t st)
+                           uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, const ExpandAllOptions &opt, cudaStream_t st)
 {
     if ((p.words != 1 && p.words != 2) || p.NHWp >= (1LL << 31)) return REXSC_E_UNSUPPORTED;
     const int esz = d.act_dtype == REXSC_F32 ? 4 : 2;
@@ -1205,7 +1279,7 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     ExpandActArgs &a = g.act;
     a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
     a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
-    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow; a.origin = p.origin;
     a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.scale = (float)p.scale;
@@ -1219,6 +1293,10 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     g.w_items = (long long)w.NC * 2 * w.KHW * w.CW; // blocks of 32 output channels x taps x channel words
     g.w_coarse = g.w_items >= 2048 ? 1 : 0;           // enough of them to occupy the grid's warps
     if (!g.w_coarse) g.w_items *= 32;                 // single output channels
+    if (opt.skip_weights) g.w_items = 0;
+    g.verify_border = opt.verify_border ? 1 : 0;
+    g.gate = opt.gate ? 1 : 0;
+    g.verify_vec = (!nchw && (long long)p.N * (2LL * p.Wp + 2LL * p.Hp) * p.C < (1LL << 31)) ? 1 : 0;
     const int CW = w.CW;
 #define REXSC_ALL(T) (p.words == 1 ? launch_expand_all_t<T, 1, false>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)   \
                                    : launch_expand_all_t<T, 2, false>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st))
@@ -1286,7 +1364,7 @@ int launch_expand_act_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     ExpandActArgs a;
     a.N = p.N; a.C = p.C; a.H = p.H; a.W = p.W; a.Hp = p.Hp; a.Wp = p.Wp; a.ph = p.ph; a.pw = p.pw;
     a.Cpad = p.Cpad; a.NHW = p.NHW; a.NHWp = p.NHWp; a.a_plane_words = p.a_plane_words;
-    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow;
+    a.sh = p.sh; a.sw = p.sw; a.nrh = p.nrh; a.nrw = p.nrw; a.Wq = p.Wq; a.Hrows = p.Hrows; a.Wrow = p.Wrow; a.origin = p.origin;
     a.plane_mod = (uint32_t)(((long long)p.Hp * p.Wp) % p.period);
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.scale = (float)p.scale;

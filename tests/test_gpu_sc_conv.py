@@ -337,6 +337,76 @@ def test_tensor_kernel_variants_vs_direct(ops, case):
     assert torch.equal(plain[0], plain_ref[0]) and torch.equal(plain[1], plain_ref[1]), f"{case} plain count"
 
 
+COMPACT_CASES = [
+    # N, Cin, H, W, Cout, L, or_n, channels_last, dtype -- 3x3 stride-1 layers of the tensor-core kernel, whose
+    # activation grid drops the shared zero border (one row and one column per image instead of two)
+    (6, 64, 7, 7, 64, 32, 2, True, torch.float32),      # few tiles: time slots split over CTAs, atomically added
+    (37, 64, 7, 9, 128, 32, 2, True, torch.float16),    # tiles span images; half-precision staging
+    (3, 96, 14, 14, 70, 64, 3, True, torch.float32),    # two word planes, ragged output channels
+    (5, 64, 8, 8, 64, 32, 1, False, torch.float32),     # NCHW fp32: single-launch expand with 4-byte staging
+    (5, 40, 8, 6, 64, 32, 2, False, torch.float16),     # NCHW fp16: separate expand launches
+    (300, 32, 4, 4, 64, 32, 2, True, torch.float32),    # more tiles than SMs
+]
+
+
+@pytest.mark.parametrize("case", COMPACT_CASES)
+def test_compact_grid_of_3x3_layers(ops, case):
+    """The same layer three ways through the tensor-core kernel, each against the direct kernel (pinned to the oracle
+    above): padding done by the op (compact grid by construction), padding done by the caller as the reference's
+    front end does (border checked on the device, compact grid), and caller-padded data whose border is NOT zero in
+    one place (the check fails, the standard grid is used)."""
+    N, Cin, H, W, Cout, L, or_n, cl, dtype = case
+    x, w = conv_inputs(N, Cin, H, W, Cout, 3, prec=7, seed=sum(case[:7]))
+    fmt = torch.channels_last if cl else torch.contiguous_format
+    x = x.to(dtype).contiguous(memory_format=fmt)
+    w = w.to(dtype).contiguous(memory_format=fmt)
+    ref = run_ours(ops, x, w, L, 1, 1, or_n, True, "direct")
+    got = run_ours(ops, x, w, L, 1, 1, or_n, True, "tensor")
+    assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), f"{case}: op-padded"
+
+    xp = torch.nn.functional.pad(x, (1, 1, 1, 1)).contiguous(memory_format=fmt)
+    got = run_ours(ops, xp, w, L, 0, 1, or_n, True, "tensor")
+    assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), f"{case}: caller-padded"
+    # values that quantise to zero are as good as zeros
+    xn = xp.clone()
+    xn[:, :, 0, :] = -0.5
+    xn[:, :, :, -1] = float("nan")
+    got = run_ours(ops, xn, w, L, 0, 1, or_n, True, "tensor")
+    assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), f"{case}: negative / NaN border"
+
+    for where in ((N - 1, Cin - 1, H + 1, W + 1), (0, 0, 0, 3), (N // 2, 1, 2, 0)):
+        xb = xp.clone()
+        xb[where] = 0.75
+        ref_b = run_ours(ops, xb, w, L, 0, 1, or_n, True, "direct")
+        got = run_ours(ops, xb, w, L, 0, 1, or_n, True, "tensor")
+        assert torch.equal(got[0], ref_b[0]) and torch.equal(got[1], ref_b[1]), f"{case}: live border at {where}"
+    # and the next call on a clean border takes the compact grid again
+    got = run_ours(ops, xp, w, L, 0, 1, or_n, True, "tensor")
+    assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1]), f"{case}: caller-padded, after a fallback"
+
+
+def test_compact_grid_with_prepared_weights(ops):
+    """Weights expanded once, caller-padded activations per call (their border decides the grid on every call)."""
+    g = torch.Generator().manual_seed(11)
+    w = (torch.randn(64, 64, 3, 3, generator=g) * 0.1).clamp(-1, 1).cuda().contiguous(memory_format=torch.channels_last)
+    args = (32, -1, (0, 0), (1, 1), PROG, 1, 1, True)
+    xs = []
+    for i in range(4):
+        x = torch.nn.functional.pad(torch.rand(9, 64, 7, 7, generator=g), (1, 1, 1, 1))
+        if i % 2:
+            x[3, 5, 8, 2] = 0.5
+        xs.append(x.cuda().contiguous(memory_format=torch.channels_last))
+    conv = ops.PreparedConv(w, xs[0].shape, xs[0].dtype, True, *args)
+    for x in xs:
+        pos, neg = conv(x)
+        ops.set_conv_kernel("direct")
+        try:
+            rpos, rneg = ops.conv2d_generic_general_split_acc(x, w, 32, -1, 16, (0, 0), (1, 1), PROG, 1, 1, True, False)
+        finally:
+            ops.set_conv_kernel("auto")
+        assert torch.equal(pos, rpos) and torch.equal(neg, rneg)
+
+
 def test_auto_kernel_choice(ops):
     """AUTO resolves to the tensor-core kernel for every layer shape of the bench workload that has >= 32 input
     channels and at most 9 taps, and to an ALU kernel for thin inputs and large filters."""
