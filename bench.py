@@ -264,24 +264,19 @@ def run_sc(args, wl, rank, world, local_rank):
         l["w"] = l["w_host"].to(dev).contiguous(memory_format=fmt)
         l["x_pin16"] = l["x_host"].half().contiguous(memory_format=fmt).pin_memory()
         l["x_pin32"] = l["x_host"].pin_memory()
-    launches = {"n": 0}
-    for l in layers:
-        # kernels per conv call: expand + accumulate where the single-launch expand stage applies (tensor-core path,
-        # streams of at most 64 bits, fp32 NCHW or channels_last with 16-byte aligned channel runs); else stream
-        # tables, activation expansion, weight expansion, accumulate
-        d = _sc_desc(_lib, l, wl, l["x"], l["w"])
-        tensor = lib.rexsc_sc_conv2d_kernel_choice(C.byref(d)) == 3
-        l["kernels"] = 2 if (tensor and l["L"] <= 64 and (not wl["channels_last"] or l["shape"][0] % 8 == 0)) else 4
-
     def conv(l, x):
-        launches["n"] += l["kernels"]
         return ops.conv2d_generic_general_split_acc(x, l["w"], l["L"], -1, 16, (0, 0), (l["stride"],) * 2, PROG,
                                                     or_n - 1, 1, True, False)
 
     # float guide sums for the point-wise kernels: synthetic conv sums of the right shape (dtype as the front end has)
     guides = {}
     for i, l in enumerate(layers):
+        # kernels per conv call, counted by the library: the single-launch expand stage and the tensor-core kernel,
+        # plus -- for 3x3 stride-1 layers, whose padding the caller did -- the gated fallback pair and the clearing of
+        # the tiles that CTAs share; four or more on the ALU paths (tables, two expansions, accumulate)
+        c0 = lib.rexsc_kernel_launch_count()
         p, n = conv(l, l["x"])
+        l["kernels"] = lib.rexsc_kernel_launch_count() - c0
         g = torch.Generator(device=dev).manual_seed(7 + i)
         guides[i] = (torch.rand(p.shape, device=dev, generator=g, dtype=torch.float32).to(wl["guide_dtype"])
                      .contiguous(memory_format=fmt) * 4)
@@ -292,7 +287,6 @@ def run_sc(args, wl, rank, world, local_rank):
                 conv(l, l["x"])
                 ops.or_approx_n_forward_acc(guides[i], or_n)
                 ops.or_approx_n_forward_acc(guides[i], or_n)
-                launches["n"] += 2
 
     # host-facing step: every call takes pinned host tensors and returns host tensors
     out_pin = {}
@@ -322,9 +316,10 @@ def run_sc(args, wl, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    launches["n"] = 0
+    c0 = lib.rexsc_kernel_launch_count()
     ms = _timed_steps(step_resident, args.steps, args.warmup, world, dev, sharding)
-    n_launch = launches["n"] * args.steps // (args.steps + args.warmup)
+    # this library's kernels inside the timed region, as the library counted them (warm-up steps taken out)
+    n_launch = (lib.rexsc_kernel_launch_count() - c0) * args.steps // (args.steps + args.warmup)
     clocks = sampler.stop() if rank == 0 else None
     e2e_steps = max(1, min(args.steps, 5))
     step16, h2d16 = host_step("x_pin16")
@@ -541,7 +536,7 @@ def sc_line(args, wl, r, world):
 
 # ---- SC linear -------------------------------------------------------------------------------------------------
 def run_linear(args, wl, rank, world, local_rank):
-    from rexsc_b200 import ops, sharding
+    from rexsc_b200 import _lib, ops, sharding
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -560,7 +555,9 @@ def run_linear(args, wl, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    c0 = _lib.load().rexsc_kernel_launch_count()
     ms = _timed_steps(step, args.steps, args.warmup, world, dev, sharding)
+    n_launch = (_lib.load().rexsc_kernel_launch_count() - c0) * args.steps // (args.steps + args.warmup)
     clocks = sampler.stop() if rank == 0 else None
     pins = [(x.cpu().pin_memory(), w, L) for x, w, L in data]
 
@@ -575,7 +572,7 @@ def run_linear(args, wl, rank, world, local_rank):
     e2e_steps = max(1, min(args.steps, 5))
     ms_e2e = _timed_steps(step_host, e2e_steps, 1, world, dev, sharding)
     bitops = sum(2 * L * B * cin * cout for cin, cout, L in wl["layers"])
-    return {"ms": ms, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "clocks": clocks, "bitops": bitops,
+    return {"ms": ms, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "clocks": clocks, "bitops": bitops, "launches": n_launch,
             "h2d": sum(x.numel() * 4 for x, _, _ in data), "d2h": sum(2 * 2 * B * cout for _, cout, _ in wl["layers"])}
 
 
@@ -591,8 +588,8 @@ def linear_line(args, wl, r, world):
         "tbitops_per_s": r["bitops"] * world * args.steps / (r["ms"] * 1e-3) / 1e12,
         "e2e": {"value": B * world * r["e2e_steps"] / (r["ms_e2e"] * 1e-3), "unit": "rows/s",
                 "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
-        "gpu_launches": 4 * len(wl["layers"]) * args.steps, "clocks": r["clocks"],
-        "roofline": {"bound": "latency", "kernel": "SC linear = SC conv with 1x1 geometry (4 launches per layer)",
+        "gpu_launches": r["launches"], "clocks": r["clocks"],
+        "roofline": {"bound": "latency", "kernel": "SC linear = SC conv with 1x1 geometry",
                      "achieved": r["ms"] / args.steps / len(wl["layers"]) * 1e3, "unit": "us per layer call",
                      "peak": None, "frac": None, "traffic": None},
     }
@@ -600,7 +597,7 @@ def linear_line(args, wl, r, world):
 
 # ---- FXP conv ---------------------------------------------------------------------------------------------------
 def run_fxp(args, wl, rank, world, local_rank):
-    from rexsc_b200 import ops, sharding
+    from rexsc_b200 import _lib, ops, sharding
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -619,7 +616,9 @@ def run_fxp(args, wl, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    c0 = _lib.load().rexsc_kernel_launch_count()
     ms = _timed_steps(step, args.steps, args.warmup, world, dev, sharding)
+    n_launch = (_lib.load().rexsc_kernel_launch_count() - c0) * args.steps // (args.steps + args.warmup)
     clocks = sampler.stop() if rank == 0 else None
     pins = [(x.cpu().pin_memory(), w, p, pin) for x, w, p, pin in data]
 
@@ -638,7 +637,7 @@ def run_fxp(args, wl, rank, world, local_rank):
         total_ops += intops
         per_layer.append({"shape": [cin, h, cout, k, p, pin], "ms": round(t, 4), "int8_tops": round(intops / t / 1e9, 1)})
     return {"ms": ms, "ms_e2e": ms_e2e, "e2e_steps": e2e_steps, "clocks": clocks, "per_layer": per_layer,
-            "intops": total_ops, "mma_peak_ops": _mma_peak(ops, dev), "h2d": sum(x.numel() * 4 for x, _, _, _ in data),
+            "launches": n_launch, "intops": total_ops, "mma_peak_ops": _mma_peak(ops, dev), "h2d": sum(x.numel() * 4 for x, _, _, _ in data),
             "d2h": sum(4 * B * cout * (h + 2 * p - k + 1) ** 2 for cin, h, cout, k, p, pin in wl["layers"])}
 
 
@@ -655,7 +654,7 @@ def fxp_line(args, wl, r, world):
                    "l2_policy": "working set (< 40 MB) fits L2: small-layer workload, reported as such"},
         "e2e": {"value": B * world * r["e2e_steps"] / (r["ms_e2e"] * 1e-3), "unit": "img/s",
                 "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
-        "gpu_launches": 2 * len(wl["layers"]) * args.steps, "clocks": r["clocks"],
+        "gpu_launches": r["launches"], "clocks": r["clocks"],
         "roofline": {"bound": "tensor", "kernel": "fxp_conv_umma_kernel (tcgen05 int8 closed form) + operand packing",
                      "achieved": achieved / 1e12, "peak": r["mma_peak_ops"] / 1e12, "unit": "TOP/s int8",
                      "frac": achieved / r["mma_peak_ops"], "traffic": None, "kernel_ms_per_step": kernel_ms,

@@ -76,6 +76,9 @@ typedef struct rexsc_sc_conv_desc {
 int rexsc_abi_version(void);
 /* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
 const char *rexsc_last_cuda_error(void);
+/* Kernels this library has launched in the calling process so far, on any device and stream (memsets and copies are
+ * not kernels).  The difference between two reads counts the launches of the calls in between. */
+unsigned long long rexsc_kernel_launch_count(void);
 
 /*
  * SC conv2d forward.  Replaces conv2d_generic_general_split_acc / conv2d_generic_general_acc
@@ -129,6 +132,11 @@ int rexsc_sc_conv2d_static_status(void *stream);
  * expanded streams across calls while the tensors they came from are unchanged: expand accepts a null d_act or a
  * null d_weight (not both) and then leaves that operand's part of the workspace as an earlier expand with the same
  * descriptor wrote it -- e.g. inference expands the weights of a layer once and only the activations per call.
+ * The workspace also records HOW the last activation expand laid the activations out (3x3 stride-1 layers drop the
+ * zero border from their bit planes when the border is indeed zero, which the expand stage checks on the device), so
+ * accumulate must be given the descriptor and workspace of the activation expand that precedes it on the stream.
+ * Between the kernels of one call the device decides which of two prepared launches runs; nothing synchronises
+ * with the host.
  */
 int rexsc_sc_conv2d_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight,
                            void *d_workspace, size_t workspace_bytes, void *stream);

@@ -38,6 +38,7 @@ _vp, _i32, _i64, _u64, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_s
 SYMBOLS = {
     "rexsc_abi_version": (C.c_int, []),
     "rexsc_last_cuda_error": (C.c_char_p, []),
+    "rexsc_kernel_launch_count": (C.c_ulonglong, []),
     "rexsc_sc_conv2d_workspace_size": (_sz, [C.POINTER(ScConvDesc)]),
     "rexsc_sc_conv2d_kernel_choice": (C.c_int, [C.POINTER(ScConvDesc)]),
     "rexsc_sc_conv2d_fwd": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _vp, _vp, _sz, _vp]),

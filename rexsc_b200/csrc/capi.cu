@@ -1,4 +1,5 @@
 // extern "C" entry points of the SC conv / linear forward, plus library-wide helpers.
+#include <atomic>
 #include <stdio.h>
 #include <string.h>
 
@@ -12,6 +13,10 @@ void set_cuda_error(cudaError_t e, const char *where)
 {
     snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
 }
+
+static std::atomic<unsigned long long> g_kernel_launches{0};
+
+void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
 
 struct ConvBuffers {
     int *status;
@@ -148,17 +153,12 @@ static int conv_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, i
     if (k == REXSC_KERNEL_TENSOR) {
         const size_t w_off = conv_tc_weight_offset(p);
         const int mode = grid_mode(desc, p, k, &pc);
-        if (mode == kGridStandard) return launch_conv_tc(p, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, 0, true, st);
-        if (mode == kGridCompact) return launch_conv_tc(pc, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, 0, true, st);
-        // one launch per possible verdict of the expand stage; the outputs are cleared once if either adds into them
-        if (conv_tc_splits(pc, *desc, d_out_pos, d_out_neg) || conv_tc_splits(p, *desc, d_out_pos, d_out_neg)) {
-            const size_t out_bytes = (size_t)p.M * p.Co * sizeof(int16_t);
-            REXSC_CUDA_CHECK(cudaMemsetAsync(d_out_pos, 0, out_bytes, st));
-            REXSC_CUDA_CHECK(cudaMemsetAsync(d_out_neg, 0, out_bytes, st));
-        }
-        rc = launch_conv_tc(pc, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, +1, false, st);
+        if (mode == kGridStandard) return launch_conv_tc(p, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, 0, st);
+        if (mode == kGridCompact) return launch_conv_tc(pc, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, 0, st);
+        // one launch per possible verdict of the expand stage
+        rc = launch_conv_tc(pc, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, +1, st);
         if (rc != REXSC_OK) return rc;
-        return launch_conv_tc(p, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, -1, false, st);
+        return launch_conv_tc(p, *desc, b.tc, w_off, d_out_pos, d_out_neg, b.status, -1, st);
     }
     if (k == REXSC_KERNEL_TILED)
         return launch_conv_tiled(p, *desc, b.A, b.Wt, b.S, d_out_pos, d_out_neg, b.status, st);
@@ -204,6 +204,8 @@ using namespace rexsc;
 extern "C" int rexsc_abi_version(void) { return REXSC_ABI_VERSION; }
 
 extern "C" const char *rexsc_last_cuda_error(void) { return g_cuda_error; }
+
+extern "C" unsigned long long rexsc_kernel_launch_count(void) { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 extern "C" size_t rexsc_sc_conv2d_workspace_size(const rexsc_sc_conv_desc *desc)
 {

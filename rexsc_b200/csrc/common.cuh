@@ -12,6 +12,9 @@ namespace rexsc {
 
 // ---- error plumbing -------------------------------------------------------------------------
 void set_cuda_error(cudaError_t e, const char *where);
+// every kernel launch of the library is followed by exactly one REXSC_LAUNCH_CHECK, which counts it
+// (rexsc_kernel_launch_count)
+void note_kernel_launch();
 #define REXSC_CUDA_CHECK(expr)                                  \
     do {                                                        \
         cudaError_t _e = (expr);                                \
@@ -22,6 +25,7 @@ void set_cuda_error(cudaError_t e, const char *where);
     } while (0)
 #define REXSC_LAUNCH_CHECK(what)                                \
     do {                                                        \
+        ::rexsc::note_kernel_launch();                          \
         cudaError_t _e = cudaGetLastError();                    \
         if (_e != cudaSuccess) {                                \
             ::rexsc::set_cuda_error(_e, what);                  \
@@ -153,11 +157,8 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
                            uint32_t *d_Ab, uint32_t *d_Wb, int *d_status, const ExpandAllOptions &opt, cudaStream_t st);
 // gate: 0 = run always; +1 = run only if d_status[1] == 0 (compact planes valid); -1 = only if d_status[1] != 0.
 // weight_offset: byte offset of the weight bit planes in d_tc_ws (that of the standard plan, whatever grid p has).
-// zero_outputs: clear the outputs when the tiles add into them (false when the caller already did).
 int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, size_t weight_offset, int16_t *d_pos,
-                   int16_t *d_neg, int *d_status, int gate, bool zero_outputs, cudaStream_t st);
-// true when the kernel would add partial sums into zeroed outputs for this plan
-bool conv_tc_splits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const int16_t *d_pos, const int16_t *d_neg);
+                   int16_t *d_neg, int *d_status, int gate, cudaStream_t st);
 
 // ---- device helpers -----------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float load_as_float(const T *p, long long i);

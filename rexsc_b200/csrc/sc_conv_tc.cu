@@ -29,6 +29,7 @@
 // that finished, and already hold the bit words of step i+2 in registers.
 // Every wait is bounded; on a time-out the CTA reports through the status word, frees its TMEM and returns.
 #include "common.cuh"
+#include <stdlib.h>
 #include <type_traits>
 
 namespace rexsc {
@@ -60,17 +61,49 @@ struct TcArgs {
     int rows_a;      // patch rows of all planes
     int slots, n_or;
     long long total_o; // candidates = N * Ho * Wo
-    int tiles_x;       // candidate tiles = ceil(total_o / kTcM); a CTA walks tiles blockIdx.x, + gridDim.x, ... of the
-    int total_tiles;   // tiles_x * (64-channel output chunks) * split; tile index = (part * chunks + chunk) * tiles_x + x
+    int tiles_x;       // candidate tiles = ceil(total_o / kTcM)
+    int total_tiles;   // tiles_x * (64-channel output chunks); tile index = chunk * tiles_x + x
     int out_vec;       // both output pointers are 16-byte aligned: rows may be stored as 128-bit vectors
-    int split;         // 1, or 2: a tile covers half of the time slots and adds its sums into zeroed outputs with
-                       // packed 16-bit atomics -- fills the last wave when there are few tiles per SM
-    int slots_part;    // slots / split
+    int balanced;      // 0: a CTA walks whole tiles blockIdx.x, + gridDim.x, ...
+                       // 1: the (tile, time slot) pairs, in that order, are cut into gridDim.x equal runs, one per CTA.
+                       //    A tile that two or more CTAs share is zeroed before the launch (zero_shared_tiles_kernel)
+                       //    and every sharer adds its partial sums with packed 16-bit atomics; tiles that lie inside
+                       //    one run are stored plainly.  No SM idles in a last, partly filled wave of tiles.
     long long NHWp;
     int out_nhwc;
     int descale_each; // 1: running sums would overflow 16 bits in accumulator units, so every slot is descaled
     int tap_off[kTcMaxTaps]; // patch-row offset of every tap (kernel parameters are warp-uniform by construction)
 };
+
+// the tiles and time slots of CTA b of G (TcArgs::balanced)
+struct TileRun {
+    int first_tile, tile_stride, tiles; // tile k of the CTA = first_tile + k * tile_stride
+    int slot_first;                     // first time slot of its first tile
+    int slot_last_end;                  // end (exclusive) of the time slots of its last tile
+    int slots;                          // time slots of all its tiles together
+};
+
+__host__ __device__ __forceinline__ TileRun tile_run(int total_tiles, int slots, int balanced, int b, int G)
+{
+    TileRun r;
+    if (!balanced) {
+        r.first_tile = b; r.tile_stride = G;
+        r.tiles = (total_tiles - b + G - 1) / G;
+        r.slot_first = 0; r.slot_last_end = slots;
+        r.slots = r.tiles * slots;
+    } else {
+        // run b = units [u0, u1) of the total_tiles * slots (tile, slot) pairs; G <= units, so no run is empty
+        const long long units = (long long)total_tiles * slots;
+        const long long u0 = units * b / G, u1 = units * (b + 1) / G;
+        const long long last = (u1 - 1) / slots;
+        r.first_tile = (int)(u0 / slots); r.tile_stride = 1;
+        r.tiles = (int)(last - r.first_tile) + 1;
+        r.slot_first = (int)(u0 - (long long)r.first_tile * slots);
+        r.slot_last_end = (int)(u1 - 1 - last * slots) + 1;
+        r.slots = (int)(u1 - u0);
+    }
+    return r;
+}
 
 __device__ __forceinline__ uint32_t saddr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -148,8 +181,7 @@ __device__ __forceinline__ void spread32(uint32_t h, uint4 &lo16, uint4 &hi16)
 
 // KHW_T: taps known at compile time (9, 1) or 0 for any tap count up to kTcMaxTaps
 // KWC:   32-channel words per pipeline step (TcArgs::KWc);  RA: patch rows per expanding thread (1 .. kTcMaxARows)
-// SPLIT: tiles cover a share of the time slots and add into the outputs (TcArgs::split > 1)
-template <int KHW_T, int KWC, int RA, bool SPLIT>
+template <int KHW_T, int KWC, int RA>
 __global__ void __launch_bounds__(kTcThreads, 1)
 sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__restrict__ Wb,
                   int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg, int *__restrict__ status, int gate)
@@ -171,16 +203,19 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     const int tid = threadIdx.x, lane = tid & 31;
     // the shuffle tells the compiler what it cannot see: the warp index is the same in every lane
     const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    // Persistent CTA: it owns tiles blockIdx.x, blockIdx.x + gridDim.x, ... and runs them as ONE pipeline, so a tile's
-    // first loads / expansion and its last epilogue / store overlap the neighbouring tiles' MMAs.
-    const int my_tiles = (a.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int n_chunks = SPLIT ? a.total_tiles / (a.tiles_x * a.split) : 1;
-    auto tile_origin = [&](int k, long long &o0, int &nc, int &part) {
-        const int L = (int)blockIdx.x + k * (int)gridDim.x;
-        const int t = L / a.tiles_x;
-        o0 = (long long)(L - t * a.tiles_x) * kTcM;          // first candidate of the tile
-        part = SPLIT ? t / n_chunks : 0;                     // which share of the time slots
-        nc = t - part * n_chunks;                            // 64-channel output chunk
+    // Persistent CTA: it runs its tiles as ONE pipeline, so a tile's first loads / expansion and its last epilogue /
+    // store overlap the neighbouring tiles' MMAs.  Its k-th tile is tile first_tile + k * tile_stride, of which it
+    // computes time slots [slot_lo(k), slot_hi(k)): all of them, except in the first and last tile of a balanced run.
+    // (The run is needed at tile switches only: it lives in shared memory, not in registers.)
+    const TileRun &run = *reinterpret_cast<const TileRun *>(tmem_slot + 2);
+    if (tid == 0)
+        *reinterpret_cast<TileRun *>(tmem_slot + 2) = tile_run(a.total_tiles, a.slots, a.balanced, (int)blockIdx.x, (int)gridDim.x);
+    auto slot_lo = [&](int k) { return k == 0 ? run.slot_first : 0; };
+    auto slot_hi = [&](int k) { return k == run.tiles - 1 ? run.slot_last_end : a.slots; };
+    auto tile_origin = [&](int k, long long &o0, int &nc) {
+        const int L = run.first_tile + k * run.tile_stride;
+        nc = L / a.tiles_x;                                  // 64-channel output chunk
+        o0 = (long long)(L - nc * a.tiles_x) * kTcM;         // first candidate of the tile
     };
 
     // mbarriers (index = operand buffer or accumulator buffer):
@@ -213,6 +248,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    const int my_tiles = run.tiles;
 
     // instruction descriptor: int32 accumulators, signed int8 operands, both K-major, N = 128, M = 128
     const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcN >> 3) << 17) | ((uint32_t)(kTcSub >> 4) << 24);
@@ -247,12 +283,12 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // point the loads at tile k of this CTA: slot 0, chunk 0
     auto load_tile = [&](int k) {
         long long o0;
-        int nc, part;
-        tile_origin(k, o0, nc, part);
-        const int slot0 = part * a.slots_part;                             // first slot of the tile
+        int nc;
+        tile_origin(k, o0, nc);
+        const int slot0 = slot_lo(k);                                      // first slot of the tile
         ld_tile = k;
         ld_ck = 0;
-        ld_left = a.slots_part * a.CK;
+        ld_left = (slot_hi(k) - slot0) * a.CK;
         w_ptr = Wb + ((size_t)nc * a.slots + slot0) * kTcN * wrow_words + ((size_t)w_tap0 * a.CW + w_half) * kTcN + w_row;
         a_plane = Ab + (size_t)slot0 * a.CW * a.NHWp;                       // bit plane of the first slot, word 0
         pf_plane = a_plane + (size_t)kTcPrefetch * KWC * a.NHWp;
@@ -412,8 +448,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     };
 
     bool failed = false;
-    const int n_steps = a.slots_part * a.CK;  // pipeline steps of one tile
-    const int total_steps = my_tiles * n_steps; // ... of this CTA; slots are numbered through all of its tiles
+    const int total_steps = run.slots * a.CK; // pipeline steps of this CTA; slots are numbered through all of its tiles
     // The warps run unsynchronised; every dependence is an mbarrier phase.  Phase parities: barrier index b is used
     // by steps (or slots) b, b + 2, ...; its k-th completion has parity k & 1.  A timed-out wait ends the warp's
     // loop; the warps that depend on it time out in turn, so everybody reaches the end of the kernel.
@@ -429,8 +464,9 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
     // origin grid, it is an output pixel iff i < OH and j < OW
     auto store_tile = [&](int k) {
         long long o0;
-        int nc, part;
-        tile_origin(k, o0, nc, part);
+        int nc;
+        tile_origin(k, o0, nc);
+        const bool shared_tile = slot_hi(k) - slot_lo(k) < a.slots; // other CTAs hold the tile's other time slots
         if (!a.descale_each) {
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[j] = (acc[j] >> kTcScaleLog2) & kDescaleMask;
@@ -446,9 +482,9 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 int16_t *dst = (warp >> 3) ? out_neg : out_pos;
                 if (a.out_nhwc) {
                     int16_t *row = dst + m * a.Co + co0;
-                    if (SPLIT) {
+                    if (shared_tile) {
                         // partial sums of this share of the slots: two int16 per 32-bit add, no carry can cross the
-                        // halves because the complete sums fit 16 bits (the host enables this for aligned rows only)
+                        // halves because the complete sums fit 16 bits (the host cuts tiles for aligned rows only)
                         unsigned int *row32 = reinterpret_cast<unsigned int *>(row);
 #pragma unroll
                         for (int j = 0; j < 32; j++) atomicAdd(row32 + j, acc[j]);
@@ -497,7 +533,7 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
         warp_arrive(&bar_full[0]);
         if (total_steps > 1) load_bits();
         int s_prev = 0, ck_prev = -1; // slot (counted through all tiles) and chunk of step - 1
-        int tile_prev = 0, slot_in_tile_prev = 0;
+        int tile_prev = 0, slots_left_prev = slot_hi(0) - slot_lo(0); // tile of step - 1, its slots still to fold
         for (int step = 0; step <= total_steps; step++) {
             // the previous step's MMAs: its operand buffer is free again and, after the last chunk of a slot, the
             // slot's counts are complete
@@ -515,10 +551,10 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
             if (ck_prev == a.CK - 1) {
                 slot_epilogue(s_prev & 1);
                 warp_arrive(&bar_tfree[s_prev & 1]);
-                if (++slot_in_tile_prev == a.slots_part) {
+                if (--slots_left_prev == 0) {
                     store_tile(tile_prev);
                     tile_prev++;
-                    slot_in_tile_prev = 0;
+                    slots_left_prev = slot_hi(tile_prev) - slot_lo(tile_prev);
                 }
             }
             if (++ck_prev == a.CK) { ck_prev = 0; s_prev++; }
@@ -538,6 +574,41 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
 }
 
 // Tensor-pipe issue-rate probe: back-to-back int8 MMAs (M128 x N x K32) on fixed shared-memory operands.
+// Zeroes the output rows of every tile that two CTAs of a balanced launch share (see TcArgs::balanced).  Block b looks
+// at the cut between runs b and b + 1; a cut inside a tile makes that tile shared.  `grid` is the conv launch's grid.
+__global__ void __launch_bounds__(kTcM)
+zero_shared_tiles_kernel(TcArgs a, int grid, int16_t *__restrict__ out_pos, int16_t *__restrict__ out_neg,
+                         const int *__restrict__ status, int gate)
+{
+    if (gate != 0 && (gate > 0) == (status[1] != 0)) return;
+    const long long units = (long long)a.total_tiles * a.slots;
+    const long long cut = units * ((int)blockIdx.x + 1) / grid;
+    if (cut % a.slots == 0) return;
+    const int L = (int)(cut / a.slots), nc = L / a.tiles_x;
+    const uint32_t o0 = (uint32_t)(L - nc * a.tiles_x) * kTcM;
+    // One row (candidate) per thread decodes its output position; then the warp writes its 32 rows one after the other,
+    // lane l the l-th of the row's 32 words of each sign (rows are 4-byte aligned and hold whole 64-channel chunks, or
+    // the host would not have cut tiles).
+    const int lane = threadIdx.x & 31;
+    const uint32_t o = o0 + threadIdx.x; // blockDim.x == kTcM
+    long long word0 = -1;                // first 32-bit word of the row, -1: the candidate is no output pixel
+    if (o < (uint32_t)a.total_o) {
+        const uint32_t t = o / (uint32_t)a.Wo, n = t / (uint32_t)a.Ho;
+        const int ow = (int)(o - t * (uint32_t)a.Wo), oh = (int)(t - n * (uint32_t)a.Ho);
+        if (ow < a.OW && oh < a.OH)
+            word0 = (long long)(((((size_t)n * a.OH + oh) * a.OW + ow) * a.Co + (size_t)nc * kTcCout) / 2);
+    }
+    uint32_t *pos32 = reinterpret_cast<uint32_t *>(out_pos), *neg32 = reinterpret_cast<uint32_t *>(out_neg);
+#pragma unroll 4
+    for (int j = 0; j < 32; j++) {
+        const long long w = __shfl_sync(0xffffffffu, word0, j);
+        if (w >= 0) {
+            pos32[w + lane] = 0u;
+            neg32[w + lane] = 0u;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(128, 2) mma_probe_kernel(int iters, int n_cols, uint32_t *sink)
 {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -634,7 +705,7 @@ TcGeom tc_geometry(const ConvPlan &p)
         }
     g.CW = (p.C + 31) / 32;
     for (int kwc = g.CW >= 2 ? 2 : 1; kwc >= 1; kwc--) {
-        const size_t need = 2 * ((size_t)2 * kwc * g.rows_a * 16 + (size_t)p.KHW * 2 * kwc * kTcN * 16) + 8 * 8 + 8 + 128;
+        const size_t need = 2 * ((size_t)2 * kwc * g.rows_a * 16 + (size_t)p.KHW * 2 * kwc * kTcN * 16) + 8 * 8 + 8 + sizeof(TileRun) + 128;
         if (need <= 227 * 1024 && p.KHW * kwc <= 4 * kTcMaxBWords) {
             g.KWc = kwc;
             g.CK = (g.CW + kwc - 1) / kwc;
@@ -690,39 +761,6 @@ size_t conv_tc_weight_offset(const ConvPlan &p)
     return align_up((size_t)p.words * 32 * CW * p.NHWp * 4, 256);
 }
 
-// share of the time slots per tile (TcArgs::split) for a plan on a device with `sms` SMs
-static int tc_split(const ConvPlan &p, const rexsc_sc_conv_desc &d, const TcGeom &g, const int16_t *d_pos,
-                    const int16_t *d_neg, int sms)
-{
-    const int NC = (p.Co + kTcCout - 1) / kTcCout;
-    const int slots = p.words * 32;
-    const long long total_o = (long long)p.N * g.Ho * g.Wo;
-    const int tiles_x = (int)((total_o + kTcM - 1) / kTcM);
-    // Few tiles per SM: the last wave of whole tiles leaves SMs idle.  Half-length tiles (each half of the time slots,
-    // summed with atomics) waste less when that saves more than the extra prologues cost.
-    int split = 1;
-    {
-        const long long tiles = (long long)tiles_x * NC;
-        const double whole = (double)((tiles + sms - 1) / sms), halves = (double)((2 * tiles + sms - 1) / sms) / 2.0;
-        // packed 32-bit atomic adds need 4-byte aligned rows: an int16 view at an odd element offset takes whole tiles
-        const bool aligned4 = ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 3u) == 0;
-        const bool rows_ok = d.out_channels_last && (p.Co % kTcCout) == 0 && aligned4;
-        // (measured: tiles of strided layers -- several patch rows per thread, 32-channel steps -- lose more at the extra
-        // tile switches than the fuller wave gains)
-        auto long_tiles = [&](int parts) { return g.rows_a <= kTcWorkers && (slots / parts) * g.CK >= 32; };
-        // and the atomic adds cost about as much as they save once the outputs are tens of MB (measured at 28x28)
-        const bool small_out = (size_t)p.M * p.Co * sizeof(int16_t) <= (size_t)16 << 20;
-        if (rows_ok && long_tiles(2) && small_out && slots % 2 == 0 && halves < 0.95 * whole && 2 * tiles <= 0x7fffffffLL)
-            split = 2;
-        // Grids that leave most SMs idle even then (a linear layer: a handful of tiles, long streams): keep halving the
-        // share of the time slots per tile while every tile still finds an SM of its own
-        if (rows_ok && small_out)
-            while (split < 16 && slots % (2 * split) == 0 && long_tiles(2 * split) && tiles * 2 * split <= sms)
-                split *= 2;
-    }
-    return split;
-}
-
 static int device_sms(int *sms)
 {
     int dev = 0;
@@ -731,15 +769,8 @@ static int device_sms(int *sms)
     return REXSC_OK;
 }
 
-bool conv_tc_splits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const int16_t *d_pos, const int16_t *d_neg)
-{
-    int sms = 0;
-    if (!conv_tc_supported(p) || device_sms(&sms) != REXSC_OK) return false;
-    return tc_split(p, d, tc_geometry(p), d_pos, d_neg, sms) > 1;
-}
-
 int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws, size_t weight_offset, int16_t *d_pos,
-                   int16_t *d_neg, int *d_status, int gate, bool zero_outputs, cudaStream_t st)
+                   int16_t *d_neg, int *d_status, int gate, cudaStream_t st)
 {
     if (!conv_tc_supported(p)) return REXSC_E_UNSUPPORTED;
     const TcGeom g = tc_geometry(p);
@@ -758,13 +789,36 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
     a.tiles_x = (int)((a.total_o + kTcM - 1) / kTcM);
     int sms = 0;
     if (int rc = device_sms(&sms)) return rc;
-    a.split = tc_split(p, d, g, d_pos, d_neg, sms);
-    a.slots_part = slots / a.split;
-    a.total_tiles = a.tiles_x * NC * a.split;
-    if (a.split > 1 && zero_outputs) {
-        const size_t out_bytes = (size_t)p.M * p.Co * sizeof(int16_t);
-        REXSC_CUDA_CHECK(cudaMemsetAsync(d_pos, 0, out_bytes, st));
-        REXSC_CUDA_CHECK(cudaMemsetAsync(d_neg, 0, out_bytes, st));
+    a.total_tiles = a.tiles_x * NC;
+    // One persistent CTA per SM (the kernel owns the SM's tensor memory).  Whole tiles dealt round-robin leave SMs idle
+    // in the last wave (900 tiles on 148 SMs: 7 waves for the work of 6.1); cutting the (tile, slot) sequence into
+    // equal runs does not.  The cut tiles are summed with packed 32-bit atomic adds, which need 4-byte aligned rows
+    // of whole 64-channel chunks; the fallback launch of a gated pair keeps whole tiles (it is the rare one and a
+    // second clearing kernel would cost every call).
+    const long long units = (long long)a.total_tiles * slots;
+    const bool aligned4 = ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 3u) == 0;
+    const bool rows_ok = d.out_channels_last && (p.Co % kTcCout) == 0 && aligned4;
+    unsigned grid = (unsigned)(a.total_tiles < sms ? a.total_tiles : sms);
+    a.balanced = 0;
+    static const bool allow_balanced = !(getenv("REXSC_TC_BALANCED") && getenv("REXSC_TC_BALANCED")[0] == '0');
+    // (measured: tiles with little tensor work per slot -- 1x1 filters on up to 256 channels -- gain nothing: their
+    // time goes to the per-slot hand-offs, and the atomic stores of the cut tiles cost more than the idle SMs did)
+    const bool heavy_slots = p.KHW * CW >= 16 || a.total_tiles < sms;
+    if (allow_balanced && heavy_slots && rows_ok && gate >= 0 && a.total_tiles % sms != 0) {
+        // short layers: as many CTAs as leaves each about 64 pipeline steps to amortise its prologue
+        long long ctas = units * g.CK / 64;
+        if (ctas < 1) ctas = 1;
+        if (ctas > sms) ctas = sms;
+        const long long waves = (a.total_tiles + sms - 1) / sms;
+        // worth a clearing launch when the last wave of whole tiles would waste more than 1 % of the SM time
+        if ((double)a.total_tiles / sms < 0.99 * (double)waves || ctas > (long long)grid) {
+            a.balanced = 1;
+            grid = (unsigned)ctas;
+        }
+    }
+    if (a.balanced && grid > 1) {
+        zero_shared_tiles_kernel<<<grid - 1, kTcM, 0, st>>>(a, (int)grid, d_pos, d_neg, d_status, gate);
+        REXSC_LAUNCH_CHECK("zero_shared_tiles_kernel");
     }
     a.NHWp = p.NHWp; a.out_nhwc = d.out_channels_last;
     if ((reinterpret_cast<uintptr_t>(d_pos) | reinterpret_cast<uintptr_t>(d_neg)) & 1u) return REXSC_E_BAD_ARG;
@@ -775,15 +829,11 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
         a.n_or = (int)cap; // a count never exceeds the dot length, so clamping there changes nothing
     }
     for (int t = 0; t < kTcMaxTaps; t++) a.tap_off[t] = g.tap_off[t];
-    // one persistent CTA per SM (the kernel owns the SM's tensor memory), fewer when there are fewer tiles
-    const unsigned grid = (unsigned)(a.total_tiles < sms ? a.total_tiles : sms);
     const int ra = (g.rows_a + kTcWorkers - 1) / kTcWorkers;
     auto pick = [&](auto khw_tag) {
         constexpr int KHW_T = decltype(khw_tag)::value;
-        if (a.split > 1) // enabled for one-row-per-thread geometries only
-            return g.KWc == 2 ? sc_conv_tc_kernel<KHW_T, 2, 1, true> : sc_conv_tc_kernel<KHW_T, 1, 1, true>;
-        if (g.KWc == 2) return ra == 1 ? sc_conv_tc_kernel<KHW_T, 2, 1, false> : sc_conv_tc_kernel<KHW_T, 2, kTcMaxARows, false>;
-        return ra == 1 ? sc_conv_tc_kernel<KHW_T, 1, 1, false> : sc_conv_tc_kernel<KHW_T, 1, kTcMaxARows, false>;
+        if (g.KWc == 2) return ra == 1 ? sc_conv_tc_kernel<KHW_T, 2, 1> : sc_conv_tc_kernel<KHW_T, 2, kTcMaxARows>;
+        return ra == 1 ? sc_conv_tc_kernel<KHW_T, 1, 1> : sc_conv_tc_kernel<KHW_T, 1, kTcMaxARows>;
     };
     auto kernel = p.KHW == 9 ? pick(std::integral_constant<int, 9>{})
                 : p.KHW == 1 ? pick(std::integral_constant<int, 1>{}) : pick(std::integral_constant<int, 0>{});

@@ -407,6 +407,32 @@ def test_compact_grid_with_prepared_weights(ops):
         assert torch.equal(pos, rpos) and torch.equal(neg, rneg)
 
 
+def test_kernel_launch_counter(ops):
+    """rexsc_kernel_launch_count counts this library's kernels: a tensor-core conv whose padding the op does takes the
+    single-launch expand stage and the conv kernel, plus one clearing kernel when CTAs share tiles; the ALU path takes
+    tables, two expansions and the accumulate kernel."""
+    from rexsc_b200 import _lib
+    lib = _lib.load()
+    x, w = conv_inputs(4, 64, 8, 8, 64, 3, prec=7, seed=3)
+    x = x.cuda().contiguous(memory_format=torch.channels_last)
+    w = w.cuda().contiguous(memory_format=torch.channels_last)
+
+    def launches(kernel, pad, xin):
+        ops.set_conv_kernel(kernel)
+        try:
+            c0 = lib.rexsc_kernel_launch_count()
+            ops.conv2d_generic_general_split_acc(xin, w, 32, -1, 16, (pad, pad), (1, 1), PROG, 1, 1, True, False)
+            return lib.rexsc_kernel_launch_count() - c0
+        finally:
+            ops.set_conv_kernel("auto")
+
+    assert launches("tensor", 1, x) in (2, 3)
+    assert launches("direct", 1, x) == 4
+    # caller-padded: border check inside the expand launch, the gated standard-grid expand and conv behind it
+    xp = torch.nn.functional.pad(x, (1, 1, 1, 1)).contiguous(memory_format=torch.channels_last)
+    assert launches("tensor", 0, xp) in (4, 5)
+
+
 def test_auto_kernel_choice(ops):
     """AUTO resolves to the tensor-core kernel for every layer shape of the bench workload that has >= 32 input
     channels and at most 9 taps, and to an ALU kernel for thin inputs and large filters."""
