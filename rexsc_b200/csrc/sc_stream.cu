@@ -1152,25 +1152,36 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
         const size_t row_words_w = (size_t)wa.KHW * wa.CW;
         const int row_words = wa.nvals * WORDS + 1;
         uint32_t *tile = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(lut_s) + lut_smem_bytes) + warp * 2048; // [2][32][32]
-        // Small filters: one output channel per item (more items than warps matter more than coalesced stores)
-        for (long long item = (long long)blockIdx.x * kFastWarps + warp; !g.w_coarse && item < g.w_items;
-             item += (long long)gridDim.x * kFastWarps) {
+        // Small filters: one output channel per item (more items than warps matter more than coalesced stores).  The
+        // weight of the warp's NEXT item is loaded before the current one is processed.
+        auto fine_weight = [&](long long item) { // lane's weight of a fine item; 0 outside the tensor
+            const int cw = (int)(item % wa.CW);
+            const long long t = item / wa.CW;
+            const int tap = (int)(t % wa.KHW), co = (int)(t / wa.KHW);
+            const int kh = tap / wa.KW, kw = tap - kh * wa.KW;
+            const int ci = cw * 32 + lane;
+            if (item >= g.w_items || ci >= wa.C || co >= wa.Co) return 0.f;
+            const long long wi = wa.ohwi ? (((long long)co * wa.KH + kh) * wa.KW + kw) * wa.C + ci
+                                         : (((long long)co * wa.C + ci) * wa.KH + kh) * wa.KW + kw;
+            return load_weight_any(wt, g.w_dtype, wi);
+        };
+        const long long item_step = (long long)gridDim.x * kFastWarps;
+        float w_next = g.w_coarse ? 0.f : fine_weight((long long)blockIdx.x * kFastWarps + warp);
+        for (long long item = (long long)blockIdx.x * kFastWarps + warp; !g.w_coarse && item < g.w_items; item += item_step) {
+            const float w_cur = w_next;
+            w_next = fine_weight(item + item_step);
             const int cw = (int)(item % wa.CW);
             long long t = item / wa.CW;
             const int tap = (int)(t % wa.KHW);
             const int co = (int)(t / wa.KHW); // 0 .. NC*64: rows past Co stay zero
             const int kh = tap / wa.KW, kw = tap - kh * wa.KW;
             const int ci = cw * 32 + lane;
-            int mag = 0;
-            bool neg = false;
-            if (ci < wa.C && co < wa.Co) {
-                const long long wi = wa.ohwi ? (((long long)co * wa.KH + kh) * wa.KW + kw) * wa.C + ci
-                                             : (((long long)co * wa.C + ci) * wa.KH + kh) * wa.KW + kw;
-                const float v = load_weight_any(wt, g.w_dtype, wi) * wa.scale;
-                const int qp = (int)ceilf(fminf(fmaxf(v, 0.f), wa.scale - 1.f));
-                const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - wa.scale), 0.f));
-                if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
-            }
+            const float v = w_cur * wa.scale;
+            // w_pos = ceil(clamp(v, 0, L-1)); w_neg = ceil(-clamp(v, 1-L, 0))  (sc_cuda.cpp:92-93)
+            const int qp = (int)ceilf(fminf(fmaxf(v, 0.f), wa.scale - 1.f));
+            const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - wa.scale), 0.f));
+            const bool neg = qn > 0;
+            const int mag = neg ? qn : qp;
             const long long seed_ind = wa.linear_seeds ? (long long)ci : ((long long)ci * wa.KH + kh) * wa.KW + kw;
             const int row_off = (int)((13 + seed_ind) % wa.period) * row_words;
             const int nchunk = co >> 6, col = co & 63;
@@ -1197,23 +1208,34 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
             const int nchunk = cb >> 1, col0 = (cb & 1) * 32;
 #pragma unroll 1
             for (int wd = 0; wd < WORDS; wd++) {
-#pragma unroll 4
-                for (int cl = 0; cl < 32; cl++) {
-                    const int co = cb * 32 + cl;
-                    int mag = 0;
-                    bool neg = false;
-                    if (ci < wa.C && co < wa.Co) {
-                        const long long wi = wa.ohwi ? (((long long)co * wa.KH + kh) * wa.KW + kw) * wa.C + ci
-                                                     : (((long long)co * wa.C + ci) * wa.KH + kh) * wa.KW + kw;
-                        const float v = load_weight_any(wt, g.w_dtype, wi) * wa.scale;
+                // eight output channels at a time: their loads are issued together, so the item costs four memory
+                // latencies instead of thirty-two
+#pragma unroll 1
+                for (int cl0 = 0; cl0 < 32; cl0 += 8) {
+                    float wv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int co = cb * 32 + cl0 + j;
+                        wv[j] = 0.f;
+                        if (ci < wa.C && co < wa.Co) {
+                            const long long wi = wa.ohwi ? (((long long)co * wa.KH + kh) * wa.KW + kw) * wa.C + ci
+                                                         : (((long long)co * wa.C + ci) * wa.KH + kh) * wa.KW + kw;
+                            wv[j] = load_weight_any(wt, g.w_dtype, wi);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int cl = cl0 + j;
+                        const float v = wv[j] * wa.scale;
                         // w_pos = ceil(clamp(v, 0, L-1)); w_neg = ceil(-clamp(v, 1-L, 0))  (sc_cuda.cpp:92-93)
                         const int qp = (int)ceilf(fminf(fmaxf(v, 0.f), wa.scale - 1.f));
                         const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - wa.scale), 0.f));
-                        if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
+                        const bool neg = qn > 0;
+                        const int mag = neg ? qn : qp;
+                        const uint32_t sw = lut_s[row_off + mag * WORDS + wd]; // row `value 0` is zero
+                        tile[cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? 0u : sw, lane));
+                        tile[1024 + cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? sw : 0u, lane));
                     }
-                    const uint32_t v = lut_s[row_off + mag * WORDS + wd]; // row `value 0` is zero
-                    tile[cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? 0u : v, lane));
-                    tile[1024 + cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? v : 0u, lane));
                 }
                 __syncwarp();
                 uint32_t *dst = Wb + (((size_t)nchunk * slots + wd * 32) * row_words_w + (size_t)tap * wa.CW + cw) * 128 + col0 + lane;
