@@ -158,6 +158,21 @@ int rexsc_sc_linear_fwd(int32_t batch, int32_t c_in, int32_t c_out, int32_t act_
                         void *d_workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * The same op with the seed offsets of the weight generators as arguments: the stream of weight (co, c) starts from
+ * LFSR state (offset + c) mod (2^l - 1) + 1, offset = w_seed_pos for a positive and w_seed_neg for a negative weight.
+ * rexsc_sc_linear_fwd is the (13, 13) of the extension (sc_cuda_matmul.cu:77-78).  (67, 37) with OR-1 (bin_config 0)
+ * or plain counting reproduces the per-bit torch loop of the reference's linear_generic with generator='lfsr' and
+ * shared generators (utils_functional.py:147-165, 1016-1036): pos / bit_length and neg / bit_length are its
+ * result_pos.mean(0) and result_neg.mean(0).  Offsets must not be negative.
+ */
+int rexsc_sc_linear_fwd_seeded(int32_t batch, int32_t c_in, int32_t c_out, int32_t act_dtype, int32_t w_dtype,
+                               int32_t bit_length, int32_t lfsr_length, int32_t bin_config, int32_t gen_config,
+                               int32_t prog_total_width, int32_t prog_load_width, int32_t prog_load_wait,
+                               int32_t w_seed_pos, int32_t w_seed_neg, const void *d_act, const void *d_weight,
+                               int16_t *d_out_pos, int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes,
+                               void *stream);
+
+/*
  * Reads the device status word of a workspace used by the call(s) above: synchronises `stream`,
  * returns REXSC_OK or REXSC_E_DEVICE_TIMEOUT.  Optional (debug / tests); the forward calls
  * themselves never synchronise.

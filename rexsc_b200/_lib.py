@@ -49,6 +49,7 @@ SYMBOLS = {
     "rexsc_sc_conv2d_accumulate": (C.c_int, [C.POINTER(ScConvDesc), _vp, _vp, _vp, _sz, _vp]),
     "rexsc_sc_linear_workspace_size": (_sz, [_i32] * 6),
     "rexsc_sc_linear_fwd": (C.c_int, [_i32] * 12 + [_vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "rexsc_sc_linear_fwd_seeded": (C.c_int, [_i32] * 14 + [_vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "rexsc_workspace_status": (C.c_int, [_vp, _vp]),
     "rexsc_build_lfsr_lut": (C.c_int, [_i32] * 8 + [_vp, _vp]),
     "rexsc_orn_fwd": (C.c_int, [_vp, _i32, _vp, _i64, _i32, _vp]),

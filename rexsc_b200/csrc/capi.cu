@@ -78,12 +78,16 @@ static int grid_mode(const rexsc_sc_conv_desc *desc, const ConvPlan &p, int kern
 // allow_partial: a null operand is skipped and what an earlier expand with the same descriptor and workspace wrote
 // for it stays in place (a caller whose weights do not change between calls expands them once).
 static int conv_expand(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, void *d_workspace,
-                       size_t workspace_bytes, cudaStream_t st, bool allow_partial)
+                       size_t workspace_bytes, cudaStream_t st, bool allow_partial, int w_seed_pos = 13,
+                       int w_seed_neg = 13)
 {
     ConvPlan p, pc;
     ConvBuffers b;
     int rc = conv_buffers(desc, d_workspace, workspace_bytes, &p, &b);
     if (rc != REXSC_OK) return rc;
+    if (w_seed_pos < 0 || w_seed_neg < 0) return REXSC_E_BAD_ARG;
+    p.w_seed_pos = w_seed_pos; // (a local copy of the cached plan; the compact plan below is derived from it)
+    p.w_seed_neg = w_seed_neg;
     if (allow_partial ? (!d_act && !d_weight) : (!d_act || !d_weight)) return REXSC_E_BAD_ARG;
     const int k = resolve_kernel(desc, p);
     if (k < 0) return k;
@@ -166,14 +170,15 @@ static int conv_accumulate(const rexsc_sc_conv_desc *desc, int16_t *d_out_pos, i
 }
 
 int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
-                 int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st)
+                 int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st, int w_seed_pos,
+                 int w_seed_neg)
 {
     if (!d_act || !d_weight || !d_out_pos || !d_out_neg) {
         ConvPlan p;
         int rc = make_conv_plan(desc, &p);
         return rc != REXSC_OK ? rc : REXSC_E_BAD_ARG;
     }
-    int rc = conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, st, false);
+    int rc = conv_expand(desc, d_act, d_weight, d_workspace, workspace_bytes, st, false, w_seed_pos, w_seed_neg);
     if (rc != REXSC_OK) return rc;
     return conv_accumulate(desc, d_out_pos, d_out_neg, d_workspace, workspace_bytes, st);
 }
@@ -262,6 +267,20 @@ extern "C" int rexsc_sc_linear_fwd(int32_t batch, int32_t c_in, int32_t c_out, i
                 prog_total_width, prog_load_width, prog_load_wait);
     return conv_forward(&d, d_act, d_weight, d_out_pos, d_out_neg, d_workspace, workspace_bytes,
                         (cudaStream_t)stream);
+}
+
+extern "C" int rexsc_sc_linear_fwd_seeded(int32_t batch, int32_t c_in, int32_t c_out, int32_t act_dtype, int32_t w_dtype,
+                                          int32_t bit_length, int32_t lfsr_length, int32_t bin_config,
+                                          int32_t gen_config, int32_t prog_total_width, int32_t prog_load_width,
+                                          int32_t prog_load_wait, int32_t w_seed_pos, int32_t w_seed_neg,
+                                          const void *d_act, const void *d_weight, int16_t *d_out_pos,
+                                          int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, void *stream)
+{
+    rexsc_sc_conv_desc d;
+    linear_desc(&d, batch, c_in, c_out, act_dtype, w_dtype, bit_length, lfsr_length, bin_config, gen_config,
+                prog_total_width, prog_load_width, prog_load_wait);
+    return conv_forward(&d, d_act, d_weight, d_out_pos, d_out_neg, d_workspace, workspace_bytes,
+                        (cudaStream_t)stream, w_seed_pos, w_seed_neg);
 }
 
 extern "C" int rexsc_workspace_status(const void *d_workspace, void *stream)

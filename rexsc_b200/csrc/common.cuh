@@ -66,6 +66,10 @@ struct ConvPlan {
     //   col'  = (w % sw) * Wq + w / sw       kept iff w % sw < nrw = min(sw, KW),  Wq = ceil(Wp / sw)
     //   P     = (n * Hrows + row') * Wrow + col',   Hrows = ceil(Hp / sh) * nrh,  Wrow = Wq * nrw
     int nrh, nrw, Wq, Hrows, Wrow;
+    // seed offsets of the weight generators: the phase of a weight is (offset + seed index) mod period, per sign.  The
+    // extension seeds both signs at 13 (sc_cuda_conv.cu:45,55-56; sc_cuda_matmul.cu:77-78); the front end's pure-torch
+    // linear bit loop seeds positive weights at 67 and negative ones at 37 (utils_functional.py:147-165).
+    int w_seed_pos, w_seed_neg;
     int origin;           // 0: stored pixel (row', col') as above.  1: compact grid of 3x3 stride-1 layers whose border
                           // pixels are zero (see make_compact_plan): stored pixel (r, c) = padded pixel (r + 1, c + 1)
     int max_tap;          // largest tap offset (see tap_offset)
@@ -134,8 +138,10 @@ static inline long long patch_bound_words(long long BM, long long M, int OW, int
 }
 
 // pad + quantise + stream generation + OR-n accumulation with the scratch at d_workspace (capi.cu)
+// w_seed_pos / w_seed_neg: see ConvPlan (13, 13 reproduces the extension)
 int conv_forward(const rexsc_sc_conv_desc *desc, const void *d_act, const void *d_weight, int16_t *d_out_pos,
-                 int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st);
+                 int16_t *d_out_neg, void *d_workspace, size_t workspace_bytes, cudaStream_t st, int w_seed_pos = 13,
+                 int w_seed_neg = 13);
 
 int launch_mma_probe(int blocks, int iters, int n_cols, uint32_t *d_sink, cudaStream_t st);
 bool conv_tc_supported(const ConvPlan &p);

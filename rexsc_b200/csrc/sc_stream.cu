@@ -186,6 +186,8 @@ static int make_conv_plan_uncached(const rexsc_sc_conv_desc *d, ConvPlan *p)
     p->OH = (p->Hp - p->KH) / p->sh + 1;
     p->OW = (p->Wp - p->KW) / p->sw + 1;
     p->origin = 0;
+    p->w_seed_pos = 13;
+    p->w_seed_neg = 13;
     p->nrh = p->sh < p->KH ? p->sh : p->KH;
     p->nrw = p->sw < p->KW ? p->sw : p->KW;
     p->Wq = (p->Wp + p->sw - 1) / p->sw;
@@ -1014,6 +1016,7 @@ __device__ __forceinline__ uint32_t reverse_nibbles(uint32_t v)
 struct ExpandWBitsArgs {
     int C, Co, KH, KW, KHW, CW, NC;
     int period, nvals, words, linear_seeds, ohwi;
+    int seed_pos, seed_neg; // ConvPlan::w_seed_pos / w_seed_neg
     float scale;
 };
 
@@ -1183,7 +1186,7 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
             const bool neg = qn > 0;
             const int mag = neg ? qn : qp;
             const long long seed_ind = wa.linear_seeds ? (long long)ci : ((long long)ci * wa.KH + kh) * wa.KW + kw;
-            const int row_off = (int)((13 + seed_ind) % wa.period) * row_words;
+            const int row_off = (int)(((neg ? wa.seed_neg : wa.seed_pos) + seed_ind) % wa.period) * row_words;
             const int nchunk = co >> 6, col = co & 63;
 #pragma unroll
             for (int wd = 0; wd < WORDS; wd++) {
@@ -1204,7 +1207,8 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
             const int ci = cw * 32 + lane;
             // seed index c*KH*KW + kh*KW + kw, offset 13 for both signs (sc_cuda_conv.cu:45,55-56); linear: c only
             const long long seed_ind = wa.linear_seeds ? (long long)ci : ((long long)ci * wa.KH + kh) * wa.KW + kw;
-            const int row_off = (int)((13 + seed_ind) % wa.period) * row_words;
+            const int row_off_pos = (int)((wa.seed_pos + seed_ind) % wa.period) * row_words;
+            const int row_off_neg = (int)((wa.seed_neg + seed_ind) % wa.period) * row_words;
             const int nchunk = cb >> 1, col0 = (cb & 1) * 32;
 #pragma unroll 1
             for (int wd = 0; wd < WORDS; wd++) {
@@ -1232,7 +1236,7 @@ expand_all_kernel(ExpandAllArgs g, const T *__restrict__ x, const void *__restri
                         const int qn = (int)ceilf(-fminf(fmaxf(v, 1.f - wa.scale), 0.f));
                         const bool neg = qn > 0;
                         const int mag = neg ? qn : qp;
-                        const uint32_t sw = lut_s[row_off + mag * WORDS + wd]; // row `value 0` is zero
+                        const uint32_t sw = lut_s[(neg ? row_off_neg : row_off_pos) + mag * WORDS + wd]; // row `value 0` is zero
                         tile[cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? 0u : sw, lane));
                         tile[1024 + cl * 32 + (lane ^ cl)] = reverse_nibbles(transpose32_warp(neg ? sw : 0u, lane));
                     }
@@ -1310,6 +1314,7 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     w.CW = (p.C + 31) / 32; w.NC = (p.Co + 63) / 64;
     w.period = p.period; w.nvals = p.nvals; w.words = p.words; w.linear_seeds = d.linear_seeds;
     w.ohwi = d.w_channels_last; w.scale = (float)p.scale;
+    w.seed_pos = p.w_seed_pos; w.seed_neg = p.w_seed_neg;
     g.lut = LutParams{p.l, d.bit_length, d.gen_config, xnor, d.prog_total_width, d.prog_load_width, d.prog_load_wait, p.words};
     g.w_dtype = d.w_dtype;
     g.w_items = (long long)w.NC * 2 * w.KHW * w.CW; // blocks of 32 output channels x taps x channel words
@@ -1428,6 +1433,7 @@ struct ExpandWArgs {
     int period, nvals, words, linear_seeds, ohwi;
     long long w_plane_words;
     float scale;
+    int seed_pos, seed_neg; // ConvPlan::w_seed_pos / w_seed_neg
 };
 
 template <typename T>
@@ -1463,7 +1469,7 @@ __global__ void __launch_bounds__(256) expand_weight_kernel(ExpandWArgs a, const
         if (qn > 0) { neg = true; mag = qn; } else { mag = qp; }
     }
     long long seed_ind = a.linear_seeds ? (long long)ci : ((long long)ci * a.KH + kh) * a.KW + kw;
-    int phase = (int)((13 + seed_ind) % a.period);
+    int phase = (int)(((neg ? a.seed_neg : a.seed_pos) + seed_ind) % a.period);
     const uint32_t *row = lut + ((size_t)phase * a.nvals + mag) * a.words;
     size_t base = ((((size_t)nt * a.CCH + cch) * a.KHW + khw) * kChunkC + cc) * kTileN + nl;
     for (int j = 0; j < a.words; j++) {
@@ -1481,6 +1487,7 @@ int launch_expand_weight(const ConvPlan &p, const rexsc_sc_conv_desc &d, const v
     a.C = p.C; a.Co = p.Co; a.KH = p.KH; a.KW = p.KW; a.KHW = p.KHW; a.CCH = p.CCH; a.NT = p.NT;
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.ohwi = d.w_channels_last; a.w_plane_words = p.w_plane_words; a.scale = (float)p.scale;
+    a.seed_pos = p.w_seed_pos; a.seed_neg = p.w_seed_neg;
     long long total_threads = (long long)p.NT * p.CCH * p.KHW * 8 * 32;
     unsigned blocks = (unsigned)((total_threads + 255) / 256);
     switch (d.w_dtype) {
@@ -1533,7 +1540,7 @@ __global__ void __launch_bounds__(256) expand_weight_bits_kernel(ExpandWBitsArgs
         }
         // seed index c*KH*KW + kh*KW + kw, offset 13 for both signs (sc_cuda_conv.cu:45,55-56); linear: c only
         const long long seed_ind = a.linear_seeds ? (long long)ci : ((long long)ci * a.KH + kh) * a.KW + kw;
-        const int phase = (int)((13 + seed_ind) % a.period);
+        const int phase = (int)(((neg ? a.seed_neg : a.seed_pos) + seed_ind) % a.period);
         const int nchunk = co >> 6, col = co & 63;
         for (int wd = 0; wd < a.words; wd++) {
             const uint32_t v = mag > 0 ? __ldg(lut + ((size_t)phase * a.nvals + mag) * a.words + wd) : 0u;
@@ -1554,6 +1561,7 @@ int launch_expand_weight_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, co
     a.CW = (p.C + 31) / 32; a.NC = (p.Co + 63) / 64;
     a.period = p.period; a.nvals = p.nvals; a.words = p.words; a.linear_seeds = d.linear_seeds;
     a.ohwi = d.w_channels_last; a.scale = (float)p.scale;
+    a.seed_pos = p.w_seed_pos; a.seed_neg = p.w_seed_neg;
     const long long items = (long long)a.NC * 64 * a.KHW * a.CW;
     const long long blocks = (items + 7) / 8;
     if (blocks > 0x7fffffffLL) return REXSC_E_TOO_LONG;

@@ -264,9 +264,11 @@ def workspace_status(device=None) -> int:
 @_traced
 def linear_generic_general_acc(input: torch.Tensor, weight: torch.Tensor, prog_load: Sequence[int], bit_length: int,
                                lfsr_length: int, bin_config: int, gen_config: int, xnor: bool,
-                               mux: bool) -> List[torch.Tensor]:
+                               mux: bool, *, weight_seeds: Sequence[int] = (13, 13)) -> List[torch.Tensor]:
     """SC linear forward, returns [pos, neg] int16 [B, Cout] (sc_cuda.cpp:101-120).  ``xnor`` is ignored, as in
-    the reference's linear generators (sc_cuda_matmul.cu:27-57)."""
+    the reference's linear generators (sc_cuda_matmul.cu:27-57).  ``weight_seeds`` (not in the reference's op): seed
+    offsets of the positive / negative weight generators; (13, 13) is the extension, (67, 37) the front end's
+    pure-torch bit loop (utils_functional.py:147-149)."""
     _require_cuda(input, "linear_generic_general_acc")
     _require_cuda(weight, "linear_generic_general_acc")
     if input.dim() != 2 or weight.dim() != 2 or input.size(1) != weight.size(1):
@@ -284,11 +286,12 @@ def linear_generic_general_acc(input: torch.Tensor, weight: torch.Tensor, prog_l
         pos = torch.empty((B, Co), dtype=torch.int16, device=dev)
         neg = torch.empty((B, Co), dtype=torch.int16, device=dev)
         ws = _workspace(dev, nbytes)
-        rc = lib.rexsc_sc_linear_fwd(B, Cin, Co, _DTYPES[x.dtype], _DTYPES[w.dtype], int(bit_length),
-                                     int(lfsr_length), int(bin_config), int(gen_config), int(prog_load[0]),
-                                     int(prog_load[1]), int(prog_load[2]), _ptr(x), _ptr(w), _ptr(pos), _ptr(neg),
-                                     _ptr(ws), ws.numel(), _stream(dev))
-        _lib.check(rc, "rexsc_sc_linear_fwd")
+        rc = lib.rexsc_sc_linear_fwd_seeded(B, Cin, Co, _DTYPES[x.dtype], _DTYPES[w.dtype], int(bit_length),
+                                            int(lfsr_length), int(bin_config), int(gen_config), int(prog_load[0]),
+                                            int(prog_load[1]), int(prog_load[2]), int(weight_seeds[0]),
+                                            int(weight_seeds[1]), _ptr(x), _ptr(w), _ptr(pos), _ptr(neg),
+                                            _ptr(ws), ws.numel(), _stream(dev))
+        _lib.check(rc, "rexsc_sc_linear_fwd_seeded")
     return [pos, neg]
 
 

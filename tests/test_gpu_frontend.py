@@ -229,3 +229,38 @@ def test_guide_conv_pair_matches_the_two_convolutions(ops, channels_last):
     a = ops.or_approx_n_forward_bias_std_both_acc(res[0][0], res[0][1], bias, zero, 2)
     b = ops.or_approx_n_forward_bias_std_both_acc(res[1][0], res[1][1], bias, zero, 2)
     assert rel_err(b, a) < 1e-3
+
+
+@pytest.mark.parametrize("forward", ["full_or", "full_bin"])
+@pytest.mark.parametrize("bit_length", [32, 64, 128])
+def test_linear_generic_bit_loop_matches_the_sc_linear_op(fe, bit_length, forward):
+    """The opt-in replacement of the per-bit torch loop of linear_generic (utils_functional.py:955-1082,
+    generator='lfsr', shared generators) against that loop itself: values bit-identical, gradients identical (the
+    guide expression is the same).  Inputs as Linear_Or feeds them (utils_class.py:197-207): quantised to 7 bits,
+    activations in [0, 1) -- off the 1/bit_length grid for the shorter streams, which exercises the ceil rule -- and
+    no magnitude above (bit_length - 1) / bit_length, where the extension's quantiser saturates and the torch loop
+    does not (7-bit inputs with 128-bit streams, Linear_Or's defaults, never get there)."""
+    from rexsc_b200.frontend.linear import linear_generic_sc
+
+    uf = fe.utils_functional
+    torch.manual_seed(bit_length + len(forward))
+    top = (bit_length - 1) / bit_length
+    # few, mostly small weights with some large ones: OR-1 must neither stay empty nor saturate on both signs
+    c_in = 200 if forward == "full_bin" else 40
+    x = uf.quantize(torch.rand(24, c_in, device="cuda"), prec=7).clamp(max=top)
+    w = torch.randn(70, c_in, device="cuda") * 0.05
+    w[:, ::7] *= 12
+    w = uf.quantize(w.clamp(-1, 1), prec=7).clamp(-top, top)
+    cot = torch.randn(24, 70, device="cuda")
+    res = []
+    for ours in (False, True):
+        xi, wi = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        if ours:
+            out = linear_generic_sc(xi, wi, bit_length=bit_length, forward=forward, value_dtype=uf.compute_type)
+        else:
+            out = uf.linear_generic(xi, wi, bit_length=bit_length, forward=forward, generator="lfsr")
+        (out.float() * cot).sum().backward()
+        res.append((out.detach().float(), xi.grad.float(), wi.grad.float()))
+    assert (res[0][0] != 0).float().mean() > 0.3, "trivial case"
+    assert torch.equal(res[1][0], res[0][0]), f"{(res[1][0] != res[0][0]).sum().item()} values differ"
+    assert rel_err(res[1][1], res[0][1]) < 1e-6 and rel_err(res[1][2], res[0][2]) < 1e-6
