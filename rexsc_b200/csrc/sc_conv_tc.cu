@@ -69,6 +69,8 @@ struct TcArgs {
                        //    A tile that two or more CTAs share is zeroed before the launch (zero_shared_tiles_kernel)
                        //    and every sharer adds its partial sums with packed 16-bit atomics; tiles that lie inside
                        //    one run are stored plainly.  No SM idles in a last, partly filled wave of tiles.
+                       // 2: the same runs for outputs whose rows cannot take packed adds (NCHW, ragged or unaligned
+                       //    channel runs): the host clears the whole outputs and every tile adds 16-bit values.
     long long NHWp;
     int out_nhwc;
     int descale_each; // 1: running sums would overflow 16 bits in accumulator units, so every slot is descaled
@@ -480,7 +482,22 @@ sc_conv_tc_kernel(TcArgs a, const uint32_t *__restrict__ Ab, const uint32_t *__r
                 const size_t ohw = (size_t)a.OH * a.OW;
                 const size_t m = ((size_t)n * a.OH + oh) * a.OW + ow;
                 int16_t *dst = (warp >> 3) ? out_neg : out_pos;
-                if (a.out_nhwc) {
+                if (a.balanced == 2) {
+                    // Any layout: EVERY tile of the launch adds its sums into outputs that the host cleared, one
+                    // 16-bit value per 32-bit atomic add on the word that holds it (no carry leaves the value's half:
+                    // the complete sums fit 16 bits; the word's other half gets + 0).  All accesses to these words are
+                    // atomic adds, so neighbours stored by other CTAs cannot be lost.
+                    const size_t e0 = a.out_nhwc ? m * a.Co + co0 : ((size_t)n * a.Co + co0) * ohw + (size_t)oh * a.OW + ow;
+                    const size_t estep = a.out_nhwc ? 1 : ohw;
+#pragma unroll
+                    for (int j = 0; j < 64; j++) {
+                        const uint32_t v = (acc[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+                        if (co0 + j < a.Co && v != 0u) {
+                            const uintptr_t addr = reinterpret_cast<uintptr_t>(dst + e0 + (size_t)j * estep);
+                            atomicAdd(reinterpret_cast<unsigned int *>(addr & ~(uintptr_t)3), v << ((addr & 2u) * 8u));
+                        }
+                    }
+                } else if (a.out_nhwc) {
                     int16_t *row = dst + m * a.Co + co0;
                     if (shared_tile) {
                         // partial sums of this share of the slots: two int16 per 32-bit add, no carry can cross the
@@ -816,7 +833,24 @@ int launch_conv_tc(const ConvPlan &p, const rexsc_sc_conv_desc &d, void *d_tc_ws
             grid = (unsigned)ctas;
         }
     }
-    if (a.balanced && grid > 1) {
+    // Outputs without such rows (NCHW, a ragged last chunk): clear them whole and let every tile add single 16-bit
+    // values -- affordable while the outputs are small, which is where whole tiles waste most (deep layers with few
+    // tiles per SM).  The element count must be even so that the last value's 32-bit word ends inside the tensor.
+    const size_t out_elems = (size_t)p.M * p.Co;
+    if (allow_balanced && heavy_slots && !rows_ok && aligned4 && (out_elems & 1) == 0 && out_elems * sizeof(int16_t) <= ((size_t)16 << 20) &&
+        gate >= 0 && a.total_tiles % sms != 0) {
+        long long ctas = units * g.CK / 64;
+        if (ctas < 1) ctas = 1;
+        if (ctas > sms) ctas = sms;
+        const long long waves = (a.total_tiles + sms - 1) / sms;
+        if ((double)a.total_tiles / sms < 0.95 * (double)waves || ctas > (long long)grid) {
+            a.balanced = 2;
+            grid = (unsigned)ctas;
+            REXSC_CUDA_CHECK(cudaMemsetAsync(d_pos, 0, out_elems * sizeof(int16_t), st));
+            REXSC_CUDA_CHECK(cudaMemsetAsync(d_neg, 0, out_elems * sizeof(int16_t), st));
+        }
+    }
+    if (a.balanced == 1 && grid > 1) {
         zero_shared_tiles_kernel<<<grid - 1, kTcM, 0, st>>>(a, (int)grid, d_pos, d_neg, d_status, gate);
         REXSC_LAUNCH_CHECK("zero_shared_tiles_kernel");
     }
