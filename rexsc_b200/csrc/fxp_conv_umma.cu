@@ -5,12 +5,14 @@
 // non-negative, so splitting K into MMA steps cannot change where the sum saturates -- the cap is applied once to
 // the finished int32 accumulator (the host checks that K*127*127 + K cannot overflow it).
 //
-// Implicit GEMM:  D[m][n'] = sum_k' A[m][k'] * B[n'][k'],  k' runs over the K = Cin*KH*KW products twice
-// (values, then parity bits), n' over the output channels of the CTA's chunk twice (positive weights, then
-// negative weights).  CTA = 128 output pixels (TMEM lanes) x up to 256 columns.
-//   * producers (all 128 threads): gather the int8 activation slab (128 rows x 128 bytes of k') through a
-//     k' -> tensor-offset table and copy the prepacked weight slab, both written to shared memory in the
-//     128-byte swizzled K-major layout the MMA's shared-memory descriptors name;
+// Implicit GEMM:  D[m][n'] = sum_k' A[m][k'] * B[n'][k'],  k' runs over the products twice (values, then parity
+// bits), n' over the output channels of the CTA's chunk twice (positive weights, then negative weights).  CTA = 128
+// output pixels (TMEM lanes) x up to 256 columns.  The products are ordered (tap, channel) with the channels padded
+// to a multiple of 16 -- the order does not matter to the closed form -- and the int8 activations are kept pixel-major
+// (NHWC, same channel padding), so 16 consecutive k' of an output pixel are 16 consecutive bytes in memory.
+//   * producers (all 128 threads): fetch the int8 activation slab (128 rows x 128 bytes of k') as eight 16-byte
+//     loads per row through a chunk -> tensor-offset table, and copy the prepacked weight slab, both written to
+//     shared memory in the 128-byte swizzled K-major layout the MMA's shared-memory descriptors name;
 //   * one thread issues tcgen05.mma.kind::i8 (M=128, N=N', K=32) four times per slab and commits to an mbarrier;
 //   * epilogue: tcgen05.ld 32 lanes x 32 columns per warp, min(., cap), pos - neg, coalesced NCHW int32 stores.
 // Every mbarrier wait is bounded; on a time-out the CTA records it, frees its TMEM and returns.
@@ -27,6 +29,7 @@ constexpr uint32_t kUmmaWaitLimit = 1u << 22;
 
 struct UmmaArgs {
     int N, C, Hp, Wp, Co, OH, OW, sh, sw;
+    int Cp;          // channels padded to 16 (pixel pitch of the int8 activations, channel pitch of k')
     int Kp;          // k' extent padded to kSlabBytes (values + parity)
     int CB, CBp;     // output channels per CTA chunk, padded to 8
     int CBq;         // first MMA column of the negative-weight block (CBp rounded up to 32: aligned TMEM reads)
@@ -81,8 +84,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
     return false;
 }
 
-template <bool SWIZZLED>
-__global__ void __launch_bounds__(128, 1)
+// PREFETCH_B: also fetch the weight slab one step ahead (64 more registers: two CTAs per SM instead of four) -- pays
+// on grids of at most a wave or two of CTAs, whose time is one CTA's chain of slabs
+template <bool SWIZZLED, bool PREFETCH_B>
+__global__ void __launch_bounds__(128, PREFETCH_B ? 2 : 4)
 fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *__restrict__ wpk,
                      const int32_t *__restrict__ koff, int32_t *__restrict__ out, int *__restrict__ status)
 {
@@ -105,7 +110,7 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
         long long t = m / a.OW;
         oh = (int)(t % a.OH);
         n = (int)(t / a.OH);
-        abase = (((long long)n * a.C) * a.Hp + (long long)oh * a.sh) * a.Wp + (long long)ow * a.sw;
+        abase = (((long long)n * a.Hp + (long long)oh * a.sh) * a.Wp + (long long)ow * a.sw) * a.Cp;
     }
 
     if (tid == 0) {
@@ -128,28 +133,47 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
     const int n_slabs = a.Kp / kSlabBytes;
     bool failed = false;
 
-    for (int slab = 0; slab < n_slabs; slab++) {
-        // ---- A slab: row = this thread's output pixel, 8 chunks of 16 k' each --------------------------------
-#pragma unroll 1
-        for (int c = 0; c < 8; c++) {
-            uint32_t w[4] = {0u, 0u, 0u, 0u};
-            if (row_live) {
+    // The activation words of a slab are fetched into registers one slab ahead: the loads of slab s + 1 are in flight
+    // while the tensor core works through slab s (the shared-memory tiles are single: they are rewritten once those
+    // MMAs are done).  Row = this thread's output pixel, 8 chunks of 16 k' each = 16 channels of one tap.  Weight
+    // slab: NP rows x 8 chunks of the prepacked weights, chunk i * 128 + tid for i < 16 (NP <= 256).
+    uint4 av[8], bv[PREFETCH_B ? 16 : 1];
+    auto load_slab = [&](int slab) {
 #pragma unroll
-                for (int b = 0; b < 16; b++) {
-                    const int kp = slab * kSlabBytes + c * 16 + b;
-                    const int off = __ldg(koff + kp);           // < 0: padding; bit 30 set: parity operand
-                    if (off >= 0) {
-                        int v = (int)__ldg(act + abase + (off & 0x3fffffff));
-                        if (off & 0x40000000) v &= 1;
-                        w[b >> 2] |= (uint32_t)(v & 0xff) << (8 * (b & 3));
-                    }
+        for (int c = 0; c < 8; c++) {
+            av[c] = make_uint4(0u, 0u, 0u, 0u);
+            const int off = __ldg(koff + slab * 8 + c);         // < 0: padding; bit 30 set: parity operand
+            if (row_live && off >= 0) {
+                av[c] = __ldg(reinterpret_cast<const uint4 *>(act + abase + (off & 0x3fffffff)));
+                if (off & 0x40000000) {
+                    av[c].x &= 0x01010101u; av[c].y &= 0x01010101u; av[c].z &= 0x01010101u; av[c].w &= 0x01010101u;
                 }
             }
-            *reinterpret_cast<uint4 *>(a_s + (SWIZZLED ? sw128_offset(tid, c) : interleaved_offset(tid, c, kUmmaM))) =
-                make_uint4(w[0], w[1], w[2], w[3]);
         }
-        // ---- B slab: NP rows x 8 chunks, straight copy of the prepacked weights ------------------------------
-        for (int i = tid; i < a.NP * 8; i += blockDim.x) {
+        if (PREFETCH_B) {
+#pragma unroll
+            for (int i = 0; i < (PREFETCH_B ? 16 : 1); i++) {
+                const int e = i * 128 + tid, r = e >> 3, c = e & 7;
+                if (e < a.NP * 8)
+                    bv[i] = __ldg(reinterpret_cast<const uint4 *>(wchunk + (size_t)r * a.Kp + slab * kSlabBytes) + c);
+            }
+        }
+    };
+    load_slab(0);
+    for (int slab = 0; slab < n_slabs; slab++) {
+#pragma unroll
+        for (int c = 0; c < 8; c++)
+            *reinterpret_cast<uint4 *>(a_s + (SWIZZLED ? sw128_offset(tid, c) : interleaved_offset(tid, c, kUmmaM))) = av[c];
+        if (PREFETCH_B) {
+#pragma unroll
+            for (int i = 0; i < (PREFETCH_B ? 16 : 1); i++) {
+                const int e = i * 128 + tid, r = e >> 3, c = e & 7;
+                if (e < a.NP * 8)
+                    *reinterpret_cast<uint4 *>(b_s + (SWIZZLED ? sw128_offset(r, c) : interleaved_offset(r, c, a.NP))) = bv[i];
+            }
+        }
+        // B slab without prefetch: NP rows x 8 chunks, straight copy of the prepacked weights (L2-resident)
+        for (int i = tid; !PREFETCH_B && i < a.NP * 8; i += blockDim.x) {
             const int r = i >> 3, c = i & 7;
             const uint4 v = __ldg(reinterpret_cast<const uint4 *>(wchunk + (size_t)r * a.Kp + slab * kSlabBytes) + c);
             *reinterpret_cast<uint4 *>(b_s + (SWIZZLED ? sw128_offset(r, c) : interleaved_offset(r, c, a.NP))) = v;
@@ -180,6 +204,7 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
                              smem_addr(bar))
                          : "memory");
         }
+        if (slab + 1 < n_slabs) load_slab(slab + 1);
         // the slab buffers are reused next step: wait until the MMAs that read them have completed
         if (!mbar_wait(smem_addr(bar), (uint32_t)(slab & 1))) failed = true;
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
@@ -243,10 +268,12 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
 }
 
 // ---- operand preparation ------------------------------------------------------------------------------------
-__global__ void fxp_umma_pack_kernel(UmmaArgs a, int K, int KH, int KW, int n_chunks, const int32_t *__restrict__ qp,
+// k' = tap * Cp + c for the values, K2 + tap * Cp + c for the parity bits (K2 = KH * KW * Cp); qp / qn are [co][c][tap]
+__global__ void fxp_umma_pack_kernel(UmmaArgs a, int KH, int KW, int n_chunks, const int32_t *__restrict__ qp,
                                      const int32_t *__restrict__ qn, int8_t *__restrict__ wpk,
                                      int32_t *__restrict__ koff)
 {
+    const int KHW = KH * KW, K2 = KHW * a.Cp;
     // weights: wpk[chunk][row n' in 0..NP)[k' in 0..Kp), row = sign * CBq + local channel
     const long long total = (long long)n_chunks * a.NP * a.Kp;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -258,48 +285,75 @@ __global__ void fxp_umma_pack_kernel(UmmaArgs a, int K, int KH, int KW, int n_ch
         const int sign = row >= a.CBq ? 1 : 0, cl = row - sign * a.CBq;
         const int co = chunk * a.CB + cl;
         int v = 0;
-        if (cl < a.CB && co < a.Co && kp < 2 * K) {
-            const int k = kp < K ? kp : kp - K;
-            v = sign ? qn[(long long)co * K + k] : qp[(long long)co * K + k];
-            if (kp >= K) v &= 1;
+        if (cl < a.CB && co < a.Co && kp < 2 * K2) {
+            const int k = kp < K2 ? kp : kp - K2;
+            const int tap = k / a.Cp, c = k - tap * a.Cp;
+            if (c < a.C) {
+                const long long wi = ((long long)co * a.C + c) * KHW + tap;
+                v = sign ? qn[wi] : qp[wi];
+                if (kp >= K2) v &= 1;
+            }
         }
         wpk[i] = (int8_t)v;
     }
-    // k' -> offset of the activation element inside one image, relative to the tap (0,0) of the output pixel
-    for (int kp = blockIdx.x * blockDim.x + threadIdx.x; kp < a.Kp; kp += gridDim.x * blockDim.x) {
+    // 16-byte chunk of k' -> byte offset of its 16 channels inside the int8 activations, relative to tap (0,0) of the
+    // output pixel
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < a.Kp / 16; j += gridDim.x * blockDim.x) {
+        const int kp = j * 16;
         int off = -1;
-        if (kp < 2 * K) {
-            const int k = kp < K ? kp : kp - K;
-            const int ci = k / (KH * KW), r = k - ci * KH * KW, kh = r / KW, kw = r - kh * KW;
-            off = (ci * a.Hp + kh) * a.Wp + kw;
-            if (kp >= K) off |= 0x40000000;
+        if (kp < 2 * K2) {
+            const int k = kp < K2 ? kp : kp - K2;
+            const int tap = k / a.Cp, cg = k - tap * a.Cp, kh = tap / KW, kw = tap - kh * KW;
+            off = (kh * a.Wp + kw) * a.Cp + cg;
+            if (kp >= K2) off |= 0x40000000;
         }
-        koff[kp] = off;
+        koff[j] = off;
     }
 }
 
-__global__ void fxp_umma_act_kernel(long long total, const int32_t *__restrict__ q, int8_t *__restrict__ q8)
+// int32 NCHW (padded tensor) -> int8 NHWC with the channels padded to Cp; one thread per pixel and 16 channels
+__global__ void fxp_umma_act_kernel(UmmaArgs a, const int32_t *__restrict__ q, int8_t *__restrict__ q8)
 {
+    const int groups = a.Cp / 16;
+    const long long plane = (long long)a.Hp * a.Wp, total = (long long)a.N * plane * groups;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (long long)gridDim.x * blockDim.x)
-        q8[i] = (int8_t)q[i];
+         i += (long long)gridDim.x * blockDim.x) {
+        // consecutive threads take consecutive pixels of one channel group: the strided int32 reads coalesce
+        const long long pix = i % plane;
+        const long long t = i / plane;
+        const int g = (int)(t % groups), n = (int)(t / groups);
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int b = 0; b < 16; b++) {
+            const int c = g * 16 + b;
+            if (c < a.C) w[b >> 2] |= (uint32_t)(q[((long long)n * a.C + c) * plane + pix] & 0xff) << (8 * (b & 3));
+        }
+        *reinterpret_cast<uint4 *>(q8 + ((long long)n * plane + pix) * a.Cp + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
 }
 
 } // namespace
+
+static long long umma_k2(int C, long long K) // padded product count per operand kind: taps x padded channels
+{
+    const long long khw = C > 0 ? K / C : 0;
+    return khw * ((C + 15) / 16 * 16);
+}
 
 size_t fxp_umma_workspace_bytes(int N, int C, int Hp, int Wp, int Co, long long K)
 {
     const int CB = Co < 128 ? Co : 128;
     const int n_chunks = (Co + CB - 1) / CB;
-    const long long Kp = (2 * K + kSlabBytes - 1) / kSlabBytes * kSlabBytes;
-    return align_up((size_t)N * C * Hp * Wp, 256) + align_up((size_t)n_chunks * 256 * Kp, 256) +
+    const int Cp = (C + 15) / 16 * 16;
+    const long long Kp = (2 * umma_k2(C, K) + kSlabBytes - 1) / kSlabBytes * kSlabBytes;
+    return align_up((size_t)N * Hp * Wp * Cp, 256) + align_up((size_t)n_chunks * 256 * Kp, 256) +
            align_up((size_t)Kp * 4, 256);
 }
 
 bool fxp_umma_supported(int C, int Hp, int Wp, long long K)
 {
-    // the offset table keeps an in-image offset in 30 bits
-    return (long long)C * Hp * Wp < (1LL << 30) && 2 * K <= (1 << 20);
+    // the offset table keeps an in-image byte offset in 30 bits
+    return (long long)((C + 15) / 16 * 16) * Hp * Wp < (1LL << 30) && 2 * umma_k2(C, K) <= (1 << 20);
 }
 
 int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
@@ -309,7 +363,8 @@ int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, i
     UmmaArgs a;
     const long long K = (long long)C * KH * KW;
     a.N = N; a.C = C; a.Hp = Hp; a.Wp = Wp; a.Co = Co; a.OH = OH; a.OW = OW; a.sh = sh; a.sw = sw;
-    a.Kp = (int)((2 * K + kSlabBytes - 1) / kSlabBytes * kSlabBytes);
+    a.Cp = (C + 15) / 16 * 16;
+    a.Kp = (int)((2 * umma_k2(C, K) + kSlabBytes - 1) / kSlabBytes * kSlabBytes);
     a.CB = Co < 128 ? Co : 128;
     a.CBp = (a.CB + 7) / 8 * 8;
     a.CBq = (a.CBp + 31) / 32 * 32;
@@ -322,26 +377,22 @@ int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, i
     const int n_chunks = (Co + a.CB - 1) / a.CB;
     uint8_t *w8 = static_cast<uint8_t *>(ws);
     int8_t *q8 = reinterpret_cast<int8_t *>(w8);
-    int8_t *wpk = reinterpret_cast<int8_t *>(w8 + align_up((size_t)N * C * Hp * Wp, 256));
+    int8_t *wpk = reinterpret_cast<int8_t *>(w8 + align_up((size_t)N * Hp * Wp * a.Cp, 256));
     int32_t *koff = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(wpk) +
                                                 align_up((size_t)n_chunks * a.NP * a.Kp, 256));
-    const long long n_act = (long long)N * C * Hp * Wp;
+    const long long n_act = (long long)N * Hp * Wp * (a.Cp / 16); // one thread per pixel and 16 channels
     fxp_umma_act_kernel<<<(unsigned)((n_act + 255) / 256 < 148 * 16 ? (n_act + 255) / 256 : 148 * 16), 256, 0, st>>>(
-        n_act, qa, q8);
+        a, qa, q8);
     REXSC_LAUNCH_CHECK("fxp_umma_act_kernel");
-    fxp_umma_pack_kernel<<<148 * 4, 256, 0, st>>>(a, (int)K, KH, KW, n_chunks, qp, qn, wpk, koff);
+    fxp_umma_pack_kernel<<<148 * 4, 256, 0, st>>>(a, KH, KW, n_chunks, qp, qn, wpk, koff);
     REXSC_LAUNCH_CHECK("fxp_umma_pack_kernel");
     const size_t smem = (size_t)kUmmaM * kSlabBytes + 256 * kSlabBytes + 64 + 1024;
     dim3 grid((unsigned)((a.M + kUmmaM - 1) / kUmmaM), (unsigned)n_chunks);
-    if (swizzled) {
-        REXSC_CUDA_CHECK(cudaFuncSetAttribute(fxp_conv_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)smem));
-        fxp_conv_umma_kernel<true><<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
-    } else {
-        REXSC_CUDA_CHECK(cudaFuncSetAttribute(fxp_conv_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)smem));
-        fxp_conv_umma_kernel<false><<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
-    }
+    const bool few_ctas = (long long)grid.x * grid.y <= 2 * 148;
+    auto kernel = swizzled ? (few_ctas ? fxp_conv_umma_kernel<true, true> : fxp_conv_umma_kernel<true, false>)
+                           : (few_ctas ? fxp_conv_umma_kernel<false, true> : fxp_conv_umma_kernel<false, false>);
+    REXSC_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kernel<<<grid, 128, smem, st>>>(a, q8, wpk, koff, out, status);
     REXSC_LAUNCH_CHECK("fxp_conv_umma_kernel");
     return REXSC_OK;
 }
