@@ -210,6 +210,57 @@ def test_linear_golden_and_oracle(ops, oracle):
     assert torch.equal(p.cpu(), rp) and torch.equal(n.cpu(), rn)
 
 
+def _torch_loop_linear_counts(x, w, L, seeds, or1):
+    """numpy restatement of the per-bit loop of the reference's linear_generic with generator='lfsr' and shared
+    generators (utils_functional.py:147-165 seeds, :254-271 LFSR per stream length, :1016-1036 loop): returns the
+    counts sum_t OR_c(a_t & w_t) (or the plain sums) per sign."""
+    l = {8: 3, 16: 4, 32: 5, 64: 6, 128: 7}[L]
+    taps = {3: (2, 1), 4: (3, 2), 5: (4, 2), 6: (5, 4), 7: (6, 5)}[l]
+    step = lambda v: (((v >> taps[0]) ^ (v >> taps[1])) & 1) | ((v << 1) & ((1 << l) - 1))
+    c = np.arange(x.shape[1])
+    ra, rp, rn = c % (L - 1) + 1, (c + seeds[0]) % (L - 1) + 1, (c + seeds[1]) % (L - 1) + 1
+    xa = x.astype(np.float64) * L
+    wp, wn = np.clip(w.astype(np.float64) * L, 0, None), np.clip(-w.astype(np.float64) * L, 0, None)
+    pos = np.zeros((x.shape[0], w.shape[0]), np.int64)
+    neg = np.zeros_like(pos)
+    for _ in range(L):
+        ra, rp, rn = step(ra), step(rp), step(rn)
+        a = (xa > ra).astype(np.int64)
+        sp, sn = a @ (wp > rp).astype(np.int64).T, a @ (wn > rn).astype(np.int64).T
+        pos += np.minimum(sp, 1) if or1 else sp
+        neg += np.minimum(sn, 1) if or1 else sn
+    return pos, neg
+
+
+@pytest.mark.parametrize("kernel", ["direct", "tiled", "tensor"])
+def test_linear_with_weight_seed_offsets(ops, kernel):
+    """rexsc_sc_linear_fwd_seeded on all three kernels: seed offsets (67, 37) give the counts of the front end's torch
+    bit loop (restated above), other offsets differ from the extension's (13, 13), negative offsets are refused."""
+    gen = torch.Generator().manual_seed(17)
+    for L, B, Cin, Cout in ((32, 9, 70, 33), (128, 5, 64, 64)):
+        top = (L - 1) / L
+        x = ((torch.rand(B, Cin, generator=gen) * 128).floor() / 128).clamp(max=top)
+        w = torch.randn(Cout, Cin, generator=gen) * 0.08
+        w[:, ::5] *= 6
+        w = ((w.clamp(-1, 1) * 128).round() / 128).clamp(-top, top)
+        for or_n in (1, 51201):
+            rp, rn = _torch_loop_linear_counts(x.numpy(), w.numpy(), L, (67, 37), or_n == 1)
+            ops.set_conv_kernel(kernel)
+            try:
+                p, n = ops.linear_generic_general_acc(x.cuda(), w.cuda(), PROG, L, -1, or_n - 1, 1, False, False,
+                                                      weight_seeds=(67, 37))
+                d, _ = ops.linear_generic_general_acc(x.cuda(), w.cuda(), PROG, L, -1, or_n - 1, 1, False, False)
+            except ValueError as exc:
+                assert kernel != "direct" and "UNSUPPORTED" in str(exc)
+                continue
+            finally:
+                ops.set_conv_kernel("auto")
+            assert np.array_equal(p.cpu().numpy(), rp) and np.array_equal(n.cpu().numpy(), rn), (kernel, L, or_n)
+            assert not torch.equal(p, d)
+    with pytest.raises(ValueError):
+        ops.linear_generic_general_acc(x.cuda(), w.cuda(), PROG, 32, -1, 0, 1, False, False, weight_seeds=(-1, 13))
+
+
 def test_lut_matches_oracle_streams(ops, oracle):
     for l, L, xnor in [(5, 32, True), (5, 32, False), (6, 64, True), (7, 128, False), (3, 8, True)]:
         lut = ops.build_lfsr_lut(l, L, 1, xnor).cpu().numpy().astype(np.uint32)
