@@ -87,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 // PREFETCH_B: also fetch the weight slab one step ahead (64 more registers: two CTAs per SM instead of four) -- pays
 // on grids of at most a wave or two of CTAs, whose time is one CTA's chain of slabs
 template <bool SWIZZLED, bool PREFETCH_B>
-__global__ void __launch_bounds__(128, PREFETCH_B ? 2 : 4)
+__global__ void __launch_bounds__(128, PREFETCH_B ? 2 : 6)
 fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *__restrict__ wpk,
                      const int32_t *__restrict__ koff, int32_t *__restrict__ out, int *__restrict__ status)
 {
@@ -96,7 +96,7 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
     uint8_t *smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     uint8_t *a_s = smem;                                   // 128 rows x 128 B
     uint8_t *b_s = smem + kUmmaM * kSlabBytes;             // NP rows x 128 B (1024-byte aligned: 16 KB offset)
-    uint64_t *bar = reinterpret_cast<uint64_t *>(b_s + 256 * kSlabBytes);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(b_s + a.NP * kSlabBytes);        // (the launch sizes the tile by NP)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -386,7 +386,8 @@ int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, i
     REXSC_LAUNCH_CHECK("fxp_umma_act_kernel");
     fxp_umma_pack_kernel<<<148 * 4, 256, 0, st>>>(a, KH, KW, n_chunks, qp, qn, wpk, koff);
     REXSC_LAUNCH_CHECK("fxp_umma_pack_kernel");
-    const size_t smem = (size_t)kUmmaM * kSlabBytes + 256 * kSlabBytes + 64 + 1024;
+    // operand tiles sized by the layer: narrow layers fit more CTAs per SM, which is what hides their load latency
+    const size_t smem = (size_t)kUmmaM * kSlabBytes + (size_t)a.NP * kSlabBytes + 64 + 1024;
     dim3 grid((unsigned)((a.M + kUmmaM - 1) / kUmmaM), (unsigned)n_chunks);
     const bool few_ctas = (long long)grid.x * grid.y <= 2 * 148;
     auto kernel = swizzled ? (few_ctas ? fxp_conv_umma_kernel<true, true> : fxp_conv_umma_kernel<true, false>)
