@@ -295,7 +295,7 @@ def run_sc(args, wl, rank, world, local_rank):
         out_pin[i] = (torch.empty(p.shape, dtype=p.dtype).contiguous(memory_format=fmt).pin_memory(),
                       torch.empty(n.shape, dtype=n.dtype).contiguous(memory_format=fmt).pin_memory())
     d2h = sum(out_pin[i][0].numel() * 2 * 2 * l["rep"] for i, l in enumerate(layers))
-    pipe = HostConvPipeline(dev)
+    pipe = HostConvPipeline(dev, slots=args.e2e_slots, chunks=args.e2e_chunks)
 
     def host_step(key):
         calls = []
@@ -511,6 +511,8 @@ def sc_line(args, wl, r, world):
         "tbitops_per_s": bitops_per_image(wl["layers"]) * value / 1e12,
         "e2e": {"value": e2e16, "unit": "img/s", "h2d_bytes_per_step": r["h2d16"], "d2h_bytes_per_step": r["d2h"],
                 "activations": "fp16 (what the front end passes under autocast)",
+                "pipeline": f"HostConvPipeline: copy-in / compute / copy-out of consecutive calls on three streams, "
+                            f"{args.e2e_slots} device staging buffers per tensor shape, {args.e2e_chunks} batch slice(s) per call",
                 "link_gbs_both_directions_busy": r["link"]},
         "e2e_fp32_activations": {"value": e2e32, "unit": "img/s", "h2d_bytes_per_step": r["h2d32"],
                                  "d2h_bytes_per_step": r["d2h"]},
@@ -820,6 +822,10 @@ def main():
     ap.add_argument("--train-steps", type=int, default=30)
     ap.add_argument("--train-warmup", type=int, default=10)
     ap.add_argument("--train-workload", default=None)
+    ap.add_argument("--e2e-slots", type=int, default=6,
+                    help="host-buffer leg: device staging buffers per tensor shape (how far copies may run ahead)")
+    ap.add_argument("--e2e-chunks", type=int, default=1,
+                    help="host-buffer leg: run every conv call as this many calls on slices of its batch")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

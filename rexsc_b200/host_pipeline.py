@@ -4,7 +4,9 @@
 are wanted in pinned host tensors, and overlaps the three phases of consecutive calls on three CUDA streams:
 host->device copy of call i+1, compute of call i, device->host copy of call i-1.  Device staging buffers are
 double-buffered per tensor shape.  Results are identical to calling ``ops.conv2d_generic_general_split_acc`` on
-device copies; only the schedule differs.
+device copies; only the schedule differs.  With ``chunks > 1`` every call is run as that many calls on consecutive
+slices of the batch (images are independent in the SC conv: seeds depend on channel and position only), which
+shortens the ramp at both ends of a run: the first copy-in and the last copy-out are a chunk long, not a batch long.
 """
 from __future__ import annotations
 
@@ -28,11 +30,22 @@ class HostConvCall:
         self.args = (bit_length, lfsr_length, 16, tuple(padding), tuple(stride), tuple(prog_load), bin_config,
                      gen_config, xnor, False)
 
+    def narrow(self, start: int, length: int) -> "HostConvCall":
+        """The same call on images [start, start + length) of the batch (views of the same host tensors)."""
+        sub = HostConvCall.__new__(HostConvCall)
+        sub.x_host = self.x_host.narrow(0, start, length)
+        sub.weight_dev = self.weight_dev
+        sub.out_pos_host = self.out_pos_host.narrow(0, start, length)
+        sub.out_neg_host = self.out_neg_host.narrow(0, start, length)
+        sub.args = self.args
+        return sub
+
 
 class HostConvPipeline:
-    def __init__(self, device, slots: int = 2):
+    def __init__(self, device, slots: int = 2, chunks: int = 1):
         self.device = torch.device(device)
         self.slots = slots
+        self.chunks = max(1, int(chunks))
         self.s_in = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
         self._stage: Dict[tuple, List[torch.Tensor]] = {}
@@ -56,6 +69,14 @@ class HostConvPipeline:
         free_after: Dict[int, torch.cuda.Event] = {}
         self.s_in.wait_stream(compute)
         self.s_out.wait_stream(compute)
+        if self.chunks > 1:
+            split = []
+            for c in calls:
+                n = c.x_host.size(0)
+                k = min(self.chunks, n)
+                bounds = [n * i // k for i in range(k + 1)]
+                split.extend(c.narrow(bounds[i], bounds[i + 1] - bounds[i]) for i in range(k))
+            calls = split
         for c in calls:
             xb = self._buffers("x", c.x_host)
             pb = self._buffers("p", c.out_pos_host)

@@ -8,7 +8,9 @@ from helpers import conv_inputs
 pytestmark = pytest.mark.gpu
 
 
-def test_pipeline_matches_plain_op(ops):
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_pipeline_matches_plain_op(ops, chunks):
+    """chunks = 3 runs every call as up to three calls on slices of its batch (uneven: 4 -> 1 + 1 + 2 images)."""
     from rexsc_b200.host_pipeline import HostConvCall, HostConvPipeline
 
     dev = torch.device("cuda", 0)
@@ -25,7 +27,7 @@ def test_pipeline_matches_plain_op(ops):
         hn = torch.empty_like(hp).pin_memory()
         calls.append(HostConvCall(x, wd, hp, hn, 32, (s, s), 1))
         expect.append((p.cpu(), n.cpu()))
-    pipe = HostConvPipeline(dev)
+    pipe = HostConvPipeline(dev, chunks=chunks)
     for _ in range(2):          # second round reuses every staging buffer
         for c in calls:
             c.out_pos_host.fill_(-1)
