@@ -74,7 +74,8 @@ FULL_SIZE_CASES = [
 @pytest.mark.parametrize("case", FULL_SIZE_CASES)
 def test_sc_conv_full_size_matches_reference_gpu_kernels(ops, ref_gpu, case):
     """Channels_last, XNOR generator (the front end's setting), full batch: every output count of the persistent
-    tensor-core path (many tiles per CTA, slot-split sums at 7x7) against the reference's kernels, bit for bit."""
+    tensor-core path (many tiles per CTA, compact grid chosen by the border check on caller-padded inputs, atomically
+    added cut tiles) against the reference's kernels, bit for bit."""
     N, C, H, Co, K, s, p, L, or_n = case
     g = torch.Generator(device="cuda").manual_seed(sum(case))
     x = torch.rand(N, C, H + 2 * p, H + 2 * p, device="cuda", generator=g)
