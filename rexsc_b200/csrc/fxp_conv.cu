@@ -237,9 +237,9 @@ __global__ void __launch_bounds__(128) fxp_conv_closed_kernel(FxpArgs a, const i
 
 size_t fxp_umma_workspace_bytes(int N, int C, int Hp, int Wp, int Co, long long K);
 bool fxp_umma_supported(int C, int Hp, int Wp, long long K);
-int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
-                         const int32_t *qa, const int32_t *qp, const int32_t *qn, void *ws, int32_t *out, int *status,
-                         bool swizzled, cudaStream_t st);
+int launch_fxp_conv_umma(int N, int C, int H, int W, int ph, int pw, int Co, int KH, int KW, int OH, int OW, int sh,
+                         int sw, int cap, float scale, const void *d_act, int act_dtype, const void *d_w, int w_dtype,
+                         void *ws, int32_t *out, int *status, bool swizzled, cudaStream_t st);
 
 struct FxpPlan {
     FxpArgs a;
@@ -289,10 +289,11 @@ static int make_fxp_plan(const rexsc_fxp_conv_desc *d, FxpPlan *p)
     if (d->kernel >= 2 && !p->umma) return REXSC_E_UNSUPPORTED;
     size_t off = 0;
     p->off_status = off; off += 256;
-    p->off_qa = off; off += align_up((size_t)n_act * 4, 256);
-    p->off_qp = off; off += align_up((size_t)a.Co * a.K * 4, 256);
-    p->off_qn = off; off += align_up((size_t)a.Co * a.K * 4, 256);
-    p->off_pk = off; off += align_up((size_t)p->Kw * 4 * p->Cop * 4, 256);
+    // (the tensor-core path quantises straight into its own int8 operands: no int32 intermediates)
+    p->off_qa = off; off += p->umma ? 0 : align_up((size_t)n_act * 4, 256);
+    p->off_qp = off; off += p->umma ? 0 : align_up((size_t)a.Co * a.K * 4, 256);
+    p->off_qn = off; off += p->umma ? 0 : align_up((size_t)a.Co * a.K * 4, 256);
+    p->off_pk = off; off += p->umma ? 0 : align_up((size_t)p->Kw * 4 * p->Cop * 4, 256);
     p->off_umma = off;
     if (p->umma) off += fxp_umma_workspace_bytes(a.N, a.C, a.Hp, a.Wp, a.Co, a.K);
     p->total = off;
@@ -326,6 +327,10 @@ extern "C" int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void 
     int *status = (int *)(ws + p.off_status);
     const FxpArgs &a = p.a;
     REXSC_CUDA_CHECK(cudaMemsetAsync(status, 0, 256, st));
+    if (p.umma) // quantises inside its own operand-preparation kernels
+        return launch_fxp_conv_umma(a.N, a.C, a.H, a.W, a.ph, a.pw, a.Co, a.KH, a.KW, a.OH, a.OW, a.sh, a.sw, p.cap,
+                                    a.scale, d_act, desc->act_dtype, d_weight, desc->w_dtype, ws + p.off_umma, d_out,
+                                    status, desc->kernel != 3, st);
     long long n_act = (long long)a.N * a.C * a.Hp * a.Wp;
     unsigned gb = (unsigned)((n_act + 255) / 256 < 148 * 32 ? (n_act + 255) / 256 : 148 * 32);
     switch (desc->act_dtype) {
@@ -342,10 +347,6 @@ extern "C" int rexsc_fxp_conv2d_fwd(const rexsc_fxp_conv_desc *desc, const void 
     default: fxp_quant_w_kernel<__nv_bfloat16><<<wb, 256, 0, st>>>(a, (const __nv_bfloat16 *)d_weight, qp, qn); break;
     }
     REXSC_LAUNCH_CHECK("fxp_quant_w_kernel");
-    if (p.umma) {
-        return launch_fxp_conv_umma(a.N, a.C, a.Hp, a.Wp, a.Co, a.KH, a.KW, a.OH, a.OW, a.sh, a.sw, p.cap, qa, qp, qn,
-                                    ws + p.off_umma, d_out, status, desc->kernel != 3, st);
-    }
     if (p.closed) {
         long long tot = (long long)p.Kw * p.Cop;
         fxp_pack_w_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(a, qp, qn, p.Kw, p.Cop, pk);

@@ -29,6 +29,8 @@ constexpr uint32_t kUmmaWaitLimit = 1u << 22;
 
 struct UmmaArgs {
     int N, C, Hp, Wp, Co, OH, OW, sh, sw;
+    int H, W, ph, pw; // unpadded activation and the op's zero padding (operand preparation)
+    float scale;      // 2^precision_in
     int Cp;          // channels padded to 16 (pixel pitch of the int8 activations, channel pitch of k')
     int Kp;          // k' extent padded to kSlabBytes (values + parity)
     int CB, CBp;     // output channels per CTA chunk, padded to 8
@@ -268,10 +270,13 @@ fxp_conv_umma_kernel(UmmaArgs a, const int8_t *__restrict__ act, const int8_t *_
 }
 
 // ---- operand preparation ------------------------------------------------------------------------------------
-// k' = tap * Cp + c for the values, K2 + tap * Cp + c for the parity bits (K2 = KH * KW * Cp); qp / qn are [co][c][tap]
-__global__ void fxp_umma_pack_kernel(UmmaArgs a, int KH, int KW, int n_chunks, const int32_t *__restrict__ qp,
-                                     const int32_t *__restrict__ qn, int8_t *__restrict__ wpk,
-                                     int32_t *__restrict__ koff)
+// Both kernels quantise on the fly (round-half-even of value * 2^p, fixed_cuda.cpp:28-30: activations clamped to
+// [0, 2^p - 1], weights split into a positive and a negative magnitude), so the tensor-core path needs two launches
+// before the conv kernel instead of four.
+// k' = tap * Cp + c for the values, K2 + tap * Cp + c for the parity bits (K2 = KH * KW * Cp); weights are [co][c][tap]
+template <typename T>
+__global__ void fxp_umma_pack_kernel(UmmaArgs a, int KH, int KW, int n_chunks, const T *__restrict__ w,
+                                     int8_t *__restrict__ wpk, int32_t *__restrict__ koff)
 {
     const int KHW = KH * KW, K2 = KHW * a.Cp;
     // weights: wpk[chunk][row n' in 0..NP)[k' in 0..Kp), row = sign * CBq + local channel
@@ -289,8 +294,8 @@ __global__ void fxp_umma_pack_kernel(UmmaArgs a, int KH, int KW, int n_chunks, c
             const int k = kp < K2 ? kp : kp - K2;
             const int tap = k / a.Cp, c = k - tap * a.Cp;
             if (c < a.C) {
-                const long long wi = ((long long)co * a.C + c) * KHW + tap;
-                v = sign ? qn[wi] : qp[wi];
+                const float x = load_as_float<T>(w, ((long long)co * a.C + c) * KHW + tap) * a.scale;
+                v = sign ? (int)rintf(-fminf(fmaxf(x, 1.f - a.scale), 0.f)) : (int)rintf(fminf(fmaxf(x, 0.f), a.scale - 1.f));
                 if (kp >= K2) v &= 1;
             }
         }
@@ -311,22 +316,32 @@ __global__ void fxp_umma_pack_kernel(UmmaArgs a, int KH, int KW, int n_chunks, c
     }
 }
 
-// int32 NCHW (padded tensor) -> int8 NHWC with the channels padded to Cp; one thread per pixel and 16 channels
-__global__ void fxp_umma_act_kernel(UmmaArgs a, const int32_t *__restrict__ q, int8_t *__restrict__ q8)
+// dense NCHW activations -> zero-padded int8 NHWC with the channels padded to Cp; one thread per padded pixel and 16
+// channels
+template <typename T>
+__global__ void fxp_umma_act_kernel(UmmaArgs a, const T *__restrict__ x, int8_t *__restrict__ q8)
 {
     const int groups = a.Cp / 16;
     const long long plane = (long long)a.Hp * a.Wp, total = (long long)a.N * plane * groups;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
-        // consecutive threads take consecutive pixels of one channel group: the strided int32 reads coalesce
+        // consecutive threads take consecutive pixels of one channel group: the strided reads coalesce
         const long long pix = i % plane;
         const long long t = i / plane;
         const int g = (int)(t % groups), n = (int)(t / groups);
+        const int h = (int)(pix / a.Wp), wq = (int)(pix - (long long)h * a.Wp);
+        const int hi = h - a.ph, wi = wq - a.pw;
         uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (hi >= 0 && hi < a.H && wi >= 0 && wi < a.W) {
 #pragma unroll
-        for (int b = 0; b < 16; b++) {
-            const int c = g * 16 + b;
-            if (c < a.C) w[b >> 2] |= (uint32_t)(q[((long long)n * a.C + c) * plane + pix] & 0xff) << (8 * (b & 3));
+            for (int b = 0; b < 16; b++) {
+                const int c = g * 16 + b;
+                if (c < a.C) {
+                    const float v = load_as_float<T>(x, (((long long)n * a.C + c) * a.H + hi) * a.W + wi) * a.scale;
+                    const int q = (int)rintf(fminf(fmaxf(v, 0.f), a.scale - 1.f));
+                    w[b >> 2] |= (uint32_t)(q & 0xff) << (8 * (b & 3));
+                }
+            }
         }
         *reinterpret_cast<uint4 *>(q8 + ((long long)n * plane + pix) * a.Cp + g * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -356,13 +371,15 @@ bool fxp_umma_supported(int C, int Hp, int Wp, long long K)
     return (long long)((C + 15) / 16 * 16) * Hp * Wp < (1LL << 30) && 2 * umma_k2(C, K) <= (1 << 20);
 }
 
-int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, int OH, int OW, int sh, int sw, int cap,
-                         const int32_t *qa, const int32_t *qp, const int32_t *qn, void *ws, int32_t *out, int *status,
-                         bool swizzled, cudaStream_t st)
+int launch_fxp_conv_umma(int N, int C, int H, int W, int ph, int pw, int Co, int KH, int KW, int OH, int OW, int sh,
+                         int sw, int cap, float scale, const void *d_act, int act_dtype, const void *d_w, int w_dtype,
+                         void *ws, int32_t *out, int *status, bool swizzled, cudaStream_t st)
 {
     UmmaArgs a;
+    const int Hp = H + 2 * ph, Wp = W + 2 * pw;
     const long long K = (long long)C * KH * KW;
     a.N = N; a.C = C; a.Hp = Hp; a.Wp = Wp; a.Co = Co; a.OH = OH; a.OW = OW; a.sh = sh; a.sw = sw;
+    a.H = H; a.W = W; a.ph = ph; a.pw = pw; a.scale = scale;
     a.Cp = (C + 15) / 16 * 16;
     a.Kp = (int)((2 * umma_k2(C, K) + kSlabBytes - 1) / kSlabBytes * kSlabBytes);
     a.CB = Co < 128 ? Co : 128;
@@ -381,10 +398,20 @@ int launch_fxp_conv_umma(int N, int C, int Hp, int Wp, int Co, int KH, int KW, i
     int32_t *koff = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(wpk) +
                                                 align_up((size_t)n_chunks * a.NP * a.Kp, 256));
     const long long n_act = (long long)N * Hp * Wp * (a.Cp / 16); // one thread per pixel and 16 channels
-    fxp_umma_act_kernel<<<(unsigned)((n_act + 255) / 256 < 148 * 16 ? (n_act + 255) / 256 : 148 * 16), 256, 0, st>>>(
-        a, qa, q8);
+    const unsigned ab = (unsigned)((n_act + 255) / 256 < 148 * 16 ? (n_act + 255) / 256 : 148 * 16);
+    switch (act_dtype) {
+    case REXSC_F32: fxp_umma_act_kernel<float><<<ab, 256, 0, st>>>(a, (const float *)d_act, q8); break;
+    case REXSC_F16: fxp_umma_act_kernel<__half><<<ab, 256, 0, st>>>(a, (const __half *)d_act, q8); break;
+    default: fxp_umma_act_kernel<__nv_bfloat16><<<ab, 256, 0, st>>>(a, (const __nv_bfloat16 *)d_act, q8); break;
+    }
     REXSC_LAUNCH_CHECK("fxp_umma_act_kernel");
-    fxp_umma_pack_kernel<<<148 * 4, 256, 0, st>>>(a, KH, KW, n_chunks, qp, qn, wpk, koff);
+    switch (w_dtype) {
+    case REXSC_F32: fxp_umma_pack_kernel<float><<<148 * 4, 256, 0, st>>>(a, KH, KW, n_chunks, (const float *)d_w, wpk, koff); break;
+    case REXSC_F16: fxp_umma_pack_kernel<__half><<<148 * 4, 256, 0, st>>>(a, KH, KW, n_chunks, (const __half *)d_w, wpk, koff); break;
+    default:
+        fxp_umma_pack_kernel<__nv_bfloat16><<<148 * 4, 256, 0, st>>>(a, KH, KW, n_chunks, (const __nv_bfloat16 *)d_w, wpk, koff);
+        break;
+    }
     REXSC_LAUNCH_CHECK("fxp_umma_pack_kernel");
     // operand tiles sized by the layer: narrow layers fit more CTAs per SM, which is what hides their load latency
     const size_t smem = (size_t)kUmmaM * kSlabBytes + (size_t)a.NP * kSlabBytes + 64 + 1024;
