@@ -360,7 +360,7 @@ def run_sc(args, wl, rank, world, local_rank):
     del din, dout
 
     # ---- accumulate kernels timed alone per layer with CUDA events (same stream, after the layer's expand stage) ----
-    per_kernel = {k: {"ms": 0.0, "products": 0, "launches": 0, "intops": 0.0, "lop3": 0.0, "bytes": 0}
+    per_kernel = {k: {"ms": 0.0, "products": 0, "launches": 0, "intops": 0.0, "lop3": 0.0, "bytes": 0, "plane_bytes": 0}
                   for k in ("tensor", "tiled", "direct")}
     per_layer = []
     exp_ms, exp_bytes = 0.0, 0
@@ -407,6 +407,7 @@ def run_sc(args, wl, rank, world, local_rank):
         k["lop3"] += l["rep"] * float(lop3_per_product) * products * ((slots + 31) // 32)
         # DRAM bytes the accumulate kernel has to move: the activation bit planes once + both int16 outputs
         k["bytes"] += l["rep"] * (plane_bytes + 2 * 2 * d.batch * oh * oh * d.c_out)
+        k["plane_bytes"] += l["rep"] * plane_bytes
         per_layer.append({"shape": list(l["shape"]), "L": slots, "kernel": which_kernel, "rep": l["rep"],
                           "expand_ms": round(best["expand"], 4), "accumulate_ms": round(best["accumulate"], 4),
                           "tbitops_per_s": round(2 * slots * products / (best["accumulate"] * 1e-3) / 1e12, 1)})
@@ -471,11 +472,13 @@ def sc_line(args, wl, r, world):
         "bound": "tensor", "kernel": "sc_conv_tc_kernel (tcgen05 int8, one GEMM per time slot)",
         "achieved": tc_achieved / 1e12, "peak": r["mma_peak_ops"] / 1e12, "unit": "TOP/s int8",
         "frac": tc_achieved / r["mma_peak_ops"],
-        # per average launch: algorithmic DRAM bytes x 1.035, the ratio of measured (ncu dram__bytes_read.sum +
-        # dram__bytes_write.sum = 62.5 MB) to algorithmic bytes (60.4 MB) of the captured 64-channel layer at
-        # batch 64; the traffic of this kernel grows in proportion to the batch (patch halo re-reads hit L2)
-        "traffic": (1.035 * t["bytes"] / t["launches"]) if t["launches"] else None,
-        "traffic_source": "ncu capture of one layer at batch 64, scaled by algorithmic bytes",
+        # per average launch: reads = 1.23 x the activation bit planes, the ratio of ncu's dram__bytes_read.sum
+        # (65.6 MB) to the planes (53.2 MB) of the captured 64-channel layer at batch 64 (patch halos, the
+        # read-modify-write of cut tiles and the weight planes make up the rest; it grows in proportion to the batch);
+        # writes = the int16 outputs (a single captured launch leaves most of them in L2 -- 13.0 of 51.4 MB had been
+        # written back when the capture ended -- a whole step, whose layers do not fit L2 together, writes them all)
+        "traffic": ((0.23 * t["plane_bytes"] + t["bytes"]) / t["launches"]) if t["launches"] else None,
+        "traffic_source": "ncu capture of one layer at batch 64 (read ratio), scaled by algorithmic bytes",
         "peak_source": "measured live: back-to-back tcgen05.mma kind::i8 M128 N128 K32 probe on this GPU",
         "kernel_ms_per_step": t["ms"], "launches_per_step": t["launches"],
         "tbitops_per_s_kernel": t["intops"] / 2 / (t["ms"] * 1e-3) / 1e12 if t["ms"] > 0 else 0.0,
