@@ -831,7 +831,10 @@ struct ActAsyncShared {
 
 // The pipelined expansion of all groups of this CTA.  lut_s: the doubled, padded table, already in shared memory;
 // raw_all: per warp (raw_stride bytes apart) two staging tiles of 32 pixels x 32 channels.
-// NCHW (fp32 only): the staged tile is [channel][pixel], fetched with 4-byte copies (one per channel and lane = pixel).
+// NCHW: the staged tile is [channel][pixel].  fp32: fetched with 4-byte copies (one per channel and lane = pixel).
+// 2-byte types (no 2-byte asynchronous copy exists): the next tile's 32 values per lane are loaded into registers
+// before the current tile is processed and written to the other staging tile after it, which hides their latency the
+// same way.
 template <typename T, int WORDS, bool NCHW = false>
 __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, const T *__restrict__ x,
                                                       const uint32_t *lut_s, uint8_t *raw_all, int raw_stride,
@@ -840,6 +843,8 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
 {
     constexpr int E = 16 / (int)sizeof(T), LPP = 32 / E, PPI = 32 / LPP; // elements per lane, lanes per pixel, pixels per pass
     constexpr int kRowBytes = 32 * (int)sizeof(T), kTileBytes = 32 * kRowBytes;
+    constexpr bool kRegStage = NCHW && sizeof(T) == 2; // staged through registers instead of cp.async
+    uint32_t pre[kRegStage ? 16 : 1];                  // two 2-byte values per register: channels 2i, 2i + 1
     auto &q_s = sh.q;
     auto &xb_s = sh.xb;
     auto &u_s = sh.u;
@@ -870,8 +875,30 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
         return r;
     };
     // start the copies of tile (group in xb_s[buf], channel word cw) into staging buffer `stage`
+    // kRegStage: write the values that `issue` loaded into staging tile `stage`, [channel][pixel]
+    auto land = [&](int stage) {
+        if (!kRegStage) return;
+        unsigned short *dst = reinterpret_cast<unsigned short *>(raw_s + stage * kTileBytes) + lane;
+#pragma unroll
+        for (int i = 0; i < (kRegStage ? 16 : 1); i++) {
+            dst[(2 * i) * 32] = (unsigned short)(pre[i] & 0xffffu);
+            dst[(2 * i + 1) * 32] = (unsigned short)(pre[i] >> 16);
+        }
+    };
     auto issue = [&](int buf, int cw, int stage) {
         uint8_t *dst = raw_s + stage * kTileBytes;
+        if (kRegStage) {
+            const long long xb = xb_s[warp][buf][lane], plane = (long long)a.H * a.W;
+            const unsigned short *x16 = reinterpret_cast<const unsigned short *>(x);
+#pragma unroll
+            for (int i = 0; i < (kRegStage ? 16 : 1); i++) {
+                const int c0 = cw * 32 + 2 * i;
+                const uint32_t lo = (xb >= 0 && c0 < a.C) ? (uint32_t)__ldg(x16 + xb + c0 * plane) : 0u;
+                const uint32_t hi = (xb >= 0 && c0 + 1 < a.C) ? (uint32_t)__ldg(x16 + xb + (c0 + 1) * plane) : 0u;
+                pre[i] = lo | (hi << 16);
+            }
+            return;
+        }
         if (NCHW) {
             const long long xb = xb_s[warp][buf][lane], plane = (long long)a.H * a.W;
 #pragma unroll 8
@@ -897,6 +924,7 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
     Pix cur = decode(grp, 0), nxt = cur;
     __syncwarp();
     issue(0, 0, 0);
+    land(0);
     int buf = 0, stage = 0;
     for (;;) {
         const long long grp_next = grp + stride;
@@ -905,21 +933,23 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
         __syncwarp();
         for (int cw = 0; cw < CW; cw++) {
             // keep the next tile's loads in flight while this one is processed
+            const bool more = cw + 1 < CW || has_next;
             if (cw + 1 < CW) issue(buf, cw + 1, stage ^ 1);
             else if (has_next) issue(buf ^ 1, 0, stage ^ 1);
-            else cp_async_commit(); // an empty group keeps the wait below uniform
-            cp_async_wait_all_but_one();
+            else if (!kRegStage) cp_async_commit(); // an empty group keeps the wait below uniform
+            if (!kRegStage) cp_async_wait_all_but_one();
             __syncwarp();
             // ---- quantise the staged 32 pixels x 32 channels into the byte tile ----
             {
                 const uint8_t *src = raw_s + stage * kTileBytes;
                 if (NCHW) {
                     // lane = pixel reads its column of the [channel][pixel] tile and packs four channels per store
-                    const float *col = reinterpret_cast<const float *>(src) + lane;
+                    const T *colT = reinterpret_cast<const T *>(src) + lane;
+                    auto col = [&](int c) { return load_as_float<T>(colT, (long long)c * 32); };
 #pragma unroll
                     for (int c4 = 0; c4 < 32; c4 += 4) {
-                        const uint32_t lo = prmt(quant_ceil_bits(col[c4 * 32], a.scale, top), quant_ceil_bits(col[(c4 + 1) * 32], a.scale, top), 0x0040u);
-                        const uint32_t hi2 = prmt(quant_ceil_bits(col[(c4 + 2) * 32], a.scale, top), quant_ceil_bits(col[(c4 + 3) * 32], a.scale, top), 0x0040u);
+                        const uint32_t lo = prmt(quant_ceil_bits(col(c4), a.scale, top), quant_ceil_bits(col(c4 + 1), a.scale, top), 0x0040u);
+                        const uint32_t hi2 = prmt(quant_ceil_bits(col(c4 + 2), a.scale, top), quant_ceil_bits(col(c4 + 3), a.scale, top), 0x0040u);
                         *reinterpret_cast<uint32_t *>(&q_s[warp][lane][c4]) = prmt(lo, hi2, 0x5410u);
                     }
                 } else {
@@ -959,6 +989,7 @@ __device__ __forceinline__ void expand_act_async_body(const ExpandActArgs &a, co
                 }
             }
             __syncwarp(); // the byte tile, the index table and this staging buffer may be rewritten
+            if (more) land(stage ^ 1);
             stage ^= 1;
         }
         if (!has_next) break;
@@ -1291,8 +1322,8 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     const int esz = d.act_dtype == REXSC_F32 ? 4 : 2;
     const bool nchw = !d.act_channels_last;
     if (nchw) {
-        // channel-planar inputs are staged with 4-byte copies: fp32 only
-        if (d.act_dtype != REXSC_F32 || (reinterpret_cast<uintptr_t>(d_act) & 3u) != 0) return REXSC_E_UNSUPPORTED;
+        // channel-planar inputs are staged element by element: 4-byte copies (fp32) or plain 2-byte loads
+        if ((reinterpret_cast<uintptr_t>(d_act) & (uintptr_t)(esz - 1)) != 0) return REXSC_E_UNSUPPORTED;
     } else if ((p.C % (16 / esz)) != 0 || (reinterpret_cast<uintptr_t>(d_act) & 15u) != 0) {
         return REXSC_E_UNSUPPORTED;
     }
@@ -1327,9 +1358,17 @@ int launch_expand_all_bits(const ConvPlan &p, const rexsc_sc_conv_desc &d, const
     const int CW = w.CW;
 #define REXSC_ALL(T) (p.words == 1 ? launch_expand_all_t<T, 1, false>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)   \
                                    : launch_expand_all_t<T, 2, false>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st))
-    if (nchw)
-        return p.words == 1 ? launch_expand_all_t<float, 1, true>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st)
-                            : launch_expand_all_t<float, 2, true>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st);
+#define REXSC_ALL_NCHW(T) (p.words == 1 ? launch_expand_all_t<T, 1, true>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st) \
+                                        : launch_expand_all_t<T, 2, true>(g, d_act, d_w, d_Ab, d_Wb, d_status, CW, lut_bytes, st))
+    if (nchw) {
+        switch (d.act_dtype) {
+        case REXSC_F32: return REXSC_ALL_NCHW(float);
+        case REXSC_F16: return REXSC_ALL_NCHW(__half);
+        case REXSC_BF16: return REXSC_ALL_NCHW(__nv_bfloat16);
+        default: return REXSC_E_BAD_ARG;
+        }
+    }
+#undef REXSC_ALL_NCHW
     switch (d.act_dtype) {
     case REXSC_F32: return REXSC_ALL(float);
     case REXSC_F16: return REXSC_ALL(__half);

@@ -395,7 +395,7 @@ COMPACT_CASES = [
     (37, 64, 7, 9, 128, 32, 2, True, torch.float16),    # tiles span images; half-precision staging
     (3, 96, 14, 14, 70, 64, 3, True, torch.float32),    # two word planes, ragged output channels
     (5, 64, 8, 8, 64, 32, 1, False, torch.float32),     # NCHW fp32: single-launch expand with 4-byte staging
-    (5, 40, 8, 6, 64, 32, 2, False, torch.float16),     # NCHW fp16: separate expand launches
+    (5, 40, 8, 6, 64, 32, 2, False, torch.float16),     # NCHW fp16: single-launch expand staged through registers
     (300, 32, 4, 4, 64, 32, 2, True, torch.float32),    # more tiles than SMs
 ]
 
