@@ -17,7 +17,9 @@ One JSON line is printed by rank 0:
   value      images/s with inputs resident in HBM, CUDA-event time, max over ranks, whole job
   e2e        the same through the op-level API with HOST (pinned) buffers: H2D of every layer's activation and
              D2H of every layer's int16 outputs inside the timed region (fp16 activations, as the front end passes
-             them under autocast; `e2e_fp32_activations` repeats it with fp32 activations)
+             them under autocast; `e2e_fp32_activations` repeats it with fp32 activations); --e2e-slots / --e2e-chunks
+             set the staging depth and the batch slicing of the host pipeline
+  gpu_launches  this library's kernels inside the timed region, as the library counts them
   roofline   dominant kernel: the tensor-core SC conv (one int8 tcgen05 GEMM per time slot) against the int8 tensor
              rate measured live by a back-to-back MMA probe; `roofline_secondary` / `roofline_expand` the ALU kernel
              and the stream-expansion stage; `roofline_pointwise` the four point-wise kernels against HBM
