@@ -491,7 +491,6 @@ template <typename T, int N> struct SingleBwd {
 // ---- fused calibration + injection forward: eight elements per thread per iteration ------------------------------
 template <typename T> struct V8;
 template <> struct V8<float> {
-    static constexpr int kAlign = 16;
     static __device__ __forceinline__ void load(const float *p, long long i, u64 (&v)[4])
     {
         const float4 a = __ldcs(reinterpret_cast<const float4 *>(p + i));
@@ -500,7 +499,6 @@ template <> struct V8<float> {
     }
 };
 template <> struct V8<__half> {
-    static constexpr int kAlign = 16;
     static __device__ __forceinline__ void load(const __half *p, long long i, u64 (&v)[4])
     {
         const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p + i));
@@ -513,7 +511,6 @@ template <> struct V8<__half> {
     }
 };
 template <> struct V8<__nv_bfloat16> {
-    static constexpr int kAlign = 16;
     static __device__ __forceinline__ void load(const __nv_bfloat16 *p, long long i, u64 (&v)[4])
     {
         const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(p + i));
